@@ -1,0 +1,140 @@
+"""ctypes binding of ``libhi2_b200.so`` (the C-ABI of ``include/hi2_b200.h``).
+
+There is no fallback: a missing library raises at first use, and every entry point returns a
+status that is turned into an exception here.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libhi2_b200.so"
+
+OK, ERR_ARG, ERR_LAUNCH, ERR_NOT_PD, ERR_TIMEOUT, ERR_CODE_RANGE, ERR_WORKSPACE, ERR_DRIVER = range(8)
+F32, F64, F16, BF16 = range(4)
+DTYPES = {torch.float32: F32, torch.float64: F64, torch.float16: F16, torch.bfloat16: BF16}
+
+_P, _I, _L, _Z, _F, _D = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float, C.c_double
+
+# name -> (restype, argtypes); mirrors include/hi2_b200.h line by line
+SIGNATURES = {
+    "hi2_abi_version": (_I, []),
+    "hi2_last_error": (C.c_char_p, []),
+    "hi2_rotate_groups": (_I, [_P, _I, _P, _I, _P, _P, _L, _L, _P]),
+    "hi2_pack_codes": (_I, [_P, _P, _L, _L, _I, _P, _P]),
+    "hi2_assemble_piece": (_I, [_P, _L, _P, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "hi2_ladder_grid": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _P, _P, _P, _P]),
+    "hi2_fit_ladder": (_I, [_P, _L, _P, _P, _I, _I, _I, _L, _L, _I, _P, _P, _P]),
+    "hi2_quantize_rows": (
+        _I,
+        [_P, _P, _P, _L, _P, _I, _L, _L, _I, _P, _P, _P, _P, _L, _P, _P, _P, _P],
+    ),
+    "hi2_gptq_block": (_I, [_P, _L, _L, _L, _I, _P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P]),
+    "hi2_gptq_lazy_update": (_I, [_P, _L, _L, _L, _L, _P, _P, _P]),
+    "hi2_gptq_round": (
+        _I,
+        [_P, _L, _L, _P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P],
+    ),
+    "hi2_ladder_sse": (_I, [_P, _P, _L, _P, _P, _P, _L, _L, _L, _I, _P, _P]),
+    "hi2_refine_block": (_I, [_P, _I, _P, _P, _P, _P, _P, _L, _L, _L, _P, _P]),
+    "hi2_gemm_f32": (_I, [_I, _I, _L, _L, _L, _F, _P, _L, _P, _L, _F, _P, _L, _P]),
+    "hi2_hessian_workspace_bytes": (_Z, [_L, _L, _I]),
+    "hi2_hessian_accumulate": (_I, [_P, _I, _L, _L, _P, _P, _Z, _P]),
+    "hi2_hessian_status": (_I, [_P, _P]),
+    "hi2_group_moments": (_I, [_P, _L, _P, _P]),
+    "hi2_transform_sigma": (_I, [_P, _F, _P, _P, _L, _P, _P, _P]),
+    "hi2_inverse_factor_workspace_bytes": (_Z, [_L]),
+    "hi2_inverse_factor": (_I, [_P, _P, _L, _P, _P, _Z, _P, _P]),
+    "hi2_allocate_solve": (_I, [_P, _P, _I, _L, _D, _P, _P, _P]),
+}
+
+_lock = threading.Lock()
+_lib = None
+_failed: str | None = None
+
+
+def load():
+    """The loaded library.  Raises ``RuntimeError`` when it is missing or lacks a symbol."""
+    global _lib, _failed
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not LIB_PATH.exists():
+            _failed = f"{LIB_PATH} not found: build it with `python -m hi2_b200.build`"
+            raise RuntimeError(_failed)
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            try:
+                fn = getattr(lib, name)
+            except AttributeError as e:
+                _failed = f"{LIB_PATH} does not export {name}"
+                raise RuntimeError(_failed) from e
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+        return lib
+
+
+def failure() -> str | None:
+    return _failed
+
+
+def last_error() -> str:
+    return load().hi2_last_error().decode(errors="replace")
+
+
+def check(rc: int, what: str) -> None:
+    if rc == OK:
+        return
+    msg = f"{what}: {last_error()} (status {rc})"
+    if rc == ERR_ARG:
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def call(name: str, *args) -> None:
+    """Invoke an ``int``-returning entry point and raise on a non-zero status."""
+    check(getattr(load(), name)(*args), name)
+
+
+def ptr(t: torch.Tensor | None):
+    """Device address of a tensor (``None`` -> null)."""
+    if t is None:
+        return None
+    return C.c_void_p(t.data_ptr())
+
+
+def stream(device=None):
+    """The current CUDA stream of ``device`` as an opaque pointer."""
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def need_cuda(*tensors: torch.Tensor) -> torch.device:
+    """All tensors on one CUDA device; this package has no CPU path."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "hi2_b200 runs on CUDA devices only (got a tensor on " f"{t.device}); there is no CPU path"
+            )
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    return dev
+
+
+def host_floats(values):
+    arr = (C.c_float * len(values))(*[float(v) for v in values])
+    return arr
+
+
+def host_i64(values):
+    return (C.c_int64 * len(values))(*[int(v) for v in values])

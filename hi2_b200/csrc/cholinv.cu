@@ -1,0 +1,187 @@
+// Damped inverse factor (hi2/hessian.py:71-86): the upper-triangular U with
+// U^T U = (hs + lam I)^-1.
+//
+// The reference factorises, inverts and factorises again.  The same U has a closed form: with J
+// the index reversal, J (hs + lam I) J = L L^T (L lower) gives U = J L^-1 J.  So one Cholesky
+// factorisation and one triangular inverse suffice, and both come out of one recursion on the
+// reversed matrix A (fp64, lower part):
+//
+//   F(A):  split A = [A11 . ; A21 A22]
+//          (X11) = F(A11)                      X11 = L11^-1
+//          W     = A21 X11^T                   (= L21)
+//          A22  -= W W^T
+//          T     = W X11
+//          (X22) = F(A22)
+//          X21   = -X22 T
+//
+// Every step above the 64-wide leaves is a matrix product (gemm.cuh, fp64 FMA, triangular
+// operands expressed as k-ranges); a leaf factorises and inverts one 64x64 block in shared
+// memory.  W is kept in the X21 slot and T in the A21 slot, so the scratch is 2 K^2 doubles.
+// fp64 keeps the explicit-inverse solves far below fp32 rounding, so U is accurate to the final
+// conversion.  A non-positive pivot does not trap: the leaf records its index in *info, carries
+// on with a unit pivot, and the host retries with more damping.
+#include "gemm.cuh"
+
+namespace hi2 {
+namespace {
+
+constexpr int NB = 64;
+constexpr int LDL = NB + 1;
+constexpr size_t LEAF_SMEM = 2 * NB * LDL * sizeof(double);
+
+// A[i][j] = hs[k-1-i][k-1-j] (+ lam on the diagonal, added in fp32 as the reference does).
+__global__ void __launch_bounds__(256)
+reverse_damp_kernel(const float* __restrict__ hs, const float* __restrict__ lam, int64_t k,
+                    double* __restrict__ a) {
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= k * k) return;
+  const int64_t i = idx / k, j = idx % k;
+  float v = hs[(k - 1 - i) * k + (k - 1 - j)];
+  if (i == j) v = v + *lam;
+  a[idx] = (double)v;
+}
+
+// u[i][j] = (float) x[k-1-i][k-1-j]
+__global__ void __launch_bounds__(256)
+reverse_store_kernel(const double* __restrict__ x, int64_t k, float* __restrict__ u) {
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (idx >= k * k) return;
+  const int64_t i = idx / k, j = idx % k;
+  u[idx] = (float)x[(k - 1 - i) * k + (k - 1 - j)];
+}
+
+// Factorise the n x n (n <= 64) diagonal block at `off` (lower part of a, leading dim ld) and
+// write its inverse, zeros above the diagonal included, to the same place of x.
+__global__ void __launch_bounds__(256)
+leaf_kernel(const double* __restrict__ a, double* __restrict__ x, int64_t ld, int64_t off, int n,
+            int32_t* info) {
+  extern __shared__ double leaf_smem[];
+  double (*L)[LDL] = reinterpret_cast<double (*)[LDL]>(leaf_smem);
+  double (*X)[LDL] = reinterpret_cast<double (*)[LDL]>(leaf_smem + NB * LDL);
+  const int tid = threadIdx.x;
+  const double* src = a + off * ld + off;
+  for (int idx = tid; idx < NB * NB; idx += 256) {
+    const int i = idx / NB, j = idx % NB;
+    L[i][j] = (i < n && j <= i) ? src[(int64_t)i * ld + j] : 0.0;
+    X[i][j] = 0.0;
+  }
+  __syncthreads();
+  for (int j = 0; j < n; ++j) {
+    double piv = L[j][j];
+    if (!(piv > 0.0)) {  // also catches NaN
+      if (tid == 0) atomicCAS(info, 0, (int32_t)(off + j + 1));
+      piv = 1.0;
+    }
+    const double dj = sqrt(piv);
+    __syncthreads();  // everyone has read L[j][j]
+    for (int i = j + tid; i < n; i += 256) L[i][j] = (i == j) ? dj : L[i][j] / dj;
+    __syncthreads();
+    // trailing update of the lower part: (i, c) with j < c <= i < n
+    const int rem = n - j - 1;
+    for (int idx = tid; idx < rem * rem; idx += 256) {
+      const int i = j + 1 + idx / rem, c = j + 1 + idx % rem;
+      if (c <= i) L[i][c] = fma(-L[i][j], L[c][j], L[i][c]);
+    }
+    __syncthreads();
+  }
+  // X = L^-1 by forward substitution, one column per thread
+  if (tid < n) {
+    const int c = tid;
+    X[c][c] = 1.0 / L[c][c];
+    for (int i = c + 1; i < n; ++i) {
+      double acc = 0.0;
+      for (int q = c; q < i; ++q) acc = fma(L[i][q], X[q][c], acc);
+      X[i][c] = -acc / L[i][i];
+    }
+  }
+  __syncthreads();
+  double* dst = x + off * ld + off;
+  for (int idx = tid; idx < n * n; idx += 256) {
+    const int i = idx / n, j = idx % n;
+    dst[(int64_t)i * ld + j] = X[i][j];
+  }
+}
+
+struct Plan {
+  double* a;
+  double* x;
+  int64_t k;
+  int32_t* info;
+  cudaStream_t stream;
+};
+
+int product(bool trans_b, int64_t m, int64_t n, int64_t kk, double alpha, const double* a,
+            const double* b, double beta, double* c, int64_t ld, int flags, cudaStream_t stream) {
+  GemmArgs<double, double, double> p;
+  p.m = m, p.n = n, p.kk = kk, p.alpha = alpha, p.beta = beta;
+  p.a = a, p.lda = ld, p.b = b, p.ldb = ld, p.c = c, p.ldc = ld, p.flags = flags;
+  return launch_gemm<double, double, double, 8, 4, 16>(false, trans_b, p, stream, "inverse_factor");
+}
+
+int factor(const Plan& pl, int64_t off, int64_t n) {
+  const int64_t ld = pl.k;
+  if (n <= NB) {
+    leaf_kernel<<<1, 256, LEAF_SMEM, pl.stream>>>(pl.a, pl.x, ld, off, (int)n, pl.info);
+    return check_launch("inverse_factor leaf");
+  }
+  const int64_t blocks = ceil_div(n, NB);
+  const int64_t n1 = ((blocks + 1) / 2) * NB, n2 = n - n1;
+  int rc = factor(pl, off, n1);
+  if (rc != HI2_OK) return rc;
+  double* a21 = pl.a + (off + n1) * ld + off;
+  double* a22 = pl.a + (off + n1) * ld + off + n1;
+  double* x11 = pl.x + off * ld + off;
+  double* x21 = pl.x + (off + n1) * ld + off;
+  double* x22 = pl.x + (off + n1) * ld + off + n1;
+  // W (in the X21 slot) = A21 X11^T
+  rc = product(true, n2, n1, n1, 1.0, a21, x11, 0.0, x21, ld, GEMM_KB_LE_J, pl.stream);
+  if (rc != HI2_OK) return rc;
+  // A22 -= W W^T (lower tiles)
+  rc = product(true, n2, n2, n1, -1.0, x21, x21, 1.0, a22, ld, GEMM_LOWER_OUT, pl.stream);
+  if (rc != HI2_OK) return rc;
+  // T (in the A21 slot) = W X11
+  rc = product(false, n2, n1, n1, 1.0, x21, x11, 0.0, a21, ld, GEMM_KB_GE_J, pl.stream);
+  if (rc != HI2_OK) return rc;
+  rc = factor(pl, off + n1, n2);
+  if (rc != HI2_OK) return rc;
+  // X21 = -X22 T
+  return product(false, n2, n1, n2, -1.0, x22, a21, 0.0, x21, ld, GEMM_KA_LE_I, pl.stream);
+}
+
+}  // namespace
+}  // namespace hi2
+
+extern "C" size_t hi2_inverse_factor_workspace_bytes(int64_t k) {
+  return k > 0 ? (size_t)k * (size_t)k * 2 * sizeof(double) : 0;
+}
+
+extern "C" int hi2_inverse_factor(const float* hs, const float* lam, int64_t k, float* u,
+                                  void* workspace, size_t workspace_bytes, int32_t* info,
+                                  void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(k > 0, "inverse_factor: k must be positive");
+  HI2_REQUIRE(hs && lam && u && info && workspace, "inverse_factor: null pointer");
+  if (workspace_bytes < hi2_inverse_factor_workspace_bytes(k))
+    return fail(HI2_ERR_WORKSPACE, "inverse_factor: workspace too small");
+  HI2_REQUIRE(aligned16(workspace), "inverse_factor: workspace must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {  // per device, so not cached: a process may drive several
+    if (cudaFuncSetAttribute(leaf_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)LEAF_SMEM) != cudaSuccess)
+      return fail(HI2_ERR_LAUNCH, "inverse_factor: cannot reserve shared memory");
+  }
+  Plan pl;
+  pl.a = static_cast<double*>(workspace);
+  pl.x = pl.a + k * k;
+  pl.k = k, pl.info = info, pl.stream = s;
+  const unsigned grid = (unsigned)ceil_div(k * k, 256);
+  reverse_damp_kernel<<<grid, 256, 0, s>>>(hs, lam, k, pl.a);
+  int rc = check_launch("inverse_factor reverse");
+  if (rc != HI2_OK) return rc;
+  if (cudaMemsetAsync(pl.x, 0, (size_t)k * k * sizeof(double), s) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "inverse_factor: memset failed");
+  rc = factor(pl, 0, k);
+  if (rc != HI2_OK) return rc;
+  reverse_store_kernel<<<grid, 256, 0, s>>>(pl.x, k, u);
+  return check_launch("inverse_factor store");
+}

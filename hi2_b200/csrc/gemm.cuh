@@ -1,0 +1,169 @@
+// Register-tiled FMA matrix product used where the path needs full fp32 / fp64 accuracy with
+// every operand in its storage precision: the lazy trailing update of GPTQ, the products of the
+// refinement sweep, and the fp64 products of the blocked inverse factor.
+//
+//   C[m, n] = alpha * sum_k opA[m, k] * opB[k, n] + beta * C[m, n]        (row-major)
+//
+// 256 threads as a 16 x 16 grid; a thread owns TM x TN outputs laid out in 16-byte pieces that
+// are 16 pieces apart, so the shared-memory reads of a warp are contiguous (B side) or a
+// broadcast (A side).  Global tiles are fetched into registers one step ahead of the math.
+// Triangular structure of an operand is expressed as a k-range per output tile.
+#pragma once
+
+#include "common.cuh"
+
+namespace hi2 {
+
+enum : int {
+  GEMM_LOWER_OUT = 1,  // skip output tiles that lie strictly above the diagonal
+  GEMM_KA_LE_I = 2,    // opA[i, k] == 0 for k > i   (A lower triangular, square with the rows)
+  GEMM_KB_GE_J = 4,    // opB[k, j] == 0 for k < j   (B lower triangular, not transposed)
+  GEMM_KB_LE_J = 8,    // opB[k, j] == 0 for k > j   (B = L^T with L lower triangular)
+};
+
+template <typename T, typename TA, typename TB>
+struct GemmArgs {
+  int64_t m, n, kk;
+  T alpha, beta;
+  const TA* a;
+  int64_t lda;
+  const TB* b;
+  int64_t ldb;
+  T* c;
+  int64_t ldc;
+  int flags;
+};
+
+template <typename T>
+__device__ __forceinline__ T fma_t(T a, T b, T c);
+template <>
+__device__ __forceinline__ float fma_t<float>(float a, float b, float c) { return fmaf(a, b, c); }
+template <>
+__device__ __forceinline__ double fma_t<double>(double a, double b, double c) { return fma(a, b, c); }
+
+template <typename T, typename S>
+__device__ __forceinline__ T widen(S v) { return (T)v; }
+template <>
+__device__ __forceinline__ float widen<float, __nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float widen<float, __half>(__half v) { return __half2float(v); }
+
+template <typename T, typename TA, typename TB, int TM, int TN, int BK, bool TRANS_A, bool TRANS_B>
+__global__ void __launch_bounds__(256)
+gemm_kernel(const GemmArgs<T, TA, TB> p) {
+  constexpr int V = 16 / sizeof(T);  // elements per 16-byte piece
+  constexpr int BM = 16 * TM, BN = 16 * TN;
+  constexpr int NT = 256;
+  constexpr int A_PER = BM * BK / NT, B_PER = BN * BK / NT;
+  static_assert(TM % V == 0 && TN % V == 0, "micro-tile must be whole 16-byte pieces");
+  static_assert((BM * BK) % NT == 0 && (BN * BK) % NT == 0, "tile loads must divide evenly");
+
+  __shared__ __align__(16) T As[BK][BM + V];
+  __shared__ __align__(16) T Bs[BK][BN + V];
+
+  const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
+  if ((p.flags & GEMM_LOWER_OUT) && n0 > m0 + BM - 1) return;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+
+  int64_t k_lo = 0, k_hi = p.kk;
+  if (p.flags & GEMM_KA_LE_I) k_hi = min(k_hi, m0 + BM);
+  if (p.flags & GEMM_KB_LE_J) k_hi = min(k_hi, n0 + BN);
+  if (p.flags & GEMM_KB_GE_J) k_lo = (n0 / BK) * BK;
+
+  T acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = T(0);
+
+  T ra[A_PER], rb[B_PER];
+  auto fetch = [&](int64_t k0) {
+#pragma unroll
+    for (int s = 0; s < A_PER; ++s) {
+      const int idx = tid + s * NT;
+      const int mi = TRANS_A ? idx % BM : idx / BK, ki = TRANS_A ? idx / BM : idx % BK;
+      const int64_t gm = m0 + mi, gk = k0 + ki;
+      T v = T(0);
+      if (gm < p.m && gk < k_hi)
+        v = widen<T, TA>(TRANS_A ? p.a[gk * p.lda + gm] : p.a[gm * p.lda + gk]);
+      ra[s] = v;
+    }
+#pragma unroll
+    for (int s = 0; s < B_PER; ++s) {
+      const int idx = tid + s * NT;
+      const int ni = TRANS_B ? idx / BK : idx % BN, ki = TRANS_B ? idx % BK : idx / BN;
+      const int64_t gn = n0 + ni, gk = k0 + ki;
+      T v = T(0);
+      if (gn < p.n && gk < k_hi)
+        v = widen<T, TB>(TRANS_B ? p.b[gn * p.ldb + gk] : p.b[gk * p.ldb + gn]);
+      rb[s] = v;
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int s = 0; s < A_PER; ++s) {
+      const int idx = tid + s * NT;
+      const int mi = TRANS_A ? idx % BM : idx / BK, ki = TRANS_A ? idx / BM : idx % BK;
+      As[ki][mi] = ra[s];
+    }
+#pragma unroll
+    for (int s = 0; s < B_PER; ++s) {
+      const int idx = tid + s * NT;
+      const int ni = TRANS_B ? idx / BK : idx % BN, ki = TRANS_B ? idx % BK : idx / BN;
+      Bs[ki][ni] = rb[s];
+    }
+  };
+
+  if (k_lo < k_hi) fetch(k_lo);
+  for (int64_t k0 = k_lo; k0 < k_hi; k0 += BK) {
+    stash();
+    __syncthreads();
+    if (k0 + BK < k_hi) fetch(k0 + BK);
+#pragma unroll
+    for (int ki = 0; ki < BK; ++ki) {
+      T fa[TM], fb[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) fa[i] = As[ki][(i / V) * (16 * V) + ty * V + (i % V)];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) fb[j] = Bs[ki][(j / V) * (16 * V) + tx * V + (j % V)];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fma_t<T>(fa[i], fb[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int64_t gm = m0 + (i / V) * (16 * V) + ty * V + (i % V);
+    if (gm >= p.m) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int64_t gn = n0 + (j / V) * (16 * V) + tx * V + (j % V);
+      if (gn >= p.n) continue;
+      T* dst = p.c + gm * p.ldc + gn;
+      T v = p.alpha * acc[i][j];
+      if (p.beta != T(0)) v = v + p.beta * *dst;
+      *dst = v;
+    }
+  }
+}
+
+template <typename T, typename TA, typename TB, int TM, int TN, int BK>
+int launch_gemm(bool trans_a, bool trans_b, const GemmArgs<T, TA, TB>& p, cudaStream_t stream,
+                const char* what) {
+  if (p.m <= 0 || p.n <= 0) return HI2_OK;
+  dim3 grid((unsigned)ceil_div(p.n, 16 * TN), (unsigned)ceil_div(p.m, 16 * TM));
+  if (!trans_a && !trans_b)
+    gemm_kernel<T, TA, TB, TM, TN, BK, false, false><<<grid, 256, 0, stream>>>(p);
+  else if (!trans_a && trans_b)
+    gemm_kernel<T, TA, TB, TM, TN, BK, false, true><<<grid, 256, 0, stream>>>(p);
+  else if (trans_a && !trans_b)
+    gemm_kernel<T, TA, TB, TM, TN, BK, true, false><<<grid, 256, 0, stream>>>(p);
+  else
+    gemm_kernel<T, TA, TB, TM, TN, BK, true, true><<<grid, 256, 0, stream>>>(p);
+  return check_launch(what);
+}
+
+}  // namespace hi2

@@ -1,0 +1,372 @@
+// Ladder search and row quantisation (hi2/encode.py:53-173, hi2/ladder_kernel.py:44-101).
+//
+// fit kernel   one thread per (row, block).  The 32 lanes of a warp take 32 consecutive ROWS of
+//              the same block, so the column weights d of the block are warp-uniform (one
+//              broadcast load serves the warp) and the block's weights stay in registers for the
+//              whole grid search and the least-squares refits.  The work is ~800 fp32
+//              instructions per weight (effort "normal") against 4 bytes read: ALU-bound.
+// row kernel   one thread block per row: row-wide extrema of (lo, step), the three fp16 row
+//              constants, the parameter bytes, the decoded fp16 ladders, and optionally the
+//              nearest codes and the weighted error of the row.  One pass over the row: HBM-bound.
+#include "common.cuh"
+
+namespace hi2 {
+namespace {
+
+struct GridSpec {
+  float v[8];
+  int g;
+};
+
+template <int B>
+__device__ __forceinline__ float block_error(const float (&x)[B], const float* __restrict__ dd,
+                                             float lo, float step, float nmax) {
+  const float safe = (step == 0.0f) ? 1.0f : step;
+  float err = 0.0f;
+#pragma unroll
+  for (int t = 0; t < B; ++t) {
+    float q = rintf(__fdiv_rn(x[t] - lo, safe));
+    q = fminf(fmaxf(q, 0.0f), nmax);
+    const float diff = (lo + q * step) - x[t];
+    err += __ldg(dd + t) * (diff * diff);
+  }
+  return err;
+}
+
+template <int B>
+__global__ void __launch_bounds__(256)
+fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, int64_t n_rows,
+           int64_t nb, GridSpec grid, int refits, float nmax, float* __restrict__ lo_out,
+           float* __restrict__ st_out, float* __restrict__ err_out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t blk = (int64_t)blockIdx.y * 8 + warp;
+  if (blk >= nb) return;  // uniform over the warp
+  const int64_t row = (int64_t)blockIdx.x * 32 + lane;
+  const bool live = row < n_rows;
+  const float* src = w + (live ? row : n_rows - 1) * ldw + blk * B;
+  const float* dd = d + blk * B;
+
+  float x[B];
+#pragma unroll
+  for (int t = 0; t < B; t += 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src + t);
+    x[t] = v.x, x[t + 1] = v.y, x[t + 2] = v.z, x[t + 3] = v.w;
+  }
+  float mn = x[0], mx = x[0];
+#pragma unroll
+  for (int t = 1; t < B; ++t) mn = fminf(mn, x[t]), mx = fmaxf(mx, x[t]);
+  const float span = mx - mn;
+
+  float best_lo = 0.0f, best_st = 0.0f, best_err = 0.0f;
+  for (int gi = 0; gi < grid.g; ++gi) {
+    const float lo = mn + grid.v[gi] * span;
+    for (int gj = 0; gj < grid.g; ++gj) {
+      const float step = __fdiv_rn((mx - grid.v[gj] * span) - lo, nmax);
+      const float err = block_error<B>(x, dd, lo, step, nmax);
+      if ((gi | gj) == 0 || err < best_err) best_lo = lo, best_st = step, best_err = err;
+    }
+  }
+
+  for (int it = 0; it < refits; ++it) {
+    const float safe = (best_st == 0.0f) ? 1.0f : best_st;
+    float sd = 0.f, sc = 0.f, scc = 0.f, sw = 0.f, scw = 0.f, sum = 0.f;
+#pragma unroll
+    for (int t = 0; t < B; ++t) {
+      float c = rintf(__fdiv_rn(x[t] - best_lo, safe));
+      c = fminf(fmaxf(c, 0.0f), nmax);
+      const float dt = __ldg(dd + t), dc = dt * c;
+      sd += dt;
+      sc += dc;
+      scc += dc * c;
+      sw += dt * x[t];
+      scw += dc * x[t];
+      sum += x[t];
+    }
+    const float det = sd * scc - sc * sc;
+    const bool ok = fabsf(det) > 1e-20f;
+    const float step = ok ? __fdiv_rn(sd * scw - sc * sw, det) : 0.0f;
+    const float lo = ok ? __fdiv_rn(sw - step * sc, fmaxf(sd, 1e-20f)) : __fdiv_rn(sum, (float)B);
+    const float err = block_error<B>(x, dd, lo, step, nmax);
+    if (err < best_err && step > 0.0f) best_lo = lo, best_st = step, best_err = err;
+  }
+
+  if (live) {
+    const int64_t o = row * nb + blk;
+    lo_out[o] = best_lo;
+    st_out[o] = best_st;
+    if (err_out != nullptr) err_out[o] = best_err;
+  }
+}
+
+int launch_fit(const float* w, int64_t ldw, const float* d, const float* grid_host, int g,
+               int refits, int n, int64_t n_rows, int64_t nb, int block, float* lo, float* st,
+               float* err, cudaStream_t stream) {
+  GridSpec spec;
+  spec.g = g;
+  for (int i = 0; i < 8; ++i) spec.v[i] = i < g ? grid_host[i] : 0.0f;
+  dim3 grid((unsigned)ceil_div(n_rows, 32), (unsigned)ceil_div(nb, 8));
+  const float nmax = (float)(n - 1);
+#define HI2_FIT(BB)                                                                              \
+  fit_kernel<BB><<<grid, 256, 0, stream>>>(w, ldw, d, n_rows, nb, spec, refits, nmax, lo, st, err)
+  if (block == 16) HI2_FIT(16);
+  if (block == 32) HI2_FIT(32);
+  if (block == 64) HI2_FIT(64);
+#undef HI2_FIT
+  return check_launch("fit_ladder");
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+constexpr int ROW_THREADS = 256;
+
+// Dynamic shared memory: decoded lo[nb], step[nb].
+template <int B>
+__global__ void __launch_bounds__(ROW_THREADS)
+row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
+           const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, float nmax,
+           int64_t n_rows, int64_t k, uint8_t* __restrict__ params, uint16_t* __restrict__ consts,
+           float* __restrict__ lo_d, float* __restrict__ st_d, int64_t ldp,
+           uint8_t* __restrict__ codes, float* __restrict__ sse, float* __restrict__ energy) {
+  extern __shared__ float dyn[];
+  __shared__ float red[3][ROW_THREADS / 32];
+  const int64_t nb = k / B;
+  float* s_lo = dyn;
+  float* s_st = dyn + nb;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    const float* lo_r = lo_in + row * nb;
+    const float* st_r = st_in + row * nb;
+    // ---- row-wide extrema -----------------------------------------------------------------
+    float mxst = -INFINITY, mnlo = INFINITY, mxlo = -INFINITY;
+    for (int64_t b = tid; b < nb; b += ROW_THREADS) {
+      const float s = st_r[b], l = lo_r[b];
+      mxst = fmaxf(mxst, s < 0.0f ? 0.0f : s);
+      mnlo = fminf(mnlo, l);
+      mxlo = fmaxf(mxlo, l);
+    }
+    mxst = warp_max(mxst), mnlo = warp_min(mnlo), mxlo = warp_max(mxlo);
+    __syncthreads();  // previous row's readers of red[] and dyn[] are done
+    if (lane == 0) red[0][warp] = mxst, red[1][warp] = mnlo, red[2][warp] = mxlo;
+    __syncthreads();
+    mxst = red[0][0], mnlo = red[1][0], mxlo = red[2][0];
+#pragma unroll
+    for (int i = 1; i < ROW_THREADS / 32; ++i) {
+      mxst = fmaxf(mxst, red[0][i]);
+      mnlo = fminf(mnlo, red[1][i]);
+      mxlo = fmaxf(mxlo, red[2][i]);
+    }
+    // ---- the three fp16 row constants -------------------------------------------------------
+    const __half ss_h = __float2half_rn(__fdiv_rn(mxst, 255.0f));
+    const float ss = __half2float(ss_h);
+    const __half lm_h = __float2half_rn(mnlo);
+    const float lm = __half2float(lm_h);
+    float spread = mxlo - lm;
+    spread = spread < 0.0f ? 0.0f : spread;
+    const __half ls_h = __float2half_rn(__fdiv_rn(spread, 255.0f));
+    const float ls = __half2float(ls_h);
+    if (tid == 0 && consts != nullptr) {
+      consts[row * 3 + 0] = __half_as_ushort(lm_h);
+      consts[row * 3 + 1] = __half_as_ushort(ls_h);
+      consts[row * 3 + 2] = __half_as_ushort(ss_h);
+    }
+    // ---- parameter bytes and decoded ladders ------------------------------------------------
+    for (int64_t b = tid; b < nb; b += ROW_THREADS) {
+      float s = st_r[b];
+      s = s < 0.0f ? 0.0f : s;
+      float su = 0.0f, lu = 0.0f;
+      if (ss > 0.0f) su = clamp_keep_nan(rintf(__fdiv_rn(s, fmaxf(ss, 1e-30f))), 0.0f, 255.0f);
+      if (ls > 0.0f)
+        lu = clamp_keep_nan(rintf(__fdiv_rn(lo_r[b] - lm, fmaxf(ls, 1e-30f))), 0.0f, 255.0f);
+      const uint8_t su8 = (uint8_t)su, lu8 = (uint8_t)lu;
+      const float lod = round_f16(fmaf((float)lu8, ls, lm));
+      const float std_ = round_f16((float)su8 * ss);
+      s_lo[b] = lod;
+      s_st[b] = std_;
+      if (params != nullptr) {
+        params[(row * nb + b) * 2 + 0] = lu8;
+        params[(row * nb + b) * 2 + 1] = su8;
+      }
+      if (lo_d != nullptr) lo_d[row * ldp + b] = lod;
+      if (st_d != nullptr) st_d[row * ldp + b] = std_;
+    }
+    if (sse == nullptr && codes == nullptr && energy == nullptr) continue;
+    __syncthreads();
+    // ---- nearest codes, weighted error, energy ------------------------------------------------
+    const float* wr = w + row * ldw;
+    float acc = 0.0f, en = 0.0f;
+    for (int64_t j = (int64_t)tid * 4; j < k; j += ROW_THREADS * 4) {
+      const float4 wv = *reinterpret_cast<const float4*>(wr + j);
+      const float4 dv = *reinterpret_cast<const float4*>(d + j);
+      const int64_t b = j / B;
+      const float lod = s_lo[b], std_ = s_st[b];
+      const float safe = (std_ == 0.0f) ? 1.0f : std_;
+      const float ws[4] = {wv.x, wv.y, wv.z, wv.w}, ds[4] = {dv.x, dv.y, dv.z, dv.w};
+      uint8_t cs[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        float c = (std_ == 0.0f) ? 0.0f : rintf(__fdiv_rn(ws[t] - lod, safe));
+        c = clamp_keep_nan(c, 0.0f, nmax);
+        const float diff = round_f16(lod + c * std_) - ws[t];
+        acc += ds[t] * (diff * diff);
+        en += ds[t] * (ws[t] * ws[t]);
+        cs[t] = (uint8_t)c;
+      }
+      if (codes != nullptr)
+        *reinterpret_cast<uchar4*>(codes + row * k + j) = make_uchar4(cs[0], cs[1], cs[2], cs[3]);
+    }
+    acc = warp_sum(acc), en = warp_sum(en);
+    __syncthreads();
+    if (lane == 0) red[0][warp] = acc, red[1][warp] = en;
+    __syncthreads();
+    if (tid == 0) {
+      float a = 0.0f, e = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ROW_THREADS / 32; ++i) a += red[0][i], e += red[1][i];
+      if (sse != nullptr) sse[row] = a;
+      if (energy != nullptr) energy[row] = e;
+    }
+  }
+}
+
+// sse of given codes against given decoded ladders (the tail of the GPTQ path).
+template <int B>
+__global__ void __launch_bounds__(ROW_THREADS)
+sse_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ w, int64_t ldw,
+           const float* __restrict__ d, const float* __restrict__ lo, const float* __restrict__ st,
+           int64_t ldp, int64_t n_rows, int64_t k, float* __restrict__ sse) {
+  __shared__ float red[ROW_THREADS / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    float acc = 0.0f;
+    for (int64_t j = (int64_t)tid * 4; j < k; j += ROW_THREADS * 4) {
+      const float4 wv = *reinterpret_cast<const float4*>(w + row * ldw + j);
+      const float4 dv = *reinterpret_cast<const float4*>(d + j);
+      const uchar4 cv = *reinterpret_cast<const uchar4*>(codes + row * k + j);
+      const float lod = lo[row * ldp + j / B], std_ = st[row * ldp + j / B];
+      const float ws[4] = {wv.x, wv.y, wv.z, wv.w}, ds[4] = {dv.x, dv.y, dv.z, dv.w};
+      const float cs[4] = {(float)cv.x, (float)cv.y, (float)cv.z, (float)cv.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float diff = round_f16(lod + cs[t] * std_) - ws[t];
+        acc += ds[t] * (diff * diff);
+      }
+    }
+    acc = warp_sum(acc);
+    __syncthreads();
+    if (lane == 0) red[warp] = acc;
+    __syncthreads();
+    if (tid == 0) {
+      float a = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ROW_THREADS / 32; ++i) a += red[i];
+      sse[row] = a;
+    }
+  }
+}
+
+bool block_ok(int block) { return block == 16 || block == 32 || block == 64; }
+
+}  // namespace
+}  // namespace hi2
+
+extern "C" int hi2_ladder_grid(const float* wb, const float* db, const float* grid_host, int g,
+                               int n, int64_t n_rows, int64_t nb, int block, float* lo,
+                               float* step, float* err, void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(block_ok(block), "ladder_grid: block must be 16, 32 or 64");
+  HI2_REQUIRE(g >= 1 && g <= 8 && grid_host, "ladder_grid: the grid has 1 to 8 points");
+  HI2_REQUIRE(n >= 2, "ladder_grid: n must be at least 2");
+  if (n_rows == 0 || nb == 0) return HI2_OK;
+  HI2_REQUIRE(wb && db && lo && step, "ladder_grid: null pointer");
+  HI2_REQUIRE(aligned16(wb), "ladder_grid: wb must be 16-byte aligned");
+  return launch_fit(wb, nb * block, db, grid_host, g, 0, n, n_rows, nb, block, lo, step, err,
+                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hi2_fit_ladder(const float* w, int64_t ldw, const float* d, const float* grid_host,
+                              int g, int refits, int n, int64_t n_rows, int64_t k, int block,
+                              float* lo, float* step, void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(block_ok(block), "fit_ladder: block must be 16, 32 or 64");
+  HI2_REQUIRE(k > 0 && k % block == 0, "fit_ladder: k must be a multiple of the block");
+  HI2_REQUIRE(g >= 1 && g <= 8 && grid_host, "fit_ladder: the grid has 1 to 8 points");
+  HI2_REQUIRE(n >= 2 && refits >= 0, "fit_ladder: bad n or refits");
+  if (n_rows == 0) return HI2_OK;
+  HI2_REQUIRE(w && d && lo && step, "fit_ladder: null pointer");
+  HI2_REQUIRE(aligned16(w) && ldw % 4 == 0 && ldw >= k, "fit_ladder: w alignment or ldw");
+  return launch_fit(w, ldw, d, grid_host, g, refits, n, n_rows, k / block, block, lo, step,
+                    nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hi2_quantize_rows(const float* lo, const float* step, const float* w, int64_t ldw,
+                                 const float* d, int nbits, int64_t n_rows, int64_t k, int block,
+                                 uint8_t* params, uint16_t* consts, float* lo_d, float* step_d,
+                                 int64_t ldp, uint8_t* codes, float* sse, float* energy,
+                                 void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(block_ok(block), "quantize_rows: block must be 16, 32 or 64");
+  HI2_REQUIRE(k > 0 && k % block == 0, "quantize_rows: k must be a multiple of the block");
+  HI2_REQUIRE(nbits >= 1 && nbits <= 8, "quantize_rows: nbits out of range");
+  if (n_rows == 0) return HI2_OK;
+  HI2_REQUIRE(lo && step, "quantize_rows: null ladders");
+  const bool scan = codes || sse || energy;
+  if (scan) {
+    HI2_REQUIRE(w && d, "quantize_rows: codes, sse and energy need w and d");
+    HI2_REQUIRE(aligned16(w) && aligned16(d) && ldw % 4 == 0 && ldw >= k,
+                "quantize_rows: w, d alignment or ldw");
+    HI2_REQUIRE(codes == nullptr || (reinterpret_cast<uintptr_t>(codes) & 3u) == 0,
+                "quantize_rows: codes must be 4-byte aligned");
+  }
+  HI2_REQUIRE((lo_d == nullptr && step_d == nullptr) || ldp >= k / block, "quantize_rows: ldp");
+  const int64_t nb = k / block;
+  const size_t smem = (size_t)(2 * nb) * sizeof(float);
+  HI2_REQUIRE(smem <= 48 * 1024, "quantize_rows: k too large for the ladder cache");
+  const unsigned grid = (unsigned)(n_rows < 148 * 16 ? n_rows : 148 * 16);
+  const float nmax = (float)((1 << nbits) - 1);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define HI2_ROW(BB)                                                                             \
+  row_kernel<BB><<<grid, ROW_THREADS, smem, s>>>(lo, step, w, ldw, d, nmax, n_rows, k, params,  \
+                                                 consts, lo_d, step_d, ldp, codes, sse, energy)
+  if (block == 16) HI2_ROW(16);
+  if (block == 32) HI2_ROW(32);
+  if (block == 64) HI2_ROW(64);
+#undef HI2_ROW
+  return check_launch("quantize_rows");
+}
+
+extern "C" int hi2_ladder_sse(const uint8_t* codes, const float* w, int64_t ldw, const float* d,
+                              const float* lo, const float* st, int64_t ldp, int64_t n_rows,
+                              int64_t k, int block, float* sse, void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(block_ok(block), "ladder_sse: block must be 16, 32 or 64");
+  HI2_REQUIRE(k > 0 && k % block == 0, "ladder_sse: k must be a multiple of the block");
+  if (n_rows == 0) return HI2_OK;
+  HI2_REQUIRE(codes && w && d && lo && st && sse, "ladder_sse: null pointer");
+  HI2_REQUIRE(aligned16(w) && aligned16(d) && ldw % 4 == 0 &&
+                  (reinterpret_cast<uintptr_t>(codes) & 3u) == 0,
+              "ladder_sse: alignment");
+  const unsigned grid = (unsigned)(n_rows < 148 * 16 ? n_rows : 148 * 16);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define HI2_SSE(BB) \
+  sse_kernel<BB><<<grid, ROW_THREADS, 0, s>>>(codes, w, ldw, d, lo, st, ldp, n_rows, k, sse)
+  if (block == 16) HI2_SSE(16);
+  if (block == 32) HI2_SSE(32);
+  if (block == 64) HI2_SSE(64);
+#undef HI2_SSE
+  return check_launch("ladder_sse");
+}

@@ -1,0 +1,152 @@
+// Hessian basis change (hi2/hessian.py:50-68) and the 16x16 group moments (hi2/stats.py:27-33).
+//
+// transform_sigma is a tile-local operation because the rotation is block diagonal with 16-wide
+// blocks: hs = sym(M (D s D) M^T) only mixes entries inside one 16x16 cell.  A thread block takes
+// the pair of 64x64 tiles (bi, bj) and (bj, bi), applies scale, left and right products to both
+// in shared memory, averages them and writes both, so sigma is read once and hs written once
+// (8 K^2 bytes in all): bound by HBM.
+#include "common.cuh"
+
+namespace hi2 {
+namespace {
+
+constexpr int TS = 64;      // tile side
+constexpr int LD = TS + 1;  // odd stride: rows and columns of a tile are both conflict-free
+
+__device__ __forceinline__ float h16(int i, int j) { return (__popc(i & j) & 1) ? -0.25f : 0.25f; }
+
+// Load tile (tr, tc) of sigma/denom scaled by inv[row]*inv[col], then M . M^T on flagged groups.
+__device__ void transform_tile(float (*tile)[LD], const float* __restrict__ sigma, float denom,
+                               const float* __restrict__ inv_s, const uint8_t* __restrict__ had,
+                               int64_t k, int64_t tr, int64_t tc) {
+  const int tid = threadIdx.x;
+  const int64_t r0 = tr * TS, c0 = tc * TS;
+  for (int idx = tid; idx < TS * TS; idx += 256) {
+    const int i = idx / TS, j = idx % TS;
+    const int64_t gr = r0 + i, gc = c0 + j;
+    float v = 0.0f;
+    if (gr < k && gc < k) {
+      v = sigma[gr * k + gc];
+      if (denom != 1.0f) v = __fdiv_rn(v, denom);
+      if (inv_s != nullptr) v = (v * inv_s[i]) * inv_s[TS + j];
+    }
+    tile[i][j] = v;
+  }
+  __syncthreads();
+  {  // left product: thread = (column c, row group gi)
+    const int c = tid & 63, gi = tid >> 6;
+    const int64_t grp = (r0 >> 4) + gi;
+    if (grp * 16 < k && had[grp]) {
+      float in[16], out[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) in[j] = tile[gi * 16 + j][c];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc = fmaf(h16(i, j), in[j], acc);
+        out[i] = acc;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) tile[gi * 16 + i][c] = out[i];
+    }
+  }
+  __syncthreads();
+  {  // right product: thread = (row i, column group gj)
+    const int i = tid & 63, gj = tid >> 6;
+    const int64_t grp = (c0 >> 4) + gj;
+    if (grp * 16 < k && had[grp]) {
+      float in[16], out[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) in[q] = tile[i][gj * 16 + q];
+#pragma unroll
+      for (int l = 0; l < 16; ++l) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 16; ++q) acc = fmaf(in[q], h16(l, q), acc);
+        out[l] = acc;
+      }
+#pragma unroll
+      for (int l = 0; l < 16; ++l) tile[i][gj * 16 + l] = out[l];
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256)
+transform_sigma_kernel(const float* __restrict__ sigma, float denom,
+                       const uint16_t* __restrict__ col_scale, const uint8_t* __restrict__ had,
+                       int64_t k, float* __restrict__ hs, float* __restrict__ diag) {
+  const int64_t bi = blockIdx.y, bj = blockIdx.x;
+  if (bi > bj) return;
+  __shared__ float P[TS][LD];
+  __shared__ float Q[TS][LD];
+  __shared__ float inv_rc[2 * TS];  // 1/s of the rows of tile (bi, .) then of (bj, .)
+  const int tid = threadIdx.x;
+  const bool scaled = col_scale != nullptr;
+  if (scaled && tid < 2 * TS) {
+    const int64_t idx = (tid < TS ? bi * TS + tid : bj * TS + (tid - TS));
+    float v = 1.0f;
+    if (idx < k) v = __fdiv_rn(1.0f, __half2float(__ushort_as_half(col_scale[idx])));
+    inv_rc[tid] = v;
+  }
+  __syncthreads();
+  // tile (bi, bj): rows scaled by inv[bi-range], columns by inv[bj-range]
+  transform_tile(P, sigma, denom, scaled ? inv_rc : nullptr, had, k, bi, bj);
+  if (bi != bj) {
+    // tile (bj, bi) wants the two halves of inv_rc swapped
+    __shared__ float inv_cr[2 * TS];
+    if (scaled && tid < 2 * TS) inv_cr[tid] = inv_rc[(tid + TS) % (2 * TS)];
+    __syncthreads();
+    transform_tile(Q, sigma, denom, scaled ? inv_cr : nullptr, had, k, bj, bi);
+  }
+  const int64_t r0 = bi * TS, c0 = bj * TS;
+  for (int idx = tid; idx < TS * TS; idx += 256) {
+    const int i = idx / TS, j = idx % TS;
+    // upper tile (bi, bj), element (i, j) = 0.5 * (P[i][j] + Q[j][i])
+    if (r0 + i < k && c0 + j < k) {
+      const float other = (bi == bj) ? P[j][i] : Q[j][i];
+      hs[(r0 + i) * k + c0 + j] = 0.5f * (P[i][j] + other);
+    }
+    // lower tile (bj, bi), element (i, j) = 0.5 * (Q[i][j] + P[j][i]): the same sum, mirrored
+    if (bi != bj && c0 + i < k && r0 + j < k)
+      hs[(c0 + i) * k + r0 + j] = 0.5f * (P[j][i] + Q[i][j]);
+  }
+  if (bi == bj && diag != nullptr && tid < TS && r0 + tid < k)
+    diag[r0 + tid] = 0.5f * (P[tid][tid] + P[tid][tid]);
+}
+
+__global__ void __launch_bounds__(256)
+group_moments_kernel(const float* __restrict__ s, int64_t k, double* __restrict__ g) {
+  const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;  // (group, i, j)
+  if (idx >= k * 16) return;
+  const int64_t grp = idx >> 8;
+  const int i = (int)(idx >> 4) & 15, j = (int)idx & 15;
+  g[idx] += (double)s[(grp * 16 + i) * k + grp * 16 + j];
+}
+
+}  // namespace
+}  // namespace hi2
+
+extern "C" int hi2_transform_sigma(const float* sigma, float denom, const uint16_t* col_scale,
+                                   const uint8_t* had, int64_t k, float* hs, float* diag,
+                                   void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(k > 0 && k % 16 == 0, "transform_sigma: k must be a positive multiple of 16");
+  HI2_REQUIRE(sigma && had && hs, "transform_sigma: null pointer");
+  HI2_REQUIRE(sigma != hs, "transform_sigma: in-place operation is not supported");
+  HI2_REQUIRE(denom > 0.0f, "transform_sigma: denom must be positive");
+  const unsigned nt = (unsigned)ceil_div(k, TS);
+  transform_sigma_kernel<<<dim3(nt, nt), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      sigma, denom, col_scale, had, k, hs, diag);
+  return check_launch("transform_sigma");
+}
+
+extern "C" int hi2_group_moments(const float* s, int64_t k, double* g, void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(k > 0 && k % 16 == 0, "group_moments: k must be a positive multiple of 16");
+  HI2_REQUIRE(s && g, "group_moments: null pointer");
+  group_moments_kernel<<<(unsigned)ceil_div(k * 16, 256), 256, 0,
+                         static_cast<cudaStream_t>(stream)>>>(s, k, g);
+  return check_launch("group_moments");
+}

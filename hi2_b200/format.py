@@ -1,0 +1,184 @@
+"""Rotation, packing and flat-buffer assembly of the ``rdna_hint_flex`` format on B200.
+
+Same names and results as the functions of hi2/format.py that the PTQ encode path uses
+(``fwht_groups`` :30-41, ``pack_codes`` :73-85, ``assemble`` :127-184); the work runs in
+``libhi2_b200.so``.  ``decode_params`` / ``ladder_dequantize`` / ``unpack_codes`` are the
+decoder-side definitions (hi2/format.py:45-69, :88-93) written with elementwise tensor ops; the
+encode kernels carry their own copies of that arithmetic.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+GROUP = 16
+
+
+def hadamard16(dtype: torch.dtype = torch.float64, device="cpu") -> torch.Tensor:
+    """Normalised order-16 Walsh-Hadamard matrix (symmetric, its own inverse)."""
+    h = torch.ones(1, 1, dtype=torch.float64)
+    while h.shape[0] < GROUP:
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+    return (h / math.sqrt(GROUP)).to(dtype=dtype, device=device)
+
+
+def fwht_groups(x: torch.Tensor, flags: torch.Tensor, col_scale: torch.Tensor | None = None,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Transform the flagged 16-column groups of ``x[..., K]`` (an involution).
+
+    Extensions over the reference signature, both optional: ``col_scale`` (``[K]``, multiplied
+    in fp32 before the rotation, as ``W * s`` in hi2/calibrate.py:247-250) and ``out_dtype``
+    (``torch.float32`` lets a bf16/fp16 tensor be cast, scaled and rotated in one pass)."""
+    k = x.shape[-1]
+    if k % GROUP:
+        raise ValueError(f"K={k} must be a multiple of {GROUP}")
+    if flags.numel() != k // GROUP:
+        raise ValueError(f"flags has {flags.numel()} entries, expected {k // GROUP}")
+    dev = _lib.need_cuda(x)
+    if x.dtype not in _lib.DTYPES:
+        raise ValueError(f"unsupported dtype {x.dtype}")
+    out_dtype = out_dtype or x.dtype
+    xc = x.contiguous()
+    y = torch.empty(xc.shape, dtype=out_dtype, device=dev)
+    fl = flags.to(device=dev, dtype=torch.uint8).contiguous()
+    cs = None
+    if col_scale is not None:
+        cs = col_scale.to(device=dev, dtype=torch.float32).contiguous()
+    rows = xc.numel() // k
+    _lib.call(
+        "hi2_rotate_groups", _lib.ptr(xc), _lib.DTYPES[x.dtype], _lib.ptr(y), _lib.DTYPES[out_dtype],
+        _lib.ptr(fl), _lib.ptr(cs), rows, k, _lib.stream(dev),
+    )
+    return y
+
+
+# ---- block parameters ---------------------------------------------------------------------
+def decode_params(lo_u8, step_u8, lo_min, lo_scale, step_scale):
+    """fp16 ``lo = fp16(fma_f32(u, lo_scale, lo_min))`` and ``step = fp16(u * step_scale)``."""
+    lo = (lo_u8.double() * lo_scale.double() + lo_min.double()).float().to(torch.float16)
+    step = (step_u8.float() * step_scale.float()).to(torch.float16)
+    return lo, step
+
+
+def ladder_dequantize(codes, lo, step, dtype=torch.float64):
+    """``fp16(lo + code * step)`` with the sum formed in ``dtype``."""
+    v = lo.to(dtype).unsqueeze(-1) + codes.to(dtype) * step.to(dtype).unsqueeze(-1)
+    return v.to(torch.float16)
+
+
+# ---- code packing ---------------------------------------------------------------------------
+def pack_codes(codes: torch.Tensor, nbits: int) -> torch.Tensor:
+    """``[..., n]`` codes -> ``[..., n * nbits / 32]`` int32, first code in the low bits."""
+    per_word = 32 // nbits
+    n = codes.shape[-1]
+    if n % per_word:
+        raise ValueError(f"{n} codes is not a multiple of {per_word}")
+    dev = _lib.need_cuda(codes)
+    if codes.dtype != torch.uint8:
+        if codes.numel() and (int(codes.max()) >= 2**nbits or int(codes.min()) < 0):
+            raise ValueError("code outside the ladder")
+        codes = codes.to(torch.uint8)
+    c = codes.contiguous()
+    words = torch.empty(*c.shape[:-1], n // per_word, dtype=torch.int32, device=dev)
+    bad = torch.zeros(1, dtype=torch.int32, device=dev)
+    _lib.call(
+        "hi2_pack_codes", _lib.ptr(c), _lib.ptr(words), c.numel() // max(n, 1), n, nbits,
+        _lib.ptr(bad), _lib.stream(dev),
+    )
+    if int(bad.item()):
+        raise ValueError("code outside the ladder")
+    return words
+
+
+def unpack_codes(words: torch.Tensor, nbits: int) -> torch.Tensor:
+    per_word = 32 // nbits
+    w = words.to(torch.int64) & 0xFFFFFFFF
+    mask = (1 << nbits) - 1
+    c = torch.stack([(w >> (nbits * i)) & mask for i in range(per_word)], dim=-1)
+    return c.reshape(*words.shape[:-1], -1)
+
+
+# ---- tensor container ---------------------------------------------------------------------------
+@dataclass
+class HI2Tensor:
+    """Flat per-tensor buffers (hi2/format.py:97-112)."""
+
+    codes: torch.Tensor  # int32 [sum words_per_row]
+    code_off: torch.Tensor  # int32 [R+1]
+    blk_params: torch.Tensor  # uint8 [2 * sum K/B_r]
+    param_off: torch.Tensor  # int32 [R+1], in blocks
+    row_consts: torch.Tensor  # fp16 [R, 3]
+    row_nbits: torch.Tensor  # uint8 [R]
+    row_block: torch.Tensor  # uint8 [R]
+    had: torch.Tensor  # uint8 [K/16]
+    shape: tuple[int, int]
+    col_scale: torch.Tensor | None = None
+
+
+FIELDS = ("codes", "code_off", "blk_params", "param_off", "row_consts", "row_nbits", "row_block", "had")
+
+
+def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=None,
+             to_host: bool = True) -> HI2Tensor:
+    """Flat buffers from per-candidate pieces ``(rows, codes[r, K] u8, params[r, nb, 2] u8,
+    consts[r, 3] fp16)``.
+
+    The packing and the scatters run on the device of the first piece.  As in the reference the
+    result is returned on the host (``to_host=False`` keeps the three big buffers on the device,
+    which is what a caller that overlaps the copy wants); ``stager`` is accepted for signature
+    compatibility and ignored (B200 copies from ordinary pinned or pageable memory)."""
+    del stager
+    r = row_nbits.numel()
+    nb = row_nbits.to("cpu", torch.int64)
+    bl = row_block.to("cpu", torch.int64)
+    code_off = torch.zeros(r + 1, dtype=torch.int64)
+    code_off[1:] = torch.cumsum((k * nb) // 32, 0)
+    param_off = torch.zeros(r + 1, dtype=torch.int64)
+    param_off[1:] = torch.cumsum(k // bl, 0)
+    if not pieces:
+        dev = torch.device("cpu")
+        codes = torch.zeros(int(code_off[-1]), dtype=torch.int32)
+        params = torch.zeros(int(param_off[-1]) * 2, dtype=torch.uint8)
+        consts = torch.zeros(r, 3, dtype=torch.float16)
+    else:
+        dev = _lib.need_cuda(*[p[1] for p in pieces])
+        code_off_d, param_off_d = code_off.to(dev), param_off.to(dev)
+        codes = torch.zeros(int(code_off[-1]), dtype=torch.int32, device=dev)
+        params = torch.zeros(int(param_off[-1]) * 2, dtype=torch.uint8, device=dev)
+        consts = torch.zeros(r, 3, dtype=torch.float16, device=dev)
+        bad = torch.zeros(1, dtype=torch.int32, device=dev)
+        for rows, c, p, rc in pieces:
+            if rows.numel() == 0:
+                continue
+            first = int(rows[0])
+            nbits, block = int(nb[first]), int(bl[first])
+            rows_d = rows.to(dev, torch.int64).contiguous()
+            c = c.to(dev, torch.uint8).contiguous()
+            p = p.to(dev, torch.uint8).contiguous()
+            rc = rc.to(dev, torch.float16).contiguous()
+            _lib.call(
+                "hi2_assemble_piece", _lib.ptr(rows_d), rows_d.numel(), _lib.ptr(c), _lib.ptr(p),
+                _lib.ptr(rc), k, nbits, block, _lib.ptr(code_off_d), _lib.ptr(param_off_d),
+                _lib.ptr(codes), _lib.ptr(params), _lib.ptr(consts), _lib.ptr(bad), _lib.stream(dev),
+            )
+        if int(bad.item()):
+            raise ValueError("code outside the ladder")
+    if to_host:
+        codes, params, consts = codes.cpu(), params.cpu(), consts.cpu()
+    return HI2Tensor(
+        codes=codes,
+        code_off=code_off.to(torch.int32),
+        blk_params=params,
+        param_off=param_off.to(torch.int32),
+        row_consts=consts,
+        row_nbits=row_nbits.to("cpu", torch.uint8),
+        row_block=row_block.to("cpu", torch.uint8),
+        had=had.to("cpu", torch.uint8).reshape(-1),
+        shape=(r, k),
+        col_scale=col_scale,
+    )

@@ -1,0 +1,330 @@
+"""Hessian statistics and error-compensated rounding on B200 (interface of hi2/hessian.py).
+
+``HessianStats`` (:26-47), ``transform_sigma`` (:50-68), ``inverse_factor`` (:71-86), ``GptqJob``
+(:178-188), ``encode_jobs_gptq`` (:359-416) and ``encode_rows_gptq`` (:419-443) keep the
+reference's names, arguments and results.  Underneath:
+
+* the second moment is a TMA-fed tcgen05 product with fp32 accumulation (csrc/hessian.cu);
+* the basis change is one tile kernel (csrc/sigma.cu);
+* the inverse factor is one fp64 blocked factorisation plus triangular inverse (csrc/cholinv.cu)
+  with the reference's damping retries driven from here;
+* GPTQ fits the ladders once (csrc/ladder.cu), then runs the whole column loop, block kernel and
+  trailing update per 128 columns, as one enqueue without host synchronisation (csrc/gptq.cu).
+
+There is no torch loop: ``backend="torch"`` raises.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib, gptq_kernel
+from . import ladder_kernel as _ladder
+from .encode import EFFORT, Encoded
+from .format import GROUP
+
+BLOCK_COLUMNS = 128  # lazy-update block of GPTQ
+ROW_ELEMS = 1 << 26  # rows per unit, as in the reference (results do not depend on it)
+BATCH_ELEMS = int(os.environ.get("HI2_BATCH_ELEMS", 1 << 27))
+
+_workspaces: dict = {}
+
+
+def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """Grow-only scratch buffer of one device (uint8), shared by the kernels that need scratch."""
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = None
+        _workspaces.pop(key, None)
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _workspaces[key] = buf
+    return buf
+
+
+class HessianStats:
+    """Full second moment ``sum x x^T`` of a Linear's input (fp32, ``[K, K]``)."""
+
+    def __init__(self, k: int, device="cuda"):
+        self.k = k
+        self.S = torch.zeros(k, k, dtype=torch.float32, device=device)
+        self.n = 0
+
+    @torch.no_grad()
+    def update(self, x: torch.Tensor, chunk: int = 4096) -> None:
+        """``S += x^T x`` for ``x [..., K]``.  bf16 / fp16 activations feed the tensor cores
+        directly (their products are exact in fp32); anything else is taken as fp32.  ``chunk``
+        is accepted for compatibility: the kernel splits the tokens itself."""
+        del chunk
+        dev = self.S.device
+        x = x.reshape(-1, self.k)
+        if x.device != dev:
+            x = x.to(dev)
+        if x.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            x = x.float()
+        x = x.contiguous()
+        tokens = x.shape[0]
+        if tokens == 0:
+            return
+        lib = _lib.load()
+        dt = _lib.DTYPES[x.dtype]
+        need = lib.hi2_hessian_workspace_bytes(tokens, self.k, dt)
+        ws = _workspace(dev, need) if need else None
+        _lib.call(
+            "hi2_hessian_accumulate", _lib.ptr(x), dt, tokens, self.k, _lib.ptr(self.S),
+            _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.stream(dev),
+        )
+        if ws is not None:
+            status = int(ws[:4].view(torch.int32).item())
+            if status:
+                raise RuntimeError(
+                    f"hessian_accumulate: a bounded device-side wait ran out (status {status})"
+                )
+        self.n += tokens
+
+    def merge(self, other: "HessianStats") -> None:
+        self.S += other.S.to(self.S.device)
+        self.n += other.n
+
+    def mean(self) -> torch.Tensor:
+        return self.S / max(self.n, 1)
+
+
+def transform_sigma(sigma: torch.Tensor, col_scale: torch.Tensor | None, had: torch.Tensor,
+                    denom: float = 1.0, return_diag: bool = False):
+    """``Hs = T (sigma / denom) T^T`` with ``T = R diag(1/s)``, symmetrised.  ``denom`` and
+    ``return_diag`` are additions: the division of a raw sum by its token count and the
+    diagonal of the result come out of the same pass."""
+    dev = _lib.need_cuda(sigma)
+    k = sigma.shape[0]
+    s = sigma if sigma.dtype == torch.float32 else sigma.float()
+    s = s.contiguous()
+    hs = torch.empty(k, k, dtype=torch.float32, device=dev)
+    diag = torch.empty(k, dtype=torch.float32, device=dev) if return_diag else None
+    cs = None
+    if col_scale is not None:
+        cs = col_scale.to(dev, torch.float16).contiguous()
+    flags = had.to(dev, torch.uint8).contiguous()
+    if flags.numel() != k // GROUP:
+        raise ValueError(f"had has {flags.numel()} entries, expected {k // GROUP}")
+    _lib.call(
+        "hi2_transform_sigma", _lib.ptr(s), float(denom), _lib.ptr(cs), _lib.ptr(flags), k,
+        _lib.ptr(hs), _lib.ptr(diag), _lib.stream(dev),
+    )
+    return (hs, diag) if return_diag else hs
+
+
+def inverse_factor(hs: torch.Tensor, damp: float = 0.01) -> torch.Tensor:
+    """Upper Cholesky factor ``U`` of ``(Hs + damp * mean(diag) I)^-1``; the damping is raised
+    tenfold (up to five times) when the factorisation meets a non-positive pivot."""
+    dev = _lib.need_cuda(hs)
+    k = hs.shape[0]
+    h = hs if hs.dtype == torch.float32 else hs.float()
+    h = h.contiguous()
+    mean = h.diagonal().mean().clamp_min(1e-12)
+    lib = _lib.load()
+    need = lib.hi2_inverse_factor_workspace_bytes(k)
+    ws = _workspace(dev, need)
+    u = torch.empty(k, k, dtype=torch.float32, device=dev)
+    info = torch.zeros(1, dtype=torch.int32, device=dev)
+    last = 0
+    for attempt in range(6):
+        lam = (damp * mean * 10**attempt).to(torch.float32).reshape(1)
+        info.zero_()
+        _lib.call(
+            "hi2_inverse_factor", _lib.ptr(h), _lib.ptr(lam), k, _lib.ptr(u), _lib.ptr(ws),
+            ws.numel(), _lib.ptr(info), _lib.stream(dev),
+        )
+        last = int(info.item())
+        if last == 0 and bool(torch.isfinite(u.diagonal()).all()):
+            return u
+    raise RuntimeError(
+        f"Hessian is not factorisable even with heavy damping: non-positive pivot {last - 1}"
+    )
+
+
+@dataclass
+class GptqJob:
+    """One call of :func:`encode_rows_gptq`: rows ``w [N, K]`` (stored basis), ladder weights
+    ``d [K]``, factor ``u [K, K]`` (of the permuted Hessian when ``perm`` is set)."""
+
+    w: torch.Tensor
+    d: torch.Tensor
+    u: torch.Tensor
+    nbits: int
+    block: int
+    perm: torch.Tensor | None = None
+
+
+@dataclass
+class _Unit:
+    job: int
+    s: int
+    rows: int
+    wc: torch.Tensor | None  # [n, K] fp32 working copy, columns in rounding order
+    src: torch.Tensor  # [n, K] fp32 original rows
+    params: torch.Tensor
+    consts: torch.Tensor
+    lo_d: torch.Tensor  # [n, K/16] fp32 decoded, zero padded
+    step_d: torch.Tensor
+    blk_of: torch.Tensor  # [K] int32 block of each column in rounding order
+    codes: torch.Tensor | None = None
+    comp: torch.Tensor | None = None
+
+
+def _prepare(ji: int, job: GptqJob, s: int, step_rows: int, effort: str) -> _Unit:
+    dev = job.w.device
+    k = job.w.shape[1]
+    cfg = EFFORT[effort]
+    src = job.w[s : s + step_rows]
+    if src.dtype != torch.float32 or not src.is_contiguous():
+        src = src.float().contiguous()
+    d = job.d.to(dev, torch.float32).contiguous()
+    lo, st = _ladder.fit(src, d, cfg["grid"], cfg["ls"], 2**job.nbits, job.block)
+    q = _ladder.quantize_rows(lo, st, job.nbits, job.block, k, want_decoded=True, ldp=k // GROUP)
+    cols = torch.arange(k, device=dev)
+    if job.perm is not None:
+        cols = job.perm.to(dev)
+        wc = src[:, cols].contiguous()
+    else:
+        wc = src.clone()
+    return _Unit(ji, s, src.shape[0], wc, src, q["params"], q["consts"], q["lo_d"], q["step_d"],
+                 (cols // job.block).to(torch.int32))
+
+
+def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool) -> None:
+    """All ``units`` (same K, same device) through one enqueue of the column loop."""
+    dev, k = units[0].wc.device, units[0].wc.shape[1]
+    sizes = [x.rows for x in units]
+    total = sum(sizes)
+    if len(units) == 1:
+        wc, lo, st = units[0].wc, units[0].lo_d, units[0].step_d
+    else:
+        wc = torch.cat([x.wc for x in units])
+        lo = torch.cat([x.lo_d for x in units])
+        st = torch.cat([x.step_d for x in units])
+    offs = [0]
+    for n in sizes:
+        offs.append(offs[-1] + n)
+    row_grp = torch.repeat_interleave(
+        torch.arange(len(units), dtype=torch.int32), torch.tensor(sizes)
+    ).to(dev)
+    us = [jobs[x.job].u.to(dev, torch.float32).contiguous() for x in units]
+    u_ptrs = torch.tensor([u.data_ptr() for u in us], dtype=torch.int64).to(dev)
+    blk = torch.stack([x.blk_of for x in units]).contiguous()
+    nmax = torch.tensor([2 ** jobs[x.job].nbits - 1 for x in units], dtype=torch.float32).to(dev)
+    codes = torch.empty(total, k, dtype=torch.uint8, device=dev)
+    comp = torch.empty(total, k, dtype=torch.float32, device=dev) if want_comp else None
+    err1 = torch.empty(total, BLOCK_COLUMNS, dtype=torch.float32, device=dev)
+    gptq_kernel.gptq_round(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp, offs, us)
+    for x, o, n in zip(units, offs, sizes):
+        x.codes = codes[o : o + n]
+        x.comp = None if comp is None else comp[o : o + n]
+
+
+def _finish(unit: _Unit, job: GptqJob) -> Encoded:
+    dev = unit.src.device
+    k = unit.src.shape[1]
+    codes, comp = unit.codes, unit.comp
+    if job.perm is not None:
+        p = job.perm.to(dev)
+        out = torch.empty_like(codes)
+        out[:, p] = codes
+        codes = out
+        if comp is not None:
+            c = torch.empty_like(comp)
+            c[:, p] = comp
+            comp = c
+    codes = codes.contiguous()
+    sse = torch.empty(unit.rows, dtype=torch.float32, device=dev)
+    d = job.d.to(dev, torch.float32).contiguous()
+    _lib.call(
+        "hi2_ladder_sse", _lib.ptr(codes), _lib.ptr(unit.src), unit.src.stride(0), _lib.ptr(d),
+        _lib.ptr(unit.lo_d), _lib.ptr(unit.step_d), unit.lo_d.shape[1], unit.rows, k, job.block,
+        _lib.ptr(sse), _lib.stream(dev),
+    )
+    return Encoded(codes, unit.params, unit.consts, sse, comp)
+
+
+def _use_kernel(dev: torch.device, backend: str) -> bool:
+    if backend == "torch":
+        raise RuntimeError("hi2_b200 has no torch loop: backend must be 'auto' or 'kernel'")
+    if not gptq_kernel.available(dev):
+        raise RuntimeError(f"gptq kernel unavailable on {dev}: {gptq_kernel.failure()}")
+    return True
+
+
+@torch.no_grad()
+def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str | None = None,
+                     comp: bool = False) -> list[Encoded]:
+    """:func:`encode_rows_gptq` for several jobs (tensors, experts, candidate groups) at once.
+
+    Jobs are cut into row units; units with the same K on the same device are batched (up to
+    ``BATCH_ELEMS`` weights) through one column loop.  With ``comp`` every result carries
+    ``Encoded.comp``, the value each code was rounded from."""
+    backend = backend or os.environ.get("HI2_GPTQ_BACKEND", "auto")
+    units: list[_Unit] = []
+    for ji, job in enumerate(jobs):
+        _lib.need_cuda(job.w, job.u)
+        _use_kernel(job.w.device, backend)
+        n_rows, k = job.w.shape
+        step_rows = max(1, ROW_ELEMS // k)
+        for s in range(0, n_rows, step_rows):
+            units.append(_prepare(ji, job, s, step_rows, effort))
+    batches: dict[tuple, list[list[_Unit]]] = {}
+    for x in units:
+        key = (x.wc.device, x.wc.shape[1])
+        bl = batches.setdefault(key, [[]])
+        if bl[-1] and sum(y.wc.numel() for y in bl[-1]) + x.wc.numel() > BATCH_ELEMS:
+            bl.append([])
+        bl[-1].append(x)
+    for bl in batches.values():
+        for batch in bl:
+            _round_units(batch, jobs, comp)
+            for x in batch:
+                x.wc = None
+    per_job: list[list[Encoded]] = [[] for _ in jobs]
+    for x in units:
+        per_job[x.job].append(_finish(x, jobs[x.job]))
+    out = []
+    for encs in per_job:
+        if len(encs) == 1:
+            out.append(encs[0])
+            continue
+        out.append(
+            Encoded(
+                *(torch.cat([getattr(o, f) for o in encs]) for f in ("codes", "params", "consts", "sse")),
+                torch.cat([o.comp for o in encs]) if comp else None,
+            )
+        )
+    return out
+
+
+def encode_rows_gptq(w, d, u, nbits: int, block: int, effort: str = "normal", perm=None,
+                     backend: str | None = None, comp: bool = True) -> Encoded:
+    """Quantise ``w [N, K]`` (stored basis) with error compensation; ladders are fitted on the
+    uncompensated weights with weights ``d`` and then fixed.  With ``perm`` the columns are
+    rounded in that order while codes keep their original positions."""
+    return encode_jobs_gptq([GptqJob(w, d, u, nbits, block, perm)], effort, backend, comp)[0]
+
+
+def encode_rows_gptq_reference(w, d, u, nbits: int, block: int, effort: str = "normal",
+                               perm=None) -> Encoded:
+    """The reference keeps its original column loop under this name; here it is the same
+    kernel path (there is one implementation), with ``comp`` always returned."""
+    return encode_rows_gptq(w, d, u, nbits, block, effort, perm, comp=True)
+
+
+__all__ = [
+    "EFFORT",
+    "GptqJob",
+    "HessianStats",
+    "encode_jobs_gptq",
+    "encode_rows_gptq",
+    "encode_rows_gptq_reference",
+    "inverse_factor",
+    "transform_sigma",
+]

@@ -1,0 +1,60 @@
+"""One block of columns of the refinement sweep on B200 (interface of hi2/refine_kernel.py)."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .gptq_kernel import kernel_dir, supported  # noqa: F401
+
+BLOCK_COLUMNS = 128
+
+
+def load():
+    return _lib.load()
+
+
+def available(dev: torch.device) -> bool:
+    return supported(dev) and load() is not None
+
+
+def failure() -> str | None:
+    return _lib.failure()
+
+
+def refine_block(gb, c, lo_x, st_x, top, hs, b0, length, dw_block) -> None:
+    """Columns ``[b0, b0 + length)``: ``c [N, K]`` (fp32 codes) is updated in place and
+    ``dw_block [N, length]`` receives the change of each decoded value (hi2/refine_kernel.py:173)."""
+    dev = _lib.need_cuda(gb, c, lo_x, st_x, top, hs, dw_block)
+    for t, name in ((gb, "gb"), (c, "c"), (lo_x, "lo"), (st_x, "st"), (top, "top"), (hs, "hs"),
+                    (dw_block, "dw_block")):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError(f"refine_block: {name} must be a contiguous float32 tensor")
+    n, k = c.shape
+    if not (0 < length <= BLOCK_COLUMNS) or gb.shape[1] != length or dw_block.shape[1] != length:
+        raise ValueError("refine_block: bad block length")
+    if b0 < 0 or b0 + length > k or hs.shape != (k, k):
+        raise ValueError("refine_block: block outside the row or hs of the wrong shape")
+    if n == 0:
+        return
+    _lib.call(
+        "hi2_refine_block", _lib.ptr(gb), int(length), _lib.ptr(c), _lib.ptr(lo_x), _lib.ptr(st_x),
+        _lib.ptr(top), _lib.ptr(hs), n, k, int(b0), _lib.ptr(dw_block), _lib.stream(dev),
+    )
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.0) -> None:
+    """``out = alpha * a @ b + beta * out`` in fp32 FMA arithmetic; row-major views with unit
+    column stride (row strides are passed as leading dimensions)."""
+    dev = _lib.need_cuda(a, b, out)
+    for t in (a, b, out):
+        if t.dtype != torch.float32 or t.stride(1) != 1:
+            raise ValueError("gemm: operands must be fp32 with unit column stride")
+    m, kk = a.shape
+    n = b.shape[1]
+    if b.shape[0] != kk or out.shape != (m, n):
+        raise ValueError("gemm: shape mismatch")
+    _lib.call(
+        "hi2_gemm_f32", 0, 0, m, n, kk, float(alpha), _lib.ptr(a), a.stride(0), _lib.ptr(b),
+        b.stride(0), float(beta), _lib.ptr(out), out.stride(0), _lib.stream(dev),
+    )
