@@ -1,0 +1,143 @@
+"""Global allocation of ``(nbits, block)`` per row on B200 (hi2/allocate.py:212-261).
+
+The cost tables never leave the device: each multiplier of the bisection is one kernel launch
+(first-minimum argmin of ``cost + lam * bits`` in fp64 plus the exact sum of the picked bits) and
+eight bytes back to the host, which keeps the reference's bisection (geometric midpoints in
+Python floats, 80 iterations) and therefore its picks bit for bit.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+ROW_OVERHEAD_BITS = 48 + 2 + 1  # row constants + block-size flag + width flag
+
+
+def candidate_row_bits(nbits: int, block: int, k: int) -> float:
+    return nbits * k + 16 * k / block
+
+
+def row_overhead_bits(t) -> int:
+    widths = len({nb for nb, _ in t.candidates})
+    return ROW_OVERHEAD_BITS - 1 + max(1, math.ceil(math.log2(max(widths, 1))))
+
+
+def _overhead(tables) -> int:
+    return sum(
+        row_overhead_bits(t) * t.shape[0]
+        + t.shape[1] // 16
+        + (16 * t.shape[1] if t.col_scale is not None else 0)
+        for t in tables
+    )
+
+
+@dataclass
+class Allocation:
+    picks: dict  # name -> candidate index per row (int64, on the device of the tables)
+    bpw: float
+    lam: float
+    feasible: bool
+    error_ratio: float = float("nan")
+    frac_by_bits: dict | None = None
+
+
+class _Flat:
+    """Costs and bits of all tables side by side, ``[C, sum R]`` fp64 on the device."""
+
+    def __init__(self, tables, sens, dev):
+        self.dev = dev
+        cmax = max(len(t.candidates) for t in tables)
+        costs, bits, self.spans, self.per_table = [], [], [], []
+        off = 0
+        for t in tables:
+            r, k = t.shape
+            scale = sens.get(t.name, 1.0) / max(t.energy, 1e-30)
+            # fp32 product with the scalar rounded to fp32 first, then widened: what
+            # `scalar * float32_tensor` followed by `.double()` gives
+            cost = (t.sse.to(dev, torch.float32) * scale).double()
+            b = torch.tensor(
+                [candidate_row_bits(nb, bl, k) for nb, bl in t.candidates],
+                dtype=torch.float64, device=dev,
+            )
+            self.per_table.append((t, cost, b))
+            pad = cmax - cost.shape[0]
+            costs.append(torch.cat([cost, torch.full((pad, r), float("inf"), dtype=torch.float64,
+                                                      device=dev)]))
+            bits.append(torch.cat([b, torch.zeros(pad, dtype=torch.float64, device=dev)])
+                        .unsqueeze(1).expand(cmax, r))
+            self.spans.append((t.name, off, off + r))
+            off += r
+        self.cost = torch.cat(costs, 1).contiguous()
+        self.bits = torch.cat(bits, 1).contiguous()
+        self.rows = off
+        self.picks = torch.empty(off, dtype=torch.int64, device=dev)
+        self.total = torch.zeros(1, dtype=torch.float64, device=dev)
+
+    def solve(self, lam: float):
+        """``(picks [sum R] on the device, total picked bits)`` for one multiplier."""
+        self.total.zero_()
+        picks = torch.empty_like(self.picks)
+        _lib.call(
+            "hi2_allocate_solve", _lib.ptr(self.cost), _lib.ptr(self.bits), self.cost.shape[0],
+            self.rows, float(lam), _lib.ptr(picks), _lib.ptr(self.total), _lib.stream(self.dev),
+        )
+        return picks, float(self.total.item())
+
+    def split(self, picks):
+        return {name: picks[a:b].clone() for name, a, b in self.spans}
+
+
+def _summary(flat: _Flat, picks):
+    err = floor = 0.0
+    counts: dict[int, int] = {}
+    rows = 0
+    for (t, cost, _), (_, a, b) in zip(flat.per_table, flat.spans):
+        p = picks[a:b]
+        err += cost.gather(0, p[None])[0].sum().item()
+        floor += cost.min(0).values.sum().item()
+        for ci, (nb, _b) in enumerate(t.candidates):
+            counts[nb] = counts.get(nb, 0) + int((p == ci).sum())
+        rows += p.numel()
+    return err / max(floor, 1e-30), {nb: n / max(rows, 1) for nb, n in counts.items()}
+
+
+def allocate_global(tables, target_bpw: float, sensitivity: dict | None = None,
+                    iters: int = 80) -> Allocation:
+    """Minimise ``sum_t s_t * sse_t / energy_t`` under a model-wide bits-per-weight target."""
+    sens = sensitivity or {}
+    dev = _lib.need_cuda(*[t.sse for t in tables])
+    total_w = sum(t.shape[0] * t.shape[1] for t in tables)
+    overhead = _overhead(tables)
+    budget = target_bpw * total_w - overhead
+    flat = _Flat(tables, sens, dev)
+
+    lam_hi = 1.0
+    for _t, cost, bits in flat.per_table:
+        span_b = (bits.max() - bits.min()).clamp_min(1e-9)
+        lam_hi = max(lam_hi, 2 * ((cost.max(0).values - cost.min(0).values) / span_b).max().item())
+    lo, hi = lam_hi * 1e-12, lam_hi
+
+    def done(p, b, lam, ok):
+        ratio, frac = _summary(flat, p)
+        return Allocation(flat.split(p), (b + overhead) / total_w, lam, ok, ratio, frac)
+
+    picks, bits_total = flat.solve(hi)
+    if bits_total > budget:  # even the cheapest assignment is over target
+        return done(picks, bits_total, hi, False)
+    best = flat.solve(lo)
+    if best[1] <= budget:  # even the most accurate one fits
+        return done(best[0], best[1], lo, True)
+    best_lam = hi
+    for _ in range(iters):
+        mid = (lo * hi) ** 0.5
+        p, b = flat.solve(mid)
+        if b <= budget:
+            hi, picks, bits_total, best_lam = mid, p, b, mid
+        else:
+            lo = mid
+    return done(picks, bits_total, best_lam, True)

@@ -1,0 +1,231 @@
+"""Per-tensor tabulate and encode stages on one B200 (callers of the kernels; the shapes of
+hi2/calibrate.py:37-81, :96-111, :212-270, :274-424 with the device kept as the home of the data).
+
+Differences from the reference's orchestration, none of which changes a result:
+
+* one process drives one GPU, so there is no row sharding over an executor: the ``ex`` argument
+  is accepted and ignored (matrices, not rows, are what ``hi2_b200.dist`` spreads over GPUs);
+* weights are cast, scaled and rotated in one kernel pass, straight from bf16 / fp16;
+* a table costs two launches per candidate and returns ``sse`` on the device;
+* the Hessian of a shared input is transformed and factorised once per ``sigma_id``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _lib
+from .encode import encode_rows
+from .format import GROUP, HI2Tensor, assemble, fwht_groups
+from .stats import ColumnStats
+
+ALL_CANDIDATES = [(nb, b) for nb in (2, 4) for b in (16, 32, 64)]
+INT8_CANDIDATES = [(8, 32), (8, 64)]
+SELECTABLE = ALL_CANDIDATES + INT8_CANDIDATES
+
+
+@dataclass
+class Config:
+    candidates: list = field(default_factory=lambda: list(ALL_CANDIDATES))
+    rotation: str = "on"  # on | off ("auto" is a search above this path and is not built here)
+    smooth: float = 0.5
+    smooth_search: tuple = ()
+    rounding: str = "gptq"  # gptq | nearest
+    sequential: bool = False
+    damp: float = 0.01
+    act_order: bool = False
+    refine_passes: int = 0
+    effort: str = "normal"
+    expert_min_tokens: float = 2.0
+
+
+@dataclass
+class TensorTable:
+    name: str
+    shape: tuple
+    had: torch.Tensor  # uint8 [K/16]
+    sse: torch.Tensor  # float32 [C, R] (on the device)
+    candidates: list
+    energy: float
+    n_tokens: int
+    col_scale: torch.Tensor | None = None  # fp16 [K]
+
+
+def candidate_row_bits(nbits: int, block: int, k: int) -> float:
+    return nbits * k + 16 * k / block
+
+
+def _weights(stats: ColumnStats | None, k: int, flags, device, inv_scale=None) -> torch.Tensor:
+    if stats is None:
+        return torch.ones(k, device=device)
+    return stats.diag(flags, inv_scale).to(device)
+
+
+def smoothing_scale(stats: ColumnStats | None, alpha: float) -> torch.Tensor | None:
+    """fp16 smoothing vector ``s_j = clamp((d_j / geomean d)^(alpha/2), 0.05, 20)`` or None."""
+    if alpha <= 0 or stats is None or stats.n == 0:
+        return None
+    d = stats.diag().clamp_min(1e-12)
+    s = (d / d.log().mean().exp()).pow(alpha / 2).clamp(0.05, 20.0)
+    return s.to(torch.float16)
+
+
+def _flags(k: int, cfg: Config) -> torch.Tensor:
+    if cfg.rotation == "on":
+        return torch.ones(k // GROUP, dtype=torch.uint8)
+    if cfg.rotation == "off":
+        return torch.zeros(k // GROUP, dtype=torch.uint8)
+    raise NotImplementedError("rotation='auto' is chosen above this path; pass a transform")
+
+
+def stored_rows(w: torch.Tensor, s16: torch.Tensor | None, had: torch.Tensor) -> torch.Tensor:
+    """``H(W * s)`` as fp32 ``[R, K]``: cast, smoothing multiply and rotation in one pass."""
+    if w.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        w = w.float()
+    scale = None if s16 is None else s16.to(w.device, torch.float32)
+    return fwht_groups(w, had, col_scale=scale, out_dtype=torch.float32)
+
+
+def build_table(name: str, w: torch.Tensor, stats: ColumnStats | None, cfg: Config, ex=None,
+                transform=None, n_tokens: int | None = None) -> TensorTable:
+    """Activation-weighted squared error of every row at every candidate ``(nbits, block)``."""
+    del ex
+    dev = _lib.need_cuda(w)
+    r, k = w.shape
+    if transform is None:
+        s16, had = smoothing_scale(stats, cfg.smooth), _flags(k, cfg)
+    else:
+        s16, had = transform
+        s16 = None if s16 is None else s16.clone()
+        had = had.clone()
+    wt = stored_rows(w, s16, had)
+    inv = None if s16 is None else 1.0 / s16.to(dev, torch.float32)
+    d = _weights(stats, k, had, dev, inv)
+    sse, energy = [], None
+    for i, (nb, b) in enumerate(cfg.candidates):
+        enc = encode_rows(wt, d, nb, b, cfg.effort, want_codes=False, want_energy=(i == 0))
+        sse.append(enc.sse)
+        if i == 0:
+            energy = enc.energy
+    return TensorTable(
+        name, (r, k), had.cpu(), torch.stack(sse), list(cfg.candidates), float(energy.sum()),
+        n_tokens if n_tokens is not None else (stats.n if stats else 0),
+        None if s16 is None else s16.cpu(),
+    )
+
+
+@dataclass
+class EncodeRequest:
+    """One tensor for :func:`encode_many`; requests with the same ``sigma_id``, smoothing vector
+    and flags share one transformed Hessian and one factor."""
+
+    w: torch.Tensor  # [R, K] original basis (any float dtype, on the device)
+    stats: ColumnStats | None
+    table: TensorTable
+    picks: torch.Tensor  # [R] candidate index per row
+    sigma: torch.Tensor | None = None  # [K, K] mean second moment, or a raw sum with sigma_n
+    sigma_id: str | None = None
+    comp_out: dict | None = None
+    sigma_n: int = 1  # divide sigma by this (lets the raw sum be passed without a copy)
+
+
+def _factor_key(req: EncodeRequest, i: int):
+    t = req.table
+    cs = None if t.col_scale is None else t.col_scale.cpu().numpy().tobytes()
+    sid = req.sigma_id if req.sigma_id is not None else f"#{i}"
+    return sid, cs, t.had.cpu().numpy().tobytes()
+
+
+def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool = True) -> list[HI2Tensor]:
+    """Encode several tensors with their allocator picks (hi2/calibrate.py:297-424): all GPTQ
+    candidate groups of all tensors go through one batched column loop; the Hessian transform
+    and factorisation happen once per distinct input."""
+    del ex
+    from .hessian import GptqJob, encode_jobs_gptq, inverse_factor, transform_sigma
+
+    factors: dict = {}
+    pieces: dict[int, list] = {}
+    jobs, where, refine_with = [], [], []
+    stored: dict[int, torch.Tensor] = {}
+    for ri, r in enumerate(reqs):
+        dev = _lib.need_cuda(r.w)
+        t = r.table
+        had, k = t.had, t.shape[1]
+        wt = stored_rows(r.w, t.col_scale, had)
+        stored[ri] = wt
+        use_gptq = cfg.rounding == "gptq" and r.sigma is not None
+        if use_gptq:
+            fk = _factor_key(r, ri)
+            if fk not in factors:
+                hs, d = transform_sigma(r.sigma.to(dev), t.col_scale, had, denom=float(max(r.sigma_n, 1)),
+                                        return_diag=True)
+                perm = None
+                if cfg.act_order:
+                    perm = torch.argsort(d, descending=True)
+                    hs = hs[perm][:, perm].contiguous()
+                u = inverse_factor(hs, cfg.damp)
+                keep = hs if cfg.refine_passes and perm is None else None
+                factors[fk] = (d, u, perm, keep)
+            d, u, perm, hs_keep = factors[fk]
+        else:
+            inv = None if t.col_scale is None else 1.0 / t.col_scale.to(dev, torch.float32)
+            d = _weights(r.stats, k, had, dev, inv)
+        out = pieces.setdefault(ri, [])
+        picks = r.picks.to(dev)
+        for ci, (nb, b) in enumerate(t.candidates):
+            rows = (picks == ci).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            if use_gptq:
+                jobs.append(GptqJob(wt[rows], d, u, nb, b, perm))
+                where.append((ri, rows))
+                refine_with.append(hs_keep if r.comp_out is None else None)
+                out.append(None)
+            else:
+                enc = encode_rows(wt[rows], d, nb, b, cfg.effort)
+                out.append((rows, enc.codes, enc.params, enc.consts))
+    want = any(reqs[ri].comp_out is not None for ri, _ in where)
+    encs = encode_jobs_gptq(jobs, cfg.effort, comp=want) if jobs else []
+    if any(h is not None for h in refine_with):
+        from .refine import refine_groups
+
+        by_tensor: dict[int, list[int]] = {}
+        for x, (ri, _) in enumerate(where):
+            if refine_with[x] is not None:
+                by_tensor.setdefault(ri, []).append(x)
+        for xs in by_tensor.values():
+            new = refine_groups(
+                [(jobs[x].w, encs[x], jobs[x].nbits, jobs[x].block) for x in xs],
+                refine_with[xs[0]], cfg.refine_passes,
+            )
+            for x, codes in zip(xs, new):
+                encs[x] = type(encs[x])(codes, encs[x].params, encs[x].consts, encs[x].sse, encs[x].comp)
+    slot = {ri: iter([j for j, p in enumerate(pieces[ri]) if p is None]) for ri in pieces}
+    comps: dict[int, list] = {}
+    for (ri, rows), enc in zip(where, encs):
+        pieces[ri][next(slot[ri])] = (rows, enc.codes, enc.params, enc.consts)
+        if reqs[ri].comp_out is not None:
+            comps.setdefault(ri, []).append((rows, enc.comp))
+    out = []
+    for ri, r in enumerate(reqs):
+        t = r.table
+        if r.comp_out is not None:
+            full = stored[ri].clone()  # nearest rounding: the stored-basis weights themselves
+            for rows, c in comps.get(ri, []):
+                full[rows] = c
+            r.comp_out["comp"] = full
+        cand = torch.tensor(t.candidates)
+        picks = r.picks.cpu()
+        out.append(
+            assemble(pieces[ri], cand[picks, 0], cand[picks, 1], t.had, t.shape[1], t.col_scale,
+                     to_host=to_host)
+        )
+    return out
+
+
+def encode_with_picks(w, stats, table, picks, cfg: Config, ex=None, sigma=None, comp_out=None) -> HI2Tensor:
+    """Encode rows with the candidate index ``picks[r]`` chosen by the allocator."""
+    req = EncodeRequest(w, stats, table, picks, sigma, comp_out=comp_out)
+    return encode_many([req], cfg, ex)[0]

@@ -1,0 +1,103 @@
+"""Multi-GPU plan of the encode path: one process per GPU, ``torch.distributed`` underneath.
+
+The path shards in two ways and needs exactly two exchanges:
+
+* tokens - every rank accumulates the second moment of ITS calibration tokens for every shared
+  input; the partial sums (fp32 ``[K, K]``) are then reduced to the rank that owns the input
+  (NCCL over NVLink; the reference adds per-device partials on its primary device,
+  hi2/layerwise.py:221-229, hi2/hessian.py:42-44);
+* matrices - tables, factorisation, GPTQ and packing of a matrix run entirely on its owner
+  (hi2 shards rows and re-factorises on every device, hi2/calibrate.py:333-347, 399-405).
+  The global allocation needs every table, so the ``sse`` tables (a few bytes per row) are
+  all-gathered and each rank runs the same deterministic allocation.
+
+Every function takes plain tensors so the logic is testable with ``gloo`` on CPU.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def init_from_env(device_type: str | None = None, timeout_s: float = 600.0):
+    """Join the process group described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT.
+    Returns ``(rank, world, device)``; a single process without those variables is rank 0 of 1."""
+    import datetime
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if device_type is None:
+        device_type = "cuda" if torch.cuda.is_available() else "cpu"
+    device = torch.device(device_type, local) if device_type == "cuda" else torch.device("cpu")
+    if device.type == "cuda":
+        torch.cuda.set_device(device)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        kw = {"device_id": device} if device.type == "cuda" else {}
+        dist.init_process_group(
+            "nccl" if device.type == "cuda" else "gloo", rank=rank, world_size=world,
+            timeout=datetime.timedelta(seconds=timeout_s), **kw,
+        )
+    return rank, world, device
+
+
+def world_size() -> int:
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
+def rank() -> int:
+    return dist.get_rank() if dist.is_initialized() else 0
+
+
+def owner_of(index: int, world: int | None = None) -> int:
+    """Round-robin owner of unit ``index`` (a layer, a shared input, an expert group)."""
+    return index % (world or world_size())
+
+
+def token_shard(tokens: int, r: int | None = None, world: int | None = None) -> tuple[int, int]:
+    """Contiguous token range of rank ``r``: even split, remainder to the first ranks."""
+    world = world or world_size()
+    r = rank() if r is None else r
+    base, extra = divmod(tokens, world)
+    lo = r * base + min(r, extra)
+    return lo, lo + base + (1 if r < extra else 0)
+
+
+def reduce_second_moment(s: torch.Tensor, n: int, owner: int, async_op: bool = False):
+    """Sum partial second moments ``s`` (in place, fp32) onto ``owner`` and the token counts onto
+    every rank.  Returns ``(n_total, work)``; ``work`` is None unless ``async_op``."""
+    if world_size() == 1:
+        return n, None
+    count = torch.tensor([n], dtype=torch.int64, device=s.device)
+    dist.all_reduce(count)
+    work = dist.reduce(s, dst=owner, op=dist.ReduceOp.SUM, async_op=async_op)
+    return int(count.item()), work
+
+
+def all_reduce_second_moment(s: torch.Tensor, n: int):
+    """The all-reduce form (every rank ends with the full sum)."""
+    if world_size() == 1:
+        return n
+    count = torch.tensor([n], dtype=torch.int64, device=s.device)
+    dist.all_reduce(count)
+    dist.all_reduce(s)
+    return int(count.item())
+
+
+def gather_tables(local: list) -> list:
+    """Every rank's table summaries, in rank order then local order.  A summary is any picklable
+    object holding CPU tensors (name, shape, candidates, energy, ``sse``)."""
+    if world_size() == 1:
+        return list(local)
+    box: list = [None] * world_size()
+    dist.all_gather_object(box, local)
+    return [t for part in box for t in part]
+
+
+def barrier() -> None:
+    if world_size() > 1:
+        dist.barrier()

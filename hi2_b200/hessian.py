@@ -59,7 +59,7 @@ class HessianStats:
         directly (their products are exact in fp32); anything else is taken as fp32.  ``chunk``
         is accepted for compatibility: the kernel splits the tokens itself."""
         del chunk
-        dev = self.S.device
+        dev = _lib.need_cuda(self.S)
         x = x.reshape(-1, self.k)
         if x.device != dev:
             x = x.to(dev)

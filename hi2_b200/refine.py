@@ -1,0 +1,108 @@
+"""Local code refinement after GPTQ on B200 (interface of hi2/refine.py:24-162).
+
+A sweep visits the columns in blocks of 128: one launch of the block kernel decides every column
+of the block for every row (csrc/refine.cu), one fp32 FMA product brings ``g = e Hs`` up to date
+for the other columns.  Ladders are never touched.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib, refine_kernel
+from .format import decode_params
+
+BLOCK_COLUMNS = 128
+
+
+@torch.no_grad()
+def objective(w, codes, lo, step, hs, block) -> float:
+    """Sum over rows of ``e Hs e^T`` for the decoded codes."""
+    idx = torch.arange(w.shape[1], device=w.device) // block
+    e = ((lo[:, idx] + codes.float() * step[:, idx]).half().float() - w).contiguous()
+    g = torch.empty_like(e)
+    refine_kernel.gemm(e, hs.float().contiguous(), g)
+    return float((g * e).sum())
+
+
+def _expand(lo: torch.Tensor, step: torch.Tensor, block: int):
+    """Per-column ladders ``[N, K]`` from the per-block ones ``[N, K / block]``."""
+    return lo.repeat_interleave(block, dim=1), step.repeat_interleave(block, dim=1)
+
+
+@torch.no_grad()
+def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
+    """Refined codes (float) of rows ``w [N, K]`` with per-column ladders ``lo_x``/``st_x`` and
+    the highest code of each row ``top [N]``; stops early when a sweep moves no code."""
+    dev = _lib.need_cuda(w, codes, lo_x, st_x, top, hs)
+    if not refine_kernel.available(dev):
+        raise RuntimeError(f"refine kernel unavailable on {dev}: {refine_kernel.failure()}")
+    n_rows, k = w.shape
+    c = codes.float().contiguous().clone()
+    lo_x, st_x = lo_x.float().contiguous(), st_x.float().contiguous()
+    top = top.float().contiguous()
+    hs = hs.float().contiguous()
+    e = ((lo_x + c * st_x).half().float() - w.float()).contiguous()
+    g = torch.empty(n_rows, k, dtype=torch.float32, device=dev)
+    refine_kernel.gemm(e, hs, g)
+    del e
+    for _ in range(passes):
+        start = c.clone()
+        for b0 in range(0, k, BLOCK_COLUMNS):
+            b1 = min(b0 + BLOCK_COLUMNS, k)
+            gb = g[:, b0:b1].contiguous()
+            dw_block = torch.empty(n_rows, b1 - b0, dtype=torch.float32, device=dev)
+            refine_kernel.refine_block(gb, c, lo_x, st_x, top, hs, b0, b1 - b0, dw_block)
+            refine_kernel.gemm(dw_block, hs[b0:b1], g, alpha=1.0, beta=1.0)
+        if bool((c == start).all()):
+            break
+    return c
+
+
+def refine_codes(w, codes, lo, step, hs, nbits: int, block: int, passes: int) -> torch.Tensor:
+    """:func:`refine_expanded` for rows rounded at one ``(nbits, block)`` with decoded ladders
+    ``lo``/``step [N, K / block]``; returns codes of the dtype of ``codes``."""
+    lo_x, st_x = _expand(lo, step, block)
+    top = torch.full((w.shape[0],), float(2**nbits - 1), device=w.device)
+    return refine_expanded(w, codes, lo_x, st_x, top, hs, passes).to(codes.dtype)
+
+
+def _decoded(enc):
+    lo, step = decode_params(
+        enc.params[..., 0], enc.params[..., 1], enc.consts[:, 0:1], enc.consts[:, 1:2],
+        enc.consts[:, 2:3],
+    )
+    return lo.float(), step.float()
+
+
+def refine_groups(groups, hs: torch.Tensor, passes: int) -> list[torch.Tensor]:
+    """One sweep over the rows of every ``(w, enc, nbits, block)`` group of a tensor (rows of
+    different candidates share the column loop); returns the refined codes per group."""
+    parts = []
+    for w, enc, nbits, block in groups:
+        lo, step = _decoded(enc)
+        lo_x, st_x = _expand(lo, step, block)
+        top = torch.full((w.shape[0],), float(2**nbits - 1), device=w.device)
+        parts.append((w.float(), enc.codes.float(), lo_x, st_x, top))
+    cat = [torch.cat([p[i] for p in parts]) for i in range(5)]
+    out = refine_expanded(*cat, hs, passes)
+    sizes = [p[0].shape[0] for p in parts]
+    return [c.to(groups[i][1].codes.dtype) for i, c in enumerate(out.split(sizes))]
+
+
+def refine_encoded(enc, w, hs, nbits: int, block: int, passes: int):
+    """``enc`` with refined codes and a refreshed ``sse`` (weights ``diag(hs)``)."""
+    (codes,) = refine_groups([(w, enc, nbits, block)], hs, passes)
+    lo, step = _decoded(enc)
+    dev = w.device
+    k = w.shape[1]
+    wf = w.float().contiguous()
+    codes = codes.contiguous()
+    d = hs.diagonal().float().contiguous()
+    lo, step = lo.contiguous(), step.contiguous()
+    sse = torch.empty(w.shape[0], dtype=torch.float32, device=dev)
+    _lib.call(
+        "hi2_ladder_sse", _lib.ptr(codes), _lib.ptr(wf), wf.stride(0), _lib.ptr(d), _lib.ptr(lo),
+        _lib.ptr(step), lo.shape[1], w.shape[0], k, block, _lib.ptr(sse), _lib.stream(dev),
+    )
+    return type(enc)(codes, enc.params, enc.consts, sse, enc.comp)

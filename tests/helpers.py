@@ -1,0 +1,67 @@
+"""Seeded inputs and comparison helpers shared by the GPU parity tests."""
+
+import torch
+
+from oracle import ptq_oracle as po
+
+CASES = [(2, 16), (2, 32), (2, 64), (4, 16), (4, 32), (4, 64), (8, 32), (8, 64)]
+DEV = "cuda"
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def weights(rows, k, seed, outliers=True):
+    g = gen(seed)
+    w = torch.randn(rows, k, generator=g) * torch.exp(0.4 * torch.randn(rows, 1, generator=g))
+    if outliers:
+        w[:, :: max(1, k // 5)] *= 8
+    return w
+
+
+def activations(tokens, k, seed, spread=1.0, dtype=torch.float16):
+    g = gen(seed)
+    x = torch.randn(tokens, k, generator=g) * torch.exp(spread * torch.randn(1, k, generator=g))
+    return x.to(dtype)
+
+
+def correlated_layer(rows, k, seed, act_order=False):
+    """Weights, ladder weights d, factor u (oracle, CPU) and Hessian hs of a correlated input."""
+    g = gen(seed)
+    mix = torch.randn(k, k, generator=g) * 0.1 + torch.eye(k)
+    x = torch.randn(4 * k, k, generator=g) @ mix
+    x *= torch.exp(0.5 * torch.randn(1, k, generator=g))
+    hs = x.T @ x / x.shape[0]
+    w = weights(rows, k, seed + 1)
+    d = hs.diagonal().clone()
+    perm = None
+    if act_order:
+        perm = torch.argsort(d, descending=True)
+        hs = hs[perm][:, perm]
+    u = po.inverse_cholesky(hs, 0.01)
+    return w, d, u, perm, hs
+
+
+def agreement(a, b):
+    return (a.cpu() == b.cpu()).float().mean().item()
+
+
+def rel_close(a, b, rtol, atol=0.0):
+    a, b = a.double().cpu(), b.double().cpu()
+    return bool(((a - b).abs() <= atol + rtol * b.abs()).all())
+
+
+def decoded(params, consts):
+    lo, st = po.decode_ladders(params[..., 0].cpu(), params[..., 1].cpu(), consts[:, 0:1].cpu(),
+                               consts[:, 1:2].cpu(), consts[:, 2:3].cpu())
+    return lo.float(), st.float()
+
+
+def weighted_error(w, hs, codes, params, consts, block):
+    """Sum over rows of e Hs e^T for the stored-basis rows w (CPU, fp64)."""
+    lo, st = decoded(params, consts)
+    idx = torch.arange(w.shape[1]) // block
+    rec = (lo[:, idx] + codes.cpu().float() * st[:, idx]).half().double()
+    e = rec - w.double().cpu()
+    return float(((e @ hs.double().cpu()) * e).sum())

@@ -1,0 +1,124 @@
+"""No GPU needed: the library loads and exports what the header declares, the host logic of the
+multi-GPU plan is right (two gloo ranks), and the package refuses CPU tensors."""
+
+import os
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _declared():
+    text = (ROOT / "include" / "hi2_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hi2_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    from hi2_b200 import _lib
+    from hi2_b200.build import build
+
+    build()
+    lib = _lib.load()
+    names = _declared()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), n
+        assert n in _lib.SIGNATURES, f"{n} declared in the header but not bound in _lib.py"
+    assert set(_lib.SIGNATURES) <= set(names)
+    assert lib.hi2_abi_version() == 1
+
+
+def test_argument_checks_need_no_device():
+    """Bad shapes are refused before anything is launched."""
+    from hi2_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.hi2_rotate_groups(None, 0, None, 0, None, None, 4, 24, None) == _lib.ERR_ARG
+    assert b"multiple of 16" in lib.hi2_last_error()
+    assert lib.hi2_pack_codes(None, None, 1, 15, 2, None, None) == _lib.ERR_ARG
+    assert lib.hi2_gptq_lazy_update(None, 0, 128, 0, 128, None, None, None) == _lib.OK
+    assert lib.hi2_inverse_factor_workspace_bytes(1024) == 1024 * 1024 * 16
+    assert lib.hi2_hessian_workspace_bytes(100, 64, _lib.BF16) == 0  # small: FMA path, no scratch
+    need = lib.hi2_hessian_workspace_bytes(262144, 4096, _lib.BF16)
+    assert need > 0 and need % 4 == 0
+
+
+def test_cpu_tensors_are_refused_everywhere():
+    from hi2_b200.encode import encode_rows
+    from hi2_b200.format import fwht_groups, pack_codes
+    from hi2_b200.hessian import HessianStats, inverse_factor, transform_sigma
+
+    with pytest.raises(RuntimeError):
+        fwht_groups(torch.zeros(2, 32), torch.ones(2))
+    with pytest.raises(RuntimeError):
+        pack_codes(torch.zeros(2, 32, dtype=torch.uint8), 2)
+    with pytest.raises(RuntimeError):
+        encode_rows(torch.zeros(2, 32), torch.ones(32), 2, 16)
+    with pytest.raises(RuntimeError):
+        transform_sigma(torch.eye(32), None, torch.ones(2))
+    with pytest.raises(RuntimeError):
+        inverse_factor(torch.eye(32))
+    h = HessianStats(32, "cpu")
+    with pytest.raises((RuntimeError, ValueError)):
+        h.update(torch.zeros(4, 32))
+
+
+def test_token_shards_and_owners():
+    from hi2_b200 import dist as hd
+
+    for tokens, world in ((10, 4), (262144, 8), (3, 8)):
+        spans = [hd.token_shard(tokens, r, world) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == tokens
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        sizes = [b - a for a, b in spans]
+        assert max(sizes) - min(sizes) <= 1
+    assert [hd.owner_of(i, 4) for i in range(6)] == [0, 1, 2, 3, 0, 1]
+
+
+WORKER = r"""
+import os, sys, torch
+sys.path.insert(0, os.environ["HI2_ROOT"])
+from hi2_b200 import dist as hd
+rank, world, dev = hd.init_from_env("cpu", timeout_s=60)
+k, tokens = 32, 101
+g = torch.Generator().manual_seed(0)
+x = torch.randn(tokens, k, generator=g)
+lo, hi = hd.token_shard(tokens)
+part = x[lo:hi]
+full = x.T @ x
+for owner in range(world):
+    s = part.T @ part
+    n, _ = hd.reduce_second_moment(s, part.shape[0], owner)
+    assert n == tokens
+    if rank == owner:
+        assert torch.allclose(s, full, rtol=1e-5, atol=1e-4), (s - full).abs().max()
+s = part.T @ part
+assert hd.all_reduce_second_moment(s, part.shape[0]) == tokens
+assert torch.allclose(s, full, rtol=1e-5, atol=1e-4)
+tabs = hd.gather_tables([{"name": f"r{rank}", "sse": torch.full((2, 3), float(rank))}])
+assert [t["name"] for t in tabs] == [f"r{i}" for i in range(world)]
+hd.barrier()
+print("ok", rank)
+"""
+
+
+def test_two_gloo_ranks_reduce_and_gather(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, HI2_ROOT=str(ROOT), MASTER_ADDR="127.0.0.1", MASTER_PORT="29631",
+               WORLD_SIZE="2", CUDA_VISIBLE_DEVICES="")
+    procs = [
+        subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        for r in range(2)
+    ]
+    outs = [p.communicate(timeout=180)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o
+        assert "ok" in o

@@ -1,0 +1,124 @@
+"""Refinement sweep on the GPU against the oracle's column loop."""
+
+import pytest
+import torch
+
+from oracle import ptq_oracle as po
+from tests.helpers import DEV, agreement, correlated_layer
+
+pytestmark = pytest.mark.gpu
+
+
+def _groups(seed, k=448, rows=(37, 20)):
+    w, d, u, _, hs = correlated_layer(sum(rows), k, seed)
+    out, r0 = [], 0
+    for n, (nb, b) in zip(rows, ((2, 32), (4, 64))):
+        part = w[r0 : r0 + n]
+        out.append((part, po.gptq_rows(part, d, u, nb, b, "normal"), nb, b))
+        r0 += n
+    return out, hs
+
+
+def _to_dev(groups):
+    from hi2_b200.encode import Encoded
+
+    return [
+        (w.to(DEV), Encoded(e.codes.to(DEV), e.params.to(DEV), e.consts.to(DEV), e.sse.to(DEV)), nb, b)
+        for w, e, nb, b in groups
+    ]
+
+
+def test_refine_groups_matches_oracle():
+    from hi2_b200.refine import refine_groups
+
+    groups, hs = _groups(11)
+    want = po.refine_groups(groups, hs, 2)
+    got = refine_groups(_to_dev(groups), hs.to(DEV), 2)
+    for g, w_, (_, enc, nb, _) in zip(got, want, groups):
+        assert g.dtype == torch.uint8
+        assert agreement(g, w_) >= 0.999
+        assert int(g.max()) <= 2**nb - 1
+        assert (g.cpu().int() - enc.codes.int()).abs().max() <= 2
+
+
+def test_refine_fixture(golden):
+    from hi2_b200.encode import Encoded
+    from hi2_b200.refine import refine_groups
+
+    r = golden["refine"]
+    groups = [
+        (g["w"].to(DEV), Encoded(*(g["enc"][f].to(DEV) for f in ("codes", "params", "consts", "sse"))),
+         g["nbits"], g["block"])
+        for g in r["groups"]
+    ]
+    got = refine_groups(groups, r["hs"].to(DEV), 2)
+    ok = sum(int((a.cpu() == b).sum()) for a, b in zip(got, r["codes"]))
+    assert ok / sum(b.numel() for b in r["codes"]) >= 0.999
+
+
+def test_sweep_never_raises_the_objective_and_converges():
+    from hi2_b200.refine import objective, refine_codes
+
+    groups, hs = _groups(12, k=256, rows=(40, 1))
+    w, enc, nb, b = groups[0]
+    lo, st = po._decoded(enc.params[..., 0], enc.params[..., 1], enc.consts)
+    wd, hd, lod, std = w.to(DEV), hs.to(DEV), lo.to(DEV), st.to(DEV)
+    c0 = enc.codes.to(DEV)
+    before = objective(wd, c0, lod, std, hd, b)
+    c1 = refine_codes(wd, c0, lod, std, hd, nb, b, 1)
+    after1 = objective(wd, c1, lod, std, hd, b)
+    assert after1 <= before * (1 + 1e-6)
+    assert (c1.int() - c0.int()).abs().max() <= 1
+    c9 = refine_codes(wd, c0, lod, std, hd, nb, b, 50)  # runs until a sweep moves nothing
+    again = refine_codes(wd, c9, lod, std, hd, nb, b, 1)
+    assert torch.equal(again, c9)
+    assert objective(wd, c9, lod, std, hd, b) <= after1 * (1 + 1e-6)
+    assert abs(before - po.hessian_objective(w, enc.codes, lo, st, hs, b)) <= 1e-4 * before
+
+
+def test_refine_block_entry_point():
+    """The per-block entry point with the reference's buffer contract; rows and columns that do
+    not fill a thread block or a 128-column block."""
+    from hi2_b200 import refine_kernel
+
+    g = torch.Generator().manual_seed(4)
+    n, k, b0, length = 37, 192, 128, 64
+    a = torch.randn(k, k, generator=g)
+    hs = (a @ a.T / k).to(DEV).contiguous()
+    c = torch.randint(0, 4, (n, k), generator=g).float().to(DEV)
+    lo = (torch.randn(n, k, generator=g) * 0.1).half().float().to(DEV)
+    st = (torch.rand(n, k, generator=g) * 0.2).half().float().to(DEV)
+    st[:, 130] = 0.0
+    top = torch.full((n,), 3.0, device=DEV)
+    gfull = torch.randn(n, k, generator=g).to(DEV)
+    gb = gfull[:, b0 : b0 + length].contiguous()
+    dwb = torch.full((n, length), 7.0, device=DEV)
+    c_new = c.clone()
+    refine_kernel.refine_block(gb, c_new, lo, st, top, hs, b0, length, dwb)
+    # oracle: the same block by the plain loop
+    cc, gg = c.cpu().clone(), gb.cpu().clone()
+    hs_c, lo_c, st_c = hs.cpu(), lo.cpu(), st.cpu()
+    moved = torch.zeros(n, length)
+    for i in range(length):
+        j = b0 + i
+        cur = (lo_c[:, j] + cc[:, j] * st_c[:, j]).half().float()
+        best = torch.full((n,), -float("inf"))
+        pick = torch.zeros(n)
+        dws = torch.zeros(n)
+        for delta in (1.0, -1.0):
+            cand = cc[:, j] + delta
+            dw = (lo_c[:, j] + cand * st_c[:, j]).half().float() - cur
+            ok = (cand >= 0) & (cand <= 3) & (st_c[:, j] > 0)
+            gain = torch.where(ok, -(2 * dw * gg[:, i] + dw * dw * hs_c[j, j]), torch.tensor(-float("inf")))
+            better = gain > best
+            best = torch.where(better, gain, best)
+            pick = torch.where(better, torch.tensor(delta), pick)
+            dws = torch.where(better, dw, dws)
+        take = best > 0
+        cc[:, j] += torch.where(take, pick, torch.tensor(0.0))
+        dwj = torch.where(take, dws, torch.tensor(0.0))
+        moved[:, i] = dwj
+        gg += dwj[:, None] * hs_c[j, b0 : b0 + length][None, :]
+    assert torch.equal(c_new.cpu(), cc)
+    assert torch.equal(dwb.cpu(), moved)
+    assert torch.equal(c_new[:, :b0], c[:, :b0])
