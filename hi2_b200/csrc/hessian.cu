@@ -38,7 +38,7 @@ constexpr int CHUNK_KB = 16;  // stages per tensor-memory accumulation (1024 tok
 constexpr int BOX_BYTES = 64 * BKT * 2;
 constexpr int A_BYTES = (BM / 64) * BOX_BYTES;
 constexpr int STAGE_BYTES = A_BYTES + (BN / 64) * BOX_BYTES;
-constexpr int TC_THREADS = 320;  // warps 0..7 epilogue, warp 8 TMA, warp 9 MMA (200 registers each)
+constexpr int TC_THREADS = 320;  // warps 0..7 epilogue, warp 8 TMA, warp 9 MMA
 constexpr int TILE_ELEMS = BM * BN;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about one second
 
@@ -182,8 +182,9 @@ __device__ __forceinline__ void decode_tile(int tile, int njb, int& ib, int& jb)
   jb = (i >> 1) + tile;
 }
 
-// 320 threads x 200 registers = 64000 of the 65536 per SM (one CTA per SM, set by shared memory)
-__global__ void __maxnreg__(200)
+// Ten warps: the register file is four partitions of 16384, so two partitions hold three warps
+// and a thread gets at most 16384 / (3 * 32) -> 168 registers (128 of them accumulators).
+__global__ void __launch_bounds__(TC_THREADS, 1)
 hessian_tc_kernel(const __grid_constant__ CUtensorMap map, const TcParams p) {
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) &
@@ -474,4 +475,22 @@ extern "C" int hi2_hessian_accumulate(const void* x, int dtype, int64_t tokens, 
   if (dtype == HI2_F16) return accumulate_fma<__half>(x, tokens, k, s, st);
   if (dtype == HI2_F32) return accumulate_fma<float>(x, tokens, k, s, st);
   return fail(HI2_ERR_ARG, "hessian_accumulate: dtype must be F16, BF16 or F32");
+}
+
+// Launch-resource figures of the tensor-core kernel on the current device (diagnostics):
+// out = {registers, static smem, max dynamic smem, max threads per block, active blocks per SM
+// at the launch configuration, requested dynamic smem, threads}.
+extern "C" int hi2_hessian_kernel_info(int64_t* out) {
+  using namespace hi2;
+  HI2_REQUIRE(out != nullptr, "hessian_kernel_info: null pointer");
+  cudaFuncSetAttribute(hessian_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+  cudaFuncAttributes a;
+  if (cudaFuncGetAttributes(&a, hessian_tc_kernel) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "hessian_kernel_info: cudaFuncGetAttributes failed");
+  int blocks = -1;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, hessian_tc_kernel, TC_THREADS, TC_SMEM);
+  out[0] = a.numRegs, out[1] = (int64_t)a.sharedSizeBytes, out[2] = a.maxDynamicSharedSizeBytes;
+  out[3] = a.maxThreadsPerBlock, out[4] = blocks, out[5] = (int64_t)TC_SMEM, out[6] = TC_THREADS;
+  cudaGetLastError();
+  return HI2_OK;
 }

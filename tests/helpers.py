@@ -65,3 +65,21 @@ def weighted_error(w, hs, codes, params, consts, block):
     rec = (lo[:, idx] + codes.cpu().float() * st[:, idx]).half().double()
     e = rec - w.double().cpu()
     return float(((e @ hs.double().cpu()) * e).sum())
+
+
+def ladder_report(got, want):
+    """How far two encodings of the same rows agree: share of rows whose ladders (parameter bytes
+    and row constants) are identical, share of rows whose constants agree to 1e-3, share of equal
+    parameter bytes and codes, and share of equal codes inside the rows with identical ladders."""
+    gp, gc, gk = got.params.cpu(), got.consts.cpu(), got.codes.cpu()
+    same = (gp == want.params).all(-1).all(-1) & (gc == want.consts).all(-1)
+    cf, wf = gc.float(), want.consts.float()
+    consts_ok = ((cf - wf).abs() <= 1e-3 * wf.abs() + 1e-6).all(-1)
+    return dict(
+        rows_same=same.float().mean().item(),
+        consts_ok=consts_ok.float().mean().item(),
+        params=(gp == want.params).float().mean().item(),
+        codes=(gk == want.codes).float().mean().item(),
+        codes_same_rows=(gk[same] == want.codes[same]).float().mean().item() if bool(same.any()) else 1.0,
+        same=same,
+    )

