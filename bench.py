@@ -1,0 +1,517 @@
+"""Benchmark of the per-layer PTQ encode path (Hessian + tables + allocation + GPTQ + pack).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config cfg2|cfg1|tiny]
+
+One step = the whole path over one Llama-style decoder layer per GPU (BASELINE config 2: seven
+bf16 matrices, hidden 4096 / FFN 11008, 128 x 2048 synthetic calibration tokens per distinct
+input, 2.5 bpw, INT2/INT4 candidates).  With N GPUs there are N layers, layer l owned by rank l;
+the calibration tokens of every layer are sharded over the ranks, partial second moments are
+reduced to the owner over NCCL, the error tables are all-gathered for the global allocation, and
+everything else runs on the owner ("weak" scaling: work per GPU is fixed).
+
+Prints ONE JSON line (rank 0).  ``value`` is rows of weight matrix encoded per second with all
+inputs resident in HBM; ``e2e`` is the same through the public API from pinned host buffers with
+the packed result copied back.  ``--impl reference`` times the CPU restatement of the reference
+(oracle/) on the host cores on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+CONFIGS = {
+    # name: hidden, ffn, sequences, seq_len, activation spread, target bpw, weight dtype
+    "cfg2": dict(hidden=4096, ffn=11008, tokens=128 * 2048, spread=1.5, bpw=2.5, dtype="bf16",
+                 workload="llama_decoder_layer_7_matrices_4096x11008_128x2048_tokens_2.5bpw"),
+    "cfg1": dict(hidden=4096, ffn=0, tokens=2048, spread=1.0, bpw=3.0, dtype="f16",
+                 workload="single_linear_4096x4096_2048_tokens_3.0bpw"),
+    "tiny": dict(hidden=512, ffn=1024, tokens=4096, spread=1.5, bpw=2.5, dtype="bf16",
+                 workload="tiny_decoder_layer_512x1024_4096_tokens_2.5bpw"),
+}
+
+
+def shapes_of(cfg):
+    from hi2_b200.layer import LayerPlan, llama_plan, llama_shapes
+
+    if cfg["ffn"] == 0:  # a single Linear (BASELINE config 1)
+        return {"w": (cfg["hidden"], cfg["hidden"])}, {"x": cfg["hidden"]}, LayerPlan({"w": "x"})
+    w, x = llama_shapes(cfg["hidden"], cfg["ffn"])
+    return w, x, llama_plan()
+
+
+def torch_dtype(name):
+    return {"bf16": torch.bfloat16, "f16": torch.float16}[name]
+
+
+def make_weights(cfg, shapes, layer, device):
+    """Random-init weights N(0, 0.02); config 1 scales 0.1 % of the input columns by 20."""
+    g = torch.Generator(device=device).manual_seed(1000 + layer)
+    out = {}
+    for name, (r, k) in shapes.items():
+        w = torch.randn(r, k, generator=g, device=device) * 0.02
+        if cfg["ffn"] == 0:
+            cols = torch.randperm(k, generator=g, device=device)[: max(1, k // 1000)]
+            w[:, cols] *= 20
+        out[name] = w.to(torch_dtype(cfg["dtype"]))
+    return out
+
+
+def make_inputs(cfg, widths, layer, tokens, token0, device):
+    """Synthetic activations: N(0,1) times a per-channel lognormal(0, spread) scale.  The channel
+    scales depend on the layer only, the token noise on (layer, first token), so token shards of
+    one layer are shards of one tensor."""
+    out = {}
+    for i, (name, k) in enumerate(widths.items()):
+        gs = torch.Generator(device=device).manual_seed(77 + 13 * layer + i)
+        scale = torch.exp(cfg["spread"] * torch.randn(1, k, generator=gs, device=device))
+        gx = torch.Generator(device=device).manual_seed(5000 + 101 * layer + 7 * i + token0)
+        x = torch.empty(tokens, k, dtype=torch_dtype(cfg["dtype"]), device=device)
+        step = 16384
+        for t0 in range(0, tokens, step):
+            n = min(step, tokens - t0)
+            x[t0 : t0 + n] = (torch.randn(n, k, generator=gx, device=device) * scale).to(x.dtype)
+        out[name] = x
+    return out
+
+
+class Clocks:
+    """Samples nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        for line in self.lines:
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2])), power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------
+# the B200 arm
+# --------------------------------------------------------------------------------------------
+class Job:
+    """Resident workload of one rank: the weights of its own layer and its token shard of the
+    calibration activations of every layer."""
+
+    def __init__(self, cfg, rank, world, device):
+        from hi2_b200 import dist as hd
+        from hi2_b200.calibrate import ALL_CANDIDATES, Config
+
+        self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
+        self.shapes, self.widths, self.plan = shapes_of(cfg)
+        self.qcfg = Config(candidates=list(ALL_CANDIDATES))
+        self.weights = make_weights(cfg, self.shapes, rank, device)
+        lo, hi = hd.token_shard(cfg["tokens"], rank, world)
+        self.inputs = [make_inputs(cfg, self.widths, layer, hi - lo, lo, device) for layer in range(world)]
+        self.rows = sum(r for r, _ in self.shapes.values())
+        self.host = None
+        self.copy_stream = None
+        self.stage_ms: dict = {}
+
+    # bytes one rank moves per step in the end-to-end measurement
+    def h2d_bytes(self):
+        n = sum(w.numel() * w.element_size() for w in self.weights.values())
+        return n + sum(x.numel() * x.element_size() for layer in self.inputs for x in layer.values())
+
+    def pin_host_copies(self):
+        self.host = {"w": {k: v.cpu().pin_memory() for k, v in self.weights.items()},
+                     "x": [{k: v.cpu().pin_memory() for k, v in layer.items()} for layer in self.inputs]}
+        self.copy_stream = torch.cuda.Stream(self.device)
+
+    def _mark(self, marks, name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append((name, ev))
+
+    def step(self, from_host=False, to_host=False):
+        from hi2_b200 import dist as hd
+        from hi2_b200 import layer as L
+        from hi2_b200.allocate import allocate_global
+        from hi2_b200.calibrate import TensorTable
+
+        marks: list = []
+        ready = None
+        if from_host:  # this step's inputs come over PCIe, overlapped with the kernels below
+            ready = {}
+            with torch.cuda.stream(self.copy_stream):
+                for layer, xs in enumerate(self.inputs):
+                    for name, x in xs.items():
+                        x.copy_(self.host["x"][layer][name], non_blocking=True)
+                        ready[(layer, name)] = self.copy_stream.record_event()
+                for name, w in self.weights.items():
+                    w.copy_(self.host["w"][name], non_blocking=True)
+                ready["w"] = self.copy_stream.record_event()
+        cur = torch.cuda.current_stream(self.device)
+        self._mark(marks, "hessian")
+        shared_all, pending = [], []
+        for layer, xs in enumerate(self.inputs):
+            shared = {}
+            for name, x in xs.items():
+                if ready is not None:
+                    cur.wait_event(ready[(layer, name)])
+                L.accumulate({name: x}, self.device, into=shared)
+            shared_all.append(shared)
+            owner = hd.owner_of(layer, self.world)
+            for s in shared.values():  # partial sums of this rank's tokens -> the layer's owner
+                n, work = hd.reduce_second_moment(s.hessian.S, s.hessian.n, owner, async_op=True)
+                s.hessian.n = n
+                if work is not None:
+                    pending.append(work)
+        for work in pending:
+            work.wait()
+        mine = shared_all[self.rank]
+        self._mark(marks, "statistics")
+        L.finish_statistics(mine, self.qcfg)
+        if ready is not None:
+            cur.wait_event(ready["w"])
+        self._mark(marks, "tables")
+        tables = L.tabulate(self.weights, self.plan, mine, self.qcfg)
+        self._mark(marks, "allocate")
+        tag = f"L{self.rank}."
+        for name, t in tables.items():
+            t.name = tag + name
+        if self.world == 1:
+            everything = list(tables.values())
+        else:  # a few bytes per row: every rank allocates over every table and keeps its own picks
+            local = [dict(name=t.name, shape=t.shape, had=t.had, sse=t.sse.cpu(), candidates=t.candidates,
+                          energy=t.energy, n_tokens=t.n_tokens, col_scale=t.col_scale) for t in tables.values()]
+            everything = [TensorTable(**{**d, "sse": d["sse"].to(self.device)}) for d in hd.gather_tables(local)]
+        alloc = allocate_global(everything, self.cfg["bpw"])
+        picks = {name: alloc.picks[tag + name] for name in tables}
+        self._mark(marks, "encode")
+        packed = L.encode(self.weights, self.plan, mine, tables, picks, self.qcfg, to_host=to_host)
+        self._mark(marks, "end")
+        self.last = dict(marks=marks, alloc=alloc, packed=packed)
+        return packed
+
+    def collect_stage_times(self):
+        marks = self.last["marks"]
+        for (name, a), (_, b) in zip(marks, marks[1:]):
+            self.stage_ms[name] = self.stage_ms.get(name, 0.0) + a.elapsed_time(b)
+
+    def d2h_bytes(self):
+        from hi2_b200.format import FIELDS
+
+        return sum(getattr(t, f).numel() * getattr(t, f).element_size()
+                   for t in self.last["packed"].values() for f in FIELDS)
+
+
+def hessian_flops(widths, tokens):
+    """(algorithmic 2 T K^2, issued by the upper-triangle 128 x 256 tiles) summed over the inputs."""
+    algo = issued = 0.0
+    for k in widths.values():
+        nib, njb = -(-k // 128), -(-k // 256)
+        tiles = sum(njb - (ib >> 1) for ib in range(nib))
+        algo += 2.0 * tokens * k * k
+        issued += 2.0 * tokens * tiles * 128 * 256
+    return algo, issued
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return dict(hbm=p["hbm_gbs"], tensor=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    tensor_burst=p["bf16_tflops"], source="measured")
+    return dict(hbm=6650.0, tensor=1400.0, tensor_burst=1590.0, source="fallback")
+
+
+# --------------------------------------------------------------------------------------------
+# the CPU arm: the oracle (a restatement of the reference's CPU path) on the host cores
+# --------------------------------------------------------------------------------------------
+def cpu_sample(cfg, rows_s: int, tokens_s: int, threads: int) -> dict:
+    """Time every stage of the path on a bounded sample of the workload and scale each stage to
+    the full workload by the units it processes (tokens for the second moments, rows for tables,
+    GPTQ and packing; the basis change and the factorisation run at full size).  Returns the
+    extrapolated seconds per stage and their sum."""
+    from oracle import ptq_oracle as po
+
+    torch.set_num_threads(threads)
+    shapes, widths, plan = shapes_of(cfg)
+    cands = [(nb, b) for nb in (2, 4) for b in (16, 32, 64)]
+    dt = torch_dtype(cfg["dtype"])
+    g = torch.Generator().manual_seed(0)
+    t = {k: 0.0 for k in ("hessian", "statistics", "tables", "allocate", "factor", "gptq", "pack")}
+    tok_scale = cfg["tokens"] / tokens_s
+    shared = {}
+    for name, k in widths.items():
+        x = (torch.randn(tokens_s, k, generator=g) * torch.exp(cfg["spread"] * torch.randn(1, k, generator=g))).to(dt)
+        t0 = time.perf_counter()
+        sm, gm = po.SecondMoment(k), po.GroupMoments(k)
+        sm.update(x)
+        gm.update(x)
+        t["hessian"] += (time.perf_counter() - t0) * tok_scale
+        t0 = time.perf_counter()
+        s16 = po.smoothing_vector(gm, 0.5)
+        had = torch.ones(k // 16, dtype=torch.uint8)
+        d_tab = gm.diag(had, 1.0 / s16.float())
+        t["statistics"] += time.perf_counter() - t0
+        t0 = time.perf_counter()
+        hs = po.stored_basis_hessian(sm.mean(), s16, had)
+        u = po.inverse_cholesky(hs, 0.01)
+        t["factor"] += time.perf_counter() - t0
+        shared[name] = dict(s16=s16, had=had, d_tab=d_tab, hs=hs, u=u, d=hs.diagonal().clone())
+    tables, stored = [], {}
+    for name, (r, k) in shapes.items():
+        s = shared[plan.reads[name]]
+        rs = min(rows_s, r)
+        w = (torch.randn(rs, k, generator=g) * 0.02).to(dt)
+        t0 = time.perf_counter()
+        wt = po.rotate_groups(w.float() * s["s16"].float(), s["had"])
+        sse = torch.stack([po.nearest_rows(wt, s["d_tab"], nb, b).sse for nb, b in cands])
+        energy = float((s["d_tab"] * wt**2).sum())
+        t["tables"] += (time.perf_counter() - t0) * (r / rs)
+        tables.append(po.Table(name, (rs, k), s["had"], sse, list(cands), energy, cfg["tokens"], s["s16"]))
+        stored[name] = (wt, r / rs)
+    t0 = time.perf_counter()
+    alloc = po.allocate_rows(tables, cfg["bpw"])
+    t["allocate"] += time.perf_counter() - t0
+    for table in tables:
+        s = shared[plan.reads[table.name]]
+        wt, scale = stored[table.name]
+        picks = alloc.picks[table.name]
+        pieces = []
+        t0 = time.perf_counter()
+        for ci, (nb, b) in enumerate(cands):
+            rows = (picks == ci).nonzero().flatten()
+            if rows.numel():
+                e = po.gptq_rows(wt[rows], s["d"], s["u"], nb, b)
+                pieces.append((rows, e.codes, e.params, e.consts))
+        t["gptq"] += (time.perf_counter() - t0) * scale
+        t0 = time.perf_counter()
+        nbits = torch.tensor([cands[i][0] for i in picks.tolist()])
+        block = torch.tensor([cands[i][1] for i in picks.tolist()])
+        po.assemble_flat(pieces, nbits, block, s["had"], wt.shape[1], s["s16"])
+        t["pack"] += (time.perf_counter() - t0) * scale
+    total = sum(t.values())
+    return dict(seconds=total, stages={k: round(v, 3) for k, v in t.items()},
+                rows=sum(r for r, _ in shapes.values()),
+                sample=f"{rows_s} rows of each matrix and {tokens_s} of {cfg['tokens']} tokens per input, "
+                       f"each stage scaled by its units; basis change and factorisation at full size")
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = host_threads()
+    rows_s, tokens_s = (32, 1024) if cfg["ffn"] else (256, cfg["tokens"])
+    times = []
+    for i in range(args.warmup + args.steps):
+        res = cpu_sample(cfg, rows_s, tokens_s, threads)
+        if i >= args.warmup:
+            times.append(res)
+    secs = sum(r["seconds"] for r in times) / len(times)
+    value = res["rows"] / secs
+    line = {
+        "impl": "reference", "metric": "ptq_encode_rows_per_s", "value": value, "unit": "rows/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg["workload"], "note": "CPU restatement of the reference on the host cores; "
+                   "ms_per_step is the full-workload time extrapolated from the sample"},
+        "encode_wall_s": secs,
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
+                         "sample": res["sample"], "stages_s": res["stages"]},
+        "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# measured with ncu on the second-moment kernel (profiles/): DRAM bytes per token-column pair
+# read, filled in after a capture; None means "no capture yet"
+HESSIAN_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def mem_available_bytes() -> int:
+    try:
+        for line in open("/proc/meminfo"):
+            if line.startswith("MemAvailable"):
+                return int(line.split()[1]) * 1024
+    except OSError:
+        pass
+    return 0
+
+
+def run_ours(args, cfg):
+    import torch.distributed as dist
+
+    from hi2_b200 import _lib
+    from hi2_b200 import dist as hd
+
+    rank, world, device = hd.init_from_env("cuda")
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
+    _lib.load()
+    job = Job(cfg, rank, world, device)
+
+    def sync_all():
+        torch.cuda.synchronize(device)
+        hd.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        job.step()
+    sync_all()
+    clocks = Clocks(device.index or 0)
+    if rank == 0:
+        clocks.start()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        job.step()
+        torch.cuda.synchronize(device)
+        job.collect_stage_times()
+    ev1.record()
+    sync_all()
+    launches = _lib.launch_count() - launches0
+    ms = torch.tensor([ev0.elapsed_time(ev1) / args.steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item())
+    clock_info = clocks.stop() if rank == 0 else None
+    alloc = job.last["alloc"]
+
+    # ---- end to end: pinned host buffers in, packed buffers out ------------------------------
+    e2e = None
+    need = job.h2d_bytes()
+    if mem_available_bytes() > 3 * need * max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world))):
+        job.pin_host_copies()
+        job.step(from_host=True, to_host=True)  # warm-up of the copy path
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            job.step(from_host=True, to_host=True)
+        e1.record()
+        sync_all()
+        ems = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+        e2e = {"value": job.rows * world / (float(ems.item()) / 1e3), "unit": "rows/s",
+               "ms_per_step": float(ems.item()), "h2d_bytes_per_step": need * world,
+               "d2h_bytes_per_step": job.d2h_bytes() * world}
+    else:
+        e2e = {"value": None, "unit": "rows/s", "h2d_bytes_per_step": need * world, "d2h_bytes_per_step": 0,
+               "note": "host memory too small to pin the inputs"}
+
+    if rank != 0:
+        return
+    pk = peaks()
+    stage = {k: v / args.steps for k, v in job.stage_ms.items()}
+    algo, issued = hessian_flops(job.widths, cfg["tokens"])
+    hess_s = stage["hessian"] / 1e3
+    achieved = issued / hess_s / 1e12
+    roofline = {
+        "kernel": "hessian_tc_kernel (second moment X^T X, tcgen05, fp32 accumulate)",
+        "bound": "tensor", "achieved": achieved, "peak": pk["tensor"], "unit": "TFLOP/s",
+        "frac": achieved / pk["tensor"], "peak_source": f"{pk['source']}, sustained (kernel timed inside a long step)",
+        "effective": algo / hess_s / 1e12,
+        "note": "achieved counts the flops issued (upper-triangle 128x256 tiles); effective counts 2*T*K^2",
+        "traffic": HESSIAN_TRAFFIC_BYTES_PER_LAUNCH,
+        "launch_ms": hess_s * 1e3 / max(1, len(job.widths) * world),
+    }
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        rows_s, tokens_s = (32, 1024) if cfg["ffn"] else (256, cfg["tokens"])
+        threads = host_threads()
+        res = cpu_sample(cfg, rows_s, tokens_s, threads)
+        cpu = {"value": res["rows"] / res["seconds"], "unit": "rows/s", "cores": threads, "kind": "port",
+               "sample": res["sample"], "seconds_full_workload": res["seconds"], "stages_s": res["stages"]}
+    gptq_rows_per_s = None
+    line = {
+        "metric": "ptq_encode_rows_per_s", "value": job.rows * world / (ms_per_step / 1e3), "unit": "rows/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg["workload"], "layers": world, "rows_per_layer": job.rows,
+                   "tokens_per_input": cfg["tokens"], "target_bpw": cfg["bpw"], "achieved_bpw": alloc.bpw,
+                   "candidates": "int2,int4 x b16,b32,b64", "parallelism": f"layer-per-gpu x{world}, token-sharded hessian",
+                   "l2": "inputs larger than L2 (12 GB of activations per step)"},
+        "encode_wall_s": ms_per_step / 1e3,
+        "stage_ms": {k: round(v, 3) for k, v in stage.items()},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+        "gpu_launches": launches, "clocks": clock_info,
+    }
+    del gptq_rows_per_s
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="cfg2", choices=sorted(CONFIGS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -24,6 +24,8 @@ _P, _I, _L, _Z, _F, _D = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float, 
 SIGNATURES = {
     "hi2_abi_version": (_I, []),
     "hi2_last_error": (C.c_char_p, []),
+    "hi2_launch_count": (C.c_longlong, []),
+    "hi2_hessian_kernel_info": (_I, [_P]),
     "hi2_rotate_groups": (_I, [_P, _I, _P, _I, _P, _P, _L, _L, _P]),
     "hi2_pack_codes": (_I, [_P, _P, _L, _L, _I, _P, _P]),
     "hi2_assemble_piece": (_I, [_P, _L, _P, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
@@ -82,6 +84,10 @@ def load():
 
 def failure() -> str | None:
     return _failed
+
+
+def launch_count() -> int:
+    return int(load().hi2_launch_count())
 
 
 def last_error() -> str:

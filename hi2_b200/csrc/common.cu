@@ -2,12 +2,17 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace hi2 {
 namespace {
 thread_local char g_error[512] = "";
+std::atomic<long long> g_launches{0};
 }
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -19,3 +24,4 @@ void set_error(const char* fmt, ...) {
 
 extern "C" int hi2_abi_version(void) { return 1; }
 extern "C" const char* hi2_last_error(void) { return hi2::g_error; }
+extern "C" long long hi2_launch_count(void) { return hi2::g_launches.load(std::memory_order_relaxed); }

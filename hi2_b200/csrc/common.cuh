@@ -16,6 +16,7 @@
 namespace hi2 {
 
 void set_error(const char* fmt, ...);
+void note_launch();  // one more kernel launch enqueued by this library (process-wide counter)
 
 inline int fail(int code, const char* what) {
   set_error("%s", what);
@@ -23,6 +24,7 @@ inline int fail(int code, const char* what) {
 }
 
 inline int check_launch(const char* what) {
+  note_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("%s: %s", what, cudaGetErrorString(e));

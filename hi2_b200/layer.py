@@ -1,0 +1,103 @@
+"""One decoder layer through the whole encode path on one GPU: the call a user of this package
+makes when the calibration activations of the layer's Linears are at hand.
+
+    stats  = accumulate(inputs)                      second moments (tcgen05) + group moments
+    tables = tabulate(weights, stats, cfg)           rotation + per-row error tables
+    alloc  = allocate_global(tables, target_bpw)     (hi2_b200.allocate; all tables of the model)
+    packed = encode(weights, stats, tables, alloc)   basis change, factor, GPTQ, packing
+
+It is the order of hi2's pipeline (tabulate -> allocate -> encode, hi2/pipeline.py:1087-1252) with
+the per-tensor stages of hi2/calibrate.py; Linears that read the same tensor (q/k/v, gate/up)
+share one set of statistics, one smoothing vector and one factor, as in hi2/layerwise.py:140-154.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .calibrate import Config, EncodeRequest, TensorTable, build_table, encode_many, smoothing_scale
+from .format import GROUP, HI2Tensor
+from .hessian import HessianStats
+from .stats import ColumnStats
+
+
+@dataclass
+class SharedInput:
+    """Calibration statistics of one distinct Linear input of width ``k``."""
+
+    name: str
+    k: int
+    hessian: HessianStats
+    moments: ColumnStats | None = None
+    transform: tuple | None = None  # (fp16 smoothing vector or None, uint8 flags)
+
+
+@dataclass
+class LayerPlan:
+    """Which weight reads which input: ``{"q": "attn_in", ...}``."""
+
+    reads: dict = field(default_factory=dict)
+
+
+def accumulate(inputs: dict, device, into: dict | None = None) -> dict:
+    """``{input name: activations [tokens, k]}`` -> ``{input name: SharedInput}`` with the second
+    moment summed (``into`` continues earlier sums: more tokens, or another rank's shard)."""
+    out = into if into is not None else {}
+    for name, x in inputs.items():
+        k = x.shape[-1]
+        if name not in out:
+            out[name] = SharedInput(name, k, HessianStats(k, device))
+        out[name].hessian.update(x)
+    return out
+
+
+def finish_statistics(shared: dict, cfg: Config) -> None:
+    """Group moments, smoothing vector and rotation flags of every input (after all tokens, and
+    after any cross-rank reduction of the second moments)."""
+    for s in shared.values():
+        s.moments = ColumnStats.from_second_moment(s.hessian.S, s.hessian.n)
+        flags = torch.ones(s.k // GROUP, dtype=torch.uint8) if cfg.rotation == "on" else torch.zeros(
+            s.k // GROUP, dtype=torch.uint8)
+        s.transform = (smoothing_scale(s.moments, cfg.smooth), flags)
+
+
+def tabulate(weights: dict, plan: LayerPlan, shared: dict, cfg: Config) -> dict:
+    """Error tables of every weight ``{name: [R, K] tensor}``."""
+    tables = {}
+    for name, w in weights.items():
+        s = shared[plan.reads[name]]
+        tables[name] = build_table(name, w, s.moments, cfg, transform=s.transform)
+    return tables
+
+
+def encode(weights: dict, plan: LayerPlan, shared: dict, tables: dict, picks: dict, cfg: Config,
+           to_host: bool = True) -> dict:
+    """Packed ``HI2Tensor`` of every weight for the allocator's ``picks``."""
+    reqs, names = [], []
+    for name, w in weights.items():
+        s = shared[plan.reads[name]]
+        reqs.append(EncodeRequest(w, s.moments, tables[name], picks[name], sigma=s.hessian.S,
+                                  sigma_id=s.name, sigma_n=s.hessian.n))
+        names.append(name)
+    out = encode_many(reqs, cfg, to_host=to_host)
+    return dict(zip(names, out))
+
+
+def llama_plan() -> LayerPlan:
+    """The seven matrices of a Llama-style decoder layer and the four tensors they read."""
+    return LayerPlan({"q": "attn_in", "k": "attn_in", "v": "attn_in", "o": "attn_out",
+                      "gate": "mlp_in", "up": "mlp_in", "down": "mlp_mid"})
+
+
+def llama_shapes(hidden: int = 4096, ffn: int = 11008) -> tuple[dict, dict]:
+    """``({weight: (rows, k)}, {input: k})`` of one decoder layer."""
+    w = {"q": (hidden, hidden), "k": (hidden, hidden), "v": (hidden, hidden), "o": (hidden, hidden),
+         "gate": (ffn, hidden), "up": (ffn, hidden), "down": (hidden, ffn)}
+    x = {"attn_in": hidden, "attn_out": hidden, "mlp_in": hidden, "mlp_mid": ffn}
+    return w, x
+
+
+__all__ = ["SharedInput", "LayerPlan", "accumulate", "finish_statistics", "tabulate", "encode",
+           "llama_plan", "llama_shapes", "Config", "TensorTable", "HI2Tensor"]

@@ -38,6 +38,13 @@ enum { HI2_F32 = 0, HI2_F64 = 1, HI2_F16 = 2, HI2_BF16 = 3 };
 
 int hi2_abi_version(void);
 const char* hi2_last_error(void);
+/* Kernel launches this library has enqueued in the process so far (all threads).  No counterpart
+ * in the reference; benchmarks difference it around a timed region. */
+long long hi2_launch_count(void);
+/* Launch-resource figures of the tensor-core second-moment kernel on the current device:
+ * out[7] = registers, static smem, max dynamic smem, max threads per block, resident blocks per
+ * SM at the launch configuration, requested dynamic smem, threads.  Diagnostics only. */
+int hi2_hessian_kernel_info(int64_t* out);
 
 /* ---- rotation ------------------------------------------------------------------------------
  * hi2/format.py:30-41 fwht_groups, fused with the cast and smoothing multiply of
