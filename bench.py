@@ -38,6 +38,9 @@ CONFIGS = {
                  workload="llama_decoder_layer_7_matrices_4096x11008_128x2048_tokens_2.5bpw"),
     "cfg1": dict(hidden=4096, ffn=0, tokens=2048, spread=1.0, bpw=3.0, dtype="f16",
                  workload="single_linear_4096x4096_2048_tokens_3.0bpw"),
+    # config 2 with 32768 tokens per input: small enough for an ncu capture, inputs still > L2
+    "cfg2_32k": dict(hidden=4096, ffn=11008, tokens=32768, spread=1.5, bpw=2.5, dtype="bf16",
+                     workload="llama_decoder_layer_7_matrices_4096x11008_32768_tokens_2.5bpw"),
     "tiny": dict(hidden=512, ffn=1024, tokens=4096, spread=1.5, bpw=2.5, dtype="bf16",
                  workload="tiny_decoder_layer_512x1024_4096_tokens_2.5bpw"),
 }
@@ -432,7 +435,10 @@ def run_ours(args, cfg):
     # ---- end to end: pinned host buffers in, packed buffers out ------------------------------
     e2e = None
     need = job.h2d_bytes()
-    if mem_available_bytes() > 3 * need * max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world))):
+    if args.no_e2e:
+        e2e = {"value": None, "unit": "rows/s", "h2d_bytes_per_step": need * world, "d2h_bytes_per_step": 0,
+               "note": "skipped (--no-e2e)"}
+    elif mem_available_bytes() > 3 * need * max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world))):
         job.pin_host_copies()
         job.step(from_host=True, to_host=True)  # warm-up of the copy path
         sync_all()
@@ -501,6 +507,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     if args.impl == "reference":

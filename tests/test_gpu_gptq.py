@@ -167,7 +167,7 @@ def test_gptq_block_entry_point_matches_driver():
     from hi2_b200.hessian import encode_rows_gptq
 
     w, d, u, _, _ = correlated_layer(37, 448, 77)
-    w, d, u = w.to(DEV), d.to(DEV), u.to(DEV)
+    w, d, u = w.to(DEV), d.to(DEV), u.to(DEV).contiguous()  # the entry point takes raw addresses
     ref = encode_rows_gptq(w, d, u, 2, 32, "normal")
     cfg = EFFORT["normal"]
     n, k = w.shape
