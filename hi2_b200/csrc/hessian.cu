@@ -25,6 +25,8 @@
 // fp32 FMA product of gemm.cuh.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "gemm.cuh"
 
 namespace hi2 {
@@ -493,4 +495,111 @@ extern "C" int hi2_hessian_kernel_info(int64_t* out) {
   out[3] = a.maxThreadsPerBlock, out[4] = blocks, out[5] = (int64_t)TC_SMEM, out[6] = TC_THREADS;
   cudaGetLastError();
   return HI2_OK;
+}
+
+// --------------------------------------------------------------------------------------------
+// Second moment without any allocation: the item tiles live in a fixed device array.
+//
+// Some callers cannot allocate device memory at the point where calibration statistics are
+// taken: a forward hook that runs while another framework's caching allocator owns the device
+// (an allocation there can synchronise or fragment the host framework's pool), a thread that
+// must not call into the CUDA allocator because a stream capture is in progress elsewhere in
+// the process, or an embedding whose memory budget was fixed up front.  For them the item tiles
+// of the tensor-core kernel are kept in g_static_tiles below: 64 MiB that every GPU loading the
+// library holds until the process exits.  That bounds the problem: tiles(k) * 128 KiB must fit,
+// which admits K up to 5632 (K = 4096 needs 34 MiB); the token split is reduced until the items
+// fit, so very few tokens per item are never needed.
+//
+// g_static_tiles is a device symbol: in host code its name is only a handle.  The address the
+// kernels receive comes from cudaGetSymbolAddress, looked up once per device with that device
+// current (first call on the device; make that call before any stream capture begins).  Every
+// call shares the array and the array keeps the previous call's tiles: each call overwrites all
+// tiles it later reads, and clears the caller's status word.  Two calls that overlap on the GPU
+// (different streams, or different host threads on one device) race on the array.
+// --------------------------------------------------------------------------------------------
+namespace hi2 {
+namespace {
+
+constexpr size_t STATIC_TILE_BYTES = (size_t)64 << 20;
+constexpr int STATIC_MAX_TILES = (int)(STATIC_TILE_BYTES / (TILE_ELEMS * sizeof(float)));  // 512
+constexpr int MAX_DEVICES = 64;
+
+static __device__ __align__(256) float g_static_tiles[STATIC_TILE_BYTES / sizeof(float)];
+
+float* static_tiles_address(int device) {
+  static float* cache[MAX_DEVICES] = {nullptr};
+  static std::mutex lock;
+  if (device < 0 || device >= MAX_DEVICES) return nullptr;
+  std::lock_guard<std::mutex> guard(lock);
+  if (cache[device] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_tiles) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    cache[device] = p;
+  }
+  return cache[device];
+}
+
+}  // namespace
+}  // namespace hi2
+
+extern "C" int hi2_hessian_accumulate_noalloc(const void* x, int dtype, int64_t tokens, int64_t k,
+                                              float* s, int32_t* status, void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(k > 0 && k % 16 == 0, "hessian_accumulate_noalloc: k must be a positive multiple of 16");
+  HI2_REQUIRE(dtype == HI2_BF16 || dtype == HI2_F16,
+              "hessian_accumulate_noalloc: activations must be bf16 or fp16");
+  HI2_REQUIRE(tokens >= 256 && k >= 256,
+              "hessian_accumulate_noalloc: needs at least 256 tokens and 256 columns");
+  HI2_REQUIRE(x && s && status, "hessian_accumulate_noalloc: null pointer");
+  HI2_REQUIRE(aligned16(x) && aligned16(s), "hessian_accumulate_noalloc: x and s must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  TcPlan pl = plan_tc(tokens, k);
+  if (pl.tiles > STATIC_MAX_TILES) {
+    set_error("hessian_accumulate_noalloc: k = %lld needs %d tiles of 128 KiB, the fixed scratch holds %d "
+              "(k <= 5632); use hi2_hessian_accumulate with a workspace",
+              (long long)k, pl.tiles, STATIC_MAX_TILES);
+    return HI2_ERR_WORKSPACE;
+  }
+  if (pl.splits > STATIC_MAX_TILES / pl.tiles) pl.splits = STATIC_MAX_TILES / pl.tiles;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return fail(HI2_ERR_LAUNCH, "hessian_accumulate_noalloc: no device");
+  float* tiles = static_tiles_address(device);
+  if (tiles == nullptr)
+    return fail(HI2_ERR_LAUNCH, "hessian_accumulate_noalloc: cudaGetSymbolAddress failed for the scratch array");
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr)
+    return fail(HI2_ERR_DRIVER, "hessian_accumulate_noalloc: cuTensorMapEncodeTiled unavailable");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)tokens};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  const cuuint32_t box[2] = {64, BKT};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&map, dtype == HI2_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("hessian_accumulate_noalloc: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return HI2_ERR_DRIVER;
+  }
+  if (cudaFuncSetAttribute(hessian_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM) !=
+      cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "hessian_accumulate_noalloc: cannot reserve shared memory");
+  if (cudaMemsetAsync(status, 0, sizeof(int32_t), st) != cudaSuccess)  // must start at zero
+    return fail(HI2_ERR_LAUNCH, "hessian_accumulate_noalloc: memset failed");
+  TcParams p;
+  p.scratch = tiles, p.status = reinterpret_cast<int*>(status), p.k = k, p.kblocks = pl.kblocks;
+  p.splits = pl.splits, p.tiles = pl.tiles, p.njb = pl.njb, p.fmt = dtype == HI2_BF16 ? 1 : 0;
+  const int items = pl.tiles * pl.splits;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  hessian_tc_kernel<<<items < sms ? items : sms, TC_THREADS, TC_SMEM, st>>>(map, p);
+  int rc = check_launch("hessian_accumulate_noalloc (tcgen05)");
+  if (rc != HI2_OK) return rc;
+  dim3 rgrid((unsigned)ceil_div(k, 256), (unsigned)k);
+  hessian_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, pl.splits, pl.tiles, pl.njb, k, s);
+  return check_launch("hessian_accumulate_noalloc (reduce)");
 }

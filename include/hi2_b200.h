@@ -153,6 +153,19 @@ int hi2_hessian_accumulate(const void* x, int dtype, int64_t tokens, int64_t k, 
  * to *status_host (synchronises with the device).  No counterpart in the reference. */
 int hi2_hessian_status(const void* workspace, int* status_host);
 
+/* No counterpart in the reference.  The second moment for callers that cannot allocate device
+ * memory where statistics are taken (a hook running inside another framework's allocator, a
+ * process with a stream capture in flight, a fixed memory budget): same result as
+ * hi2_hessian_accumulate on the tensor-core path, but the item tiles live in a 64 MiB device
+ * array inside the library instead of a caller workspace, and nothing is allocated or freed.
+ * Limits: dtype F16/BF16, tokens >= 256, 256 <= k <= 5632 (more returns HI2_ERR_WORKSPACE).
+ * *status (device int32, caller-owned output) is cleared by the call and receives
+ * HI2_ERR_TIMEOUT if a bounded device-side wait ran out.  The first call on a device looks up
+ * the array's address (cudaGetSymbolAddress): make it before any stream capture.  All calls
+ * share the array, so calls that overlap on the GPU race. */
+int hi2_hessian_accumulate_noalloc(const void* x, int dtype, int64_t tokens, int64_t k, float* s,
+                                   int32_t* status, void* stream);
+
 /* hi2/stats.py:27-33 ColumnStats.update, taken from the second moment: g [k/16, 16, 16] fp64
  * += the 16x16 diagonal blocks of s. */
 int hi2_group_moments(const float* s, int64_t k, double* g, void* stream);
