@@ -7,12 +7,14 @@ status that is turned into an exception here.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 
 import torch
 
-LIB_PATH = Path(__file__).resolve().parent / "libhi2_b200.so"
+# HI2_B200_LIB points at another build of the same library (kernel experiments)
+LIB_PATH = Path(os.environ.get("HI2_B200_LIB") or Path(__file__).resolve().parent / "libhi2_b200.so")
 
 OK, ERR_ARG, ERR_LAUNCH, ERR_NOT_PD, ERR_TIMEOUT, ERR_CODE_RANGE, ERR_WORKSPACE, ERR_DRIVER = range(8)
 F32, F64, F16, BF16 = range(4)
@@ -41,6 +43,13 @@ SIGNATURES = {
         _I,
         [_P, _L, _L, _P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P],
     ),
+    "hi2_gptq_round_tc": (
+        _I,
+        [_P, _L, _L, _P, _P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P],
+    ),
+    "hi2_gptq_lazy_update_tc": (_I, [_P, _L, _L, _L, _P, _P, _P, _P]),
+    "hi2_split_tf32_transposed": (_I, [_P, _P, _P, _L, _L, _P]),
+    "hi2_split_tf32": (_I, [_P, _P, _P, _L, _P]),
     "hi2_ladder_sse": (_I, [_P, _P, _L, _P, _P, _P, _L, _L, _L, _I, _P, _P]),
     "hi2_refine_block": (_I, [_P, _I, _P, _P, _P, _P, _P, _L, _L, _L, _P, _P]),
     "hi2_gemm_f32": (_I, [_I, _I, _L, _L, _L, _F, _P, _L, _P, _L, _F, _P, _L, _P]),

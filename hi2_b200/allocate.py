@@ -56,7 +56,7 @@ class _Flat:
         off = 0
         for t in tables:
             r, k = t.shape
-            scale = sens.get(t.name, 1.0) / max(t.energy, 1e-30)
+            scale = sens.get(t.name, 1.0) / max(float(t.energy), 1e-30)
             # fp32 product with the scalar rounded to fp32 first, then widened: what
             # `scalar * float32_tensor` followed by `.double()` gives
             cost = (t.sse.to(dev, torch.float32) * scale).double()

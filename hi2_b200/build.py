@@ -26,6 +26,7 @@ SOURCES = [
     "pack.cu",
     "ladder.cu",
     "gptq.cu",
+    "lazy_tc.cu",
     "refine.cu",
     "sigma.cu",
     "cholinv.cu",

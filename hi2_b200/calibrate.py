@@ -48,7 +48,7 @@ class TensorTable:
     had: torch.Tensor  # uint8 [K/16]
     sse: torch.Tensor  # float32 [C, R] (on the device)
     candidates: list
-    energy: float
+    energy: float | torch.Tensor  # sum d * w^2; a 0-dim device tensor until someone reads it
     n_tokens: int
     col_scale: torch.Tensor | None = None  # fp16 [K]
 
@@ -110,7 +110,7 @@ def build_table(name: str, w: torch.Tensor, stats: ColumnStats | None, cfg: Conf
         if i == 0:
             energy = enc.energy
     return TensorTable(
-        name, (r, k), had.cpu(), torch.stack(sse), list(cfg.candidates), float(energy.sum()),
+        name, (r, k), had.cpu(), torch.stack(sse), list(cfg.candidates), energy.sum(),  # no sync here
         n_tokens if n_tokens is not None else (stats.n if stats else 0),
         None if s16 is None else s16.cpu(),
     )
@@ -138,14 +138,29 @@ def _factor_key(req: EncodeRequest, i: int):
     return sid, cs, t.had.cpu().numpy().tobytes()
 
 
-def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool = True) -> list[HI2Tensor]:
+def factor_for(sigma, sigma_n, col_scale, had, cfg: Config):
+    """Enqueue basis change and inverse factor of one shared input on the current stream.
+    Returns ``(d, job, hs)``: ladder weights ``diag(Hs)``, the :class:`FactorJob`, and ``Hs``."""
+    from .hessian import FactorJob, transform_sigma
+
+    if cfg.act_order:
+        raise NotImplementedError("prefactoring with act_order: let encode_many factorise")
+    hs, d = transform_sigma(sigma, col_scale, had, denom=float(max(sigma_n, 1)), return_diag=True)
+    return d, FactorJob(hs, cfg.damp), hs
+
+
+def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool = True,
+                factors: dict | None = None) -> list[HI2Tensor]:
     """Encode several tensors with their allocator picks (hi2/calibrate.py:297-424): all GPTQ
     candidate groups of all tensors go through one batched column loop; the Hessian transform
     and factorisation happen once per distinct input."""
     del ex
     from .hessian import GptqJob, encode_jobs_gptq, inverse_factor, transform_sigma
 
-    factors: dict = {}
+    # ``factors`` (optional): {sigma_id: (d, FactorJob, hs)} from :func:`factor_for`, started earlier
+    # on side streams so the factorisations overlap the tables
+    ready = factors or {}
+    factors = {}
     pieces: dict[int, list] = {}
     jobs, where, refine_with = [], [], []
     stored: dict[int, torch.Tensor] = {}
@@ -158,6 +173,11 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
         use_gptq = cfg.rounding == "gptq" and r.sigma is not None
         if use_gptq:
             fk = _factor_key(r, ri)
+            if fk not in factors and r.sigma_id in ready:
+                d, job, hs = ready[r.sigma_id]
+                u = job.result()
+                torch.cuda.current_stream(dev).wait_stream(job.stream)
+                factors[fk] = (d, u, None, hs if cfg.refine_passes else None)
             if fk not in factors:
                 hs, d = transform_sigma(r.sigma.to(dev), t.col_scale, had, denom=float(max(r.sigma_n, 1)),
                                         return_diag=True)

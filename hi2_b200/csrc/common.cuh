@@ -51,4 +51,40 @@ __device__ __forceinline__ float clamp_keep_nan(float v, float lo, float hi) {
 
 __device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
 
+// Division by a value that stays fixed over many quotients.  r is the correctly rounded
+// reciprocal; `fast` is false when b is outside a comfortable normal range or its significand is
+// all ones (the one case Markstein's correction step does not cover): then the IEEE division
+// is used, so both helpers below return exactly what __fdiv_rn would give.
+struct Recip {
+  float r;
+  bool fast;
+};
+__device__ __forceinline__ Recip make_recip(float b) {
+  const float ab = fabsf(b);
+  Recip rc;
+  rc.fast = ab > 1e-18f && ab < 1e18f && (__float_as_uint(b) & 0x7fffffu) != 0x7fffffu;
+  rc.r = __frcp_rn(b);
+  return rc;
+}
+
+// rintf(__fdiv_rn(a, b)) for results that the caller clamps to [0, 255].  a * r is within 2 ulp
+// of the quotient, so the two can round to different integers only when a * r lies within a
+// few ulp of a half-integer; those cases (about one in 10^4) take the IEEE division.  Beyond
+// 1024 a difference of one survives no clamp to a ladder of at most 256 levels.
+__device__ __forceinline__ float rint_div(float a, float b, Recip rc) {
+  if (!rc.fast) return rintf(__fdiv_rn(a, b));
+  const float t = a * rc.r;
+  float q = rintf(t);
+  if (fabsf(fabsf(t - q) - 0.5f) < 2.5e-4f && fabsf(t) < 1024.0f) q = rintf(__fdiv_rn(a, b));
+  return q;
+}
+
+// __fdiv_rn(a, b): q0 = a * r is a faithful quotient, one fused correction step makes it the
+// correctly rounded one (Markstein).  a is assumed finite and not denormal-small.
+__device__ __forceinline__ float div_by(float a, float b, Recip rc) {
+  if (!rc.fast) return __fdiv_rn(a, b);
+  const float q0 = a * rc.r;
+  return fmaf(fmaf(-q0, b, a), rc.r, q0);
+}
+
 }  // namespace hi2

@@ -14,6 +14,12 @@
 #include "gemm.cuh"
 
 namespace hi2 {
+
+int launch_lazy_tc(float* wc, int64_t n_rows, int64_t k, int64_t i1, const float* err_hi,
+                   const float* err_lo, const float* u_hi, const float* u_lo, int* status,
+                   cudaStream_t stream);
+int launch_split_tf32(const float* x, float* hi, float* lo, int64_t n, cudaStream_t stream);
+
 namespace {
 
 constexpr int LMAX = 128;
@@ -46,6 +52,18 @@ gptq_block_kernel(const float* __restrict__ wc, int64_t n_rows, int64_t k, int64
   }
   float q_keep[4] = {0.f, 0.f, 0.f, 0.f}, e_keep[4] = {0.f, 0.f, 0.f, 0.f},
         col_keep[4] = {0.f, 0.f, 0.f, 0.f};
+  // Reciprocals of the two divisors of a column, taken off the dependent chain: the ladder
+  // step of the column's block and the diagonal entry of U.  rint_div / div_by give exactly the
+  // IEEE quotients the reference forms.
+  Recip rc_st[4], rc_u[4];
+  float udiag[4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const int64_t j = i1 + c0 + s;
+    udiag[s] = mine ? u[j * k + j] : 1.0f;
+    rc_u[s] = make_recip(udiag[s]);
+    rc_st[s] = make_recip((st_c[s] == 0.0f) ? 1.0f : st_c[s]);
+  }
 
   // rows i1 .. i1+len-1 of U, this lane's four columns
   const float* urow = u + i1 * k + i1 + c0;
@@ -72,12 +90,12 @@ gptq_block_kernel(const float* __restrict__ wc, int64_t n_rows, int64_t k, int64
       // every lane evaluates slot s of its own quad; only the owner's result is used
       const float col = w[s], lo_j = lo_c[s], st_j = st_c[s];
       const float safe = (st_j == 0.0f) ? 1.0f : st_j;
-      float q = rintf(__fdiv_rn(col - lo_j, safe));
+      float q = rint_div(col - lo_j, safe, rc_st[s]);
       q = (q < 0.0f) ? 0.0f : q;
       q = (q > nm) ? nm : q;
       if (st_j == 0.0f) q = 0.0f;
       const float wq = round_f16(lo_j + q * st_j);
-      const float e_own = __fdiv_rn(col - wq, us[s]);
+      const float e_own = div_by(col - wq, udiag[s], rc_u[s]);
       const float e = __shfl_sync(0xffffffffu, e_own, owner);
       if (lane == owner) q_keep[s] = q, e_keep[s] = e_own, col_keep[s] = col;
 #pragma unroll
@@ -188,6 +206,61 @@ extern "C" int hi2_gptq_round(float* wc, int64_t n_rows, int64_t k, float* err1,
       if (r1 <= r0) continue;
       rc = launch_lazy(wc + r0 * k, r1 - r0, k, i1, i2, err1 + r0 * len,
                        reinterpret_cast<const float*>(u_host[un]), s);
+      if (rc != HI2_OK) return rc;
+    }
+  }
+  return HI2_OK;
+}
+
+extern "C" int hi2_gptq_lazy_update_tc(float* wc, int64_t n_rows, int64_t k, int64_t i1,
+                                       const float* err_split, const float* u_split, int32_t* status,
+                                       void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(k > 0 && k % 4 == 0 && i1 >= 0 && i1 % 4 == 0 && i1 + LMAX <= k,
+              "gptq_lazy_update_tc: bad block range");
+  if (n_rows == 0 || i1 + LMAX == k) return HI2_OK;
+  HI2_REQUIRE(wc && err_split && u_split && status, "gptq_lazy_update_tc: null pointer");
+  HI2_REQUIRE(aligned16(wc) && aligned16(err_split) && aligned16(u_split), "gptq_lazy_update_tc: alignment");
+  return launch_lazy_tc(wc, n_rows, k, i1, err_split, err_split + n_rows * LMAX, u_split, u_split + k * k,
+                        reinterpret_cast<int*>(status), static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hi2_gptq_round_tc(float* wc, int64_t n_rows, int64_t k, float* err1, float* err_split,
+                                 uint8_t* codes, const float* lo, const float* st, int64_t ldp,
+                                 const int32_t* row_grp, const int64_t* u_ptrs, const int32_t* blk,
+                                 const float* nmax, float* comp, int n_units,
+                                 const int64_t* unit_rows_host, const int64_t* u_split_host,
+                                 int32_t* status, void* stream) {
+  using namespace hi2;
+  if (n_rows == 0) return HI2_OK;
+  HI2_REQUIRE(n_units >= 1 && unit_rows_host && u_split_host, "gptq_round_tc: unit table missing");
+  HI2_REQUIRE(unit_rows_host[0] == 0 && unit_rows_host[n_units] == n_rows,
+              "gptq_round_tc: units must cover the rows");
+  HI2_REQUIRE(err_split && status && aligned16(err_split), "gptq_round_tc: scratch missing or unaligned");
+  HI2_REQUIRE(k % 4 == 0, "gptq_round_tc: k must be a multiple of 4");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(status, 0, sizeof(int32_t), s) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "gptq_round_tc: memset failed");
+  float* err_hi = err_split;
+  float* err_lo = err_split + n_rows * LMAX;
+  for (int64_t i1 = 0; i1 < k; i1 += LMAX) {
+    const int64_t i2 = (i1 + LMAX < k) ? i1 + LMAX : k;
+    const int len = (int)(i2 - i1);
+    int rc = check_block_args(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs,
+                              blk, nmax, comp);
+    if (rc != HI2_OK) return rc;
+    rc = launch_block(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs, blk, nmax,
+                      comp, s);
+    if (rc != HI2_OK) return rc;
+    if (i2 == k) break;  // a block shorter than 128 columns is always the last one
+    rc = launch_split_tf32(err1, err_hi, err_lo, n_rows * LMAX, s);
+    if (rc != HI2_OK) return rc;
+    for (int un = 0; un < n_units; ++un) {
+      const int64_t r0 = unit_rows_host[un], r1 = unit_rows_host[un + 1];
+      if (r1 <= r0) continue;
+      const float* u_hi = reinterpret_cast<const float*>(u_split_host[un]);
+      rc = launch_lazy_tc(wc + r0 * k, r1 - r0, k, i1, err_hi + r0 * LMAX, err_lo + r0 * LMAX, u_hi,
+                          u_hi + k * k, reinterpret_cast<int*>(status), s);
       if (rc != HI2_OK) return rc;
     }
   }

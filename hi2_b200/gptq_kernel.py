@@ -92,3 +92,48 @@ def gptq_round(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp, unit_r
         _lib.ptr(comp), len(unit_u), _lib.host_i64(unit_rows),
         _lib.host_i64([u.data_ptr() for u in unit_u]), _lib.stream(dev),
     )
+
+
+def split_tf32(x: torch.Tensor) -> torch.Tensor:
+    """``[2, *x.shape]`` fp32: the TF32 parts ``hi = tf32(x)`` and ``lo = tf32(x - hi)`` (round to
+    nearest), the operand form of the tensor-core trailing update."""
+    dev = _lib.need_cuda(x)
+    _check(x, torch.float32, "x")
+    out = torch.empty(2, *x.shape, dtype=torch.float32, device=dev)
+    _lib.call("hi2_split_tf32", _lib.ptr(x), _lib.ptr(out[0]), _lib.ptr(out[1]), x.numel(), _lib.stream(dev))
+    return out
+
+
+def split_tf32_transposed(x: torch.Tensor) -> torch.Tensor:
+    """``[2, cols, rows]`` fp32: the TF32 parts of ``x^T`` for ``x [rows, cols]`` (the form in which
+    the tensor-core trailing update takes the factor)."""
+    dev = _lib.need_cuda(x)
+    _check(x, torch.float32, "x")
+    rows, cols = x.shape
+    out = torch.empty(2, cols, rows, dtype=torch.float32, device=dev)
+    _lib.call("hi2_split_tf32_transposed", _lib.ptr(x), _lib.ptr(out[0]), _lib.ptr(out[1]), rows, cols,
+              _lib.stream(dev))
+    return out
+
+
+def gptq_round_tc(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp, unit_rows, unit_u_split):
+    """:func:`gptq_round` with the trailing update on the tensor cores (3 x TF32, fp32-grade).
+    ``unit_u_split`` holds :func:`split_tf32_transposed` of each unit's factor.  Returns the device status
+    word (int32 tensor): non-zero when a bounded device-side wait ran out."""
+    dev = _lib.need_cuda(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp, *unit_u_split)
+    n, k = wc.shape
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    if n == 0:
+        return status
+    err_split = torch.empty(2, n, BLOCK_COLUMNS, dtype=torch.float32, device=dev)
+    for u in unit_u_split:
+        _check(u, torch.float32, "u_split")
+        if u.shape != (2, k, k):
+            raise ValueError("gptq_round_tc: a split factor must be [2, K, K]")
+    _lib.call(
+        "hi2_gptq_round_tc", _lib.ptr(wc), n, k, _lib.ptr(err1), _lib.ptr(err_split), _lib.ptr(codes),
+        _lib.ptr(lo), _lib.ptr(st), lo.shape[1], _lib.ptr(row_grp), _lib.ptr(u_ptrs), _lib.ptr(blk),
+        _lib.ptr(nmax), _lib.ptr(comp), len(unit_u_split), _lib.host_i64(unit_rows),
+        _lib.host_i64([u.data_ptr() for u in unit_u_split]), _lib.ptr(status), _lib.stream(dev),
+    )
+    return status

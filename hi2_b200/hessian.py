@@ -117,33 +117,58 @@ def transform_sigma(sigma: torch.Tensor, col_scale: torch.Tensor | None, had: to
     return (hs, diag) if return_diag else hs
 
 
+class FactorJob:
+    """One damped inverse factor in flight.  ``FactorJob(hs, damp)`` enqueues the first attempt
+    on the current stream (its own scratch, so several jobs may run on different streams at
+    once) and returns; :meth:`result` waits for that attempt and, in the rare case of a
+    non-positive pivot, repeats with ten times the damping as hi2/hessian.py:78-86 does."""
+
+    def __init__(self, hs: torch.Tensor, damp: float = 0.01, workspace: torch.Tensor | None = None):
+        self.dev = _lib.need_cuda(hs)
+        self.k = hs.shape[0]
+        h = hs if hs.dtype == torch.float32 else hs.float()
+        self.h = h.contiguous()
+        self.damp = damp
+        self.mean = self.h.diagonal().mean().clamp_min(1e-12)
+        need = _lib.load().hi2_inverse_factor_workspace_bytes(self.k)
+        self.ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=self.dev)
+        if self.ws.numel() < need:
+            raise ValueError("inverse factor workspace too small")
+        self.u = torch.empty(self.k, self.k, dtype=torch.float32, device=self.dev)
+        self.info = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.stream = torch.cuda.current_stream(self.dev)
+        self.attempt = 0
+        self._launch()
+
+    def _launch(self) -> None:
+        self.lam = (self.damp * self.mean * 10**self.attempt).to(torch.float32).reshape(1)
+        self.info.zero_()
+        _lib.call(
+            "hi2_inverse_factor", _lib.ptr(self.h), _lib.ptr(self.lam), self.k, _lib.ptr(self.u),
+            _lib.ptr(self.ws), self.ws.numel(), _lib.ptr(self.info), _lib.stream(self.dev),
+        )
+
+    def result(self) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            while True:
+                last = int(self.info.item())
+                if last == 0 and bool(torch.isfinite(self.u.diagonal()).all()):
+                    self.ws = None
+                    return self.u
+                self.attempt += 1
+                if self.attempt >= 6:
+                    raise RuntimeError(
+                        f"Hessian is not factorisable even with heavy damping: non-positive pivot {last - 1}"
+                    )
+                self._launch()
+
+
 def inverse_factor(hs: torch.Tensor, damp: float = 0.01) -> torch.Tensor:
     """Upper Cholesky factor ``U`` of ``(Hs + damp * mean(diag) I)^-1``; the damping is raised
     tenfold (up to five times) when the factorisation meets a non-positive pivot."""
     dev = _lib.need_cuda(hs)
-    k = hs.shape[0]
-    h = hs if hs.dtype == torch.float32 else hs.float()
-    h = h.contiguous()
-    mean = h.diagonal().mean().clamp_min(1e-12)
-    lib = _lib.load()
-    need = lib.hi2_inverse_factor_workspace_bytes(k)
-    ws = _workspace(dev, need)
-    u = torch.empty(k, k, dtype=torch.float32, device=dev)
-    info = torch.zeros(1, dtype=torch.int32, device=dev)
-    last = 0
-    for attempt in range(6):
-        lam = (damp * mean * 10**attempt).to(torch.float32).reshape(1)
-        info.zero_()
-        _lib.call(
-            "hi2_inverse_factor", _lib.ptr(h), _lib.ptr(lam), k, _lib.ptr(u), _lib.ptr(ws),
-            ws.numel(), _lib.ptr(info), _lib.stream(dev),
-        )
-        last = int(info.item())
-        if last == 0 and bool(torch.isfinite(u.diagonal()).all()):
-            return u
-    raise RuntimeError(
-        f"Hessian is not factorisable even with heavy damping: non-positive pivot {last - 1}"
-    )
+    need = _lib.load().hi2_inverse_factor_workspace_bytes(hs.shape[0])
+    return FactorJob(hs, damp, _workspace(dev, need)).result()
 
 
 @dataclass
@@ -195,8 +220,13 @@ def _prepare(ji: int, job: GptqJob, s: int, step_rows: int, effort: str) -> _Uni
                  (cols // job.block).to(torch.int32))
 
 
-def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool) -> None:
-    """All ``units`` (same K, same device) through one enqueue of the column loop."""
+# factors at least this wide take the tensor-core trailing update (below it the FMA product wins)
+TC_MIN_K = 512
+
+
+def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool, splits: dict) -> None:
+    """All ``units`` (same K, same device) through one enqueue of the column loop.  ``splits``
+    caches the TF32 split of each distinct factor over one :func:`encode_jobs_gptq` call."""
     dev, k = units[0].wc.device, units[0].wc.shape[1]
     sizes = [x.rows for x in units]
     total = sum(sizes)
@@ -219,7 +249,21 @@ def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool) -> No
     codes = torch.empty(total, k, dtype=torch.uint8, device=dev)
     comp = torch.empty(total, k, dtype=torch.float32, device=dev) if want_comp else None
     err1 = torch.empty(total, BLOCK_COLUMNS, dtype=torch.float32, device=dev)
-    gptq_kernel.gptq_round(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp, offs, us)
+    # INT8 ladders are 64 times finer than INT2: the 3 x TF32 update (error ~1e-6 of |err||U|, ten
+    # times an fp32 FMA chain) moves ~0.1 % of INT8 codes, so rows with 256 levels keep the FMA
+    # product; for INT2 / INT4 the codes are the same
+    if k >= TC_MIN_K and all(jobs[x.job].nbits <= 4 for x in units):
+        parts = []
+        for u in us:
+            if u.data_ptr() not in splits:
+                splits[u.data_ptr()] = (u, gptq_kernel.split_tf32_transposed(u))  # keeps u alive with its split
+            parts.append(splits[u.data_ptr()][1])
+        status = gptq_kernel.gptq_round_tc(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp,
+                                           offs, parts)
+        if int(status.item()):
+            raise RuntimeError("gptq trailing update: a bounded device-side wait ran out")
+    else:
+        gptq_kernel.gptq_round(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp, offs, us)
     for x, o, n in zip(units, offs, sizes):
         x.codes = codes[o : o + n]
         x.comp = None if comp is None else comp[o : o + n]
@@ -281,9 +325,10 @@ def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str |
         if bl[-1] and sum(y.wc.numel() for y in bl[-1]) + x.wc.numel() > BATCH_ELEMS:
             bl.append([])
         bl[-1].append(x)
+    splits: dict = {}
     for bl in batches.values():
         for batch in bl:
-            _round_units(batch, jobs, comp)
+            _round_units(batch, jobs, comp, splits)
             for x in batch:
                 x.wc = None
     per_job: list[list[Encoded]] = [[] for _ in jobs]

@@ -53,27 +53,62 @@ def accumulate(inputs: dict, device, into: dict | None = None) -> dict:
     return out
 
 
-def finish_statistics(shared: dict, cfg: Config) -> None:
-    """Group moments, smoothing vector and rotation flags of every input (after all tokens, and
-    after any cross-rank reduction of the second moments)."""
+def finish_statistics(shared: dict, cfg: Config, only: str | None = None) -> None:
+    """Group moments, smoothing vector and rotation flags of every input, or of input ``only``
+    (after all tokens, and after any cross-rank reduction of the second moments)."""
     for s in shared.values():
+        if only is not None and s.name != only:
+            continue
         s.moments = ColumnStats.from_second_moment(s.hessian.S, s.hessian.n)
         flags = torch.ones(s.k // GROUP, dtype=torch.uint8) if cfg.rotation == "on" else torch.zeros(
             s.k // GROUP, dtype=torch.uint8)
         s.transform = (smoothing_scale(s.moments, cfg.smooth), flags)
 
 
-def tabulate(weights: dict, plan: LayerPlan, shared: dict, cfg: Config) -> dict:
-    """Error tables of every weight ``{name: [R, K] tensor}``."""
-    tables = {}
+_side_streams: dict = {}
+
+
+def _side_stream(device, i: int) -> torch.cuda.Stream:
+    """Side streams are made once per device and reused: the caching allocator keeps a pool per
+    stream, so a fresh stream every step would strand the factorisation scratch of the last one."""
+    key = (torch.device(device).index, i)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device)
+    return _side_streams[key]
+
+
+def start_factors(shared: dict, cfg: Config, device, only: str | None = None, into: dict | None = None) -> dict:
+    """Basis change and inverse factor of every input (or of input ``only``), each on a stream of
+    its own, started now so they run beside the tables (which do not need them).  Pass the result
+    to :func:`encode`."""
+    from .calibrate import factor_for
+
+    main = torch.cuda.current_stream(device)
+    out = into if into is not None else {}
+    for i, s in enumerate(shared.values()):
+        if only is not None and s.name != only:
+            continue
+        side = _side_stream(device, i)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            out[s.name] = factor_for(s.hessian.S, s.hessian.n, s.transform[0], s.transform[1], cfg)
+    return out
+
+
+def tabulate(weights: dict, plan: LayerPlan, shared: dict, cfg: Config, only: str | None = None,
+             into: dict | None = None) -> dict:
+    """Error tables of every weight ``{name: [R, K] tensor}`` (or of those reading input ``only``)."""
+    tables = into if into is not None else {}
     for name, w in weights.items():
+        if only is not None and plan.reads[name] != only:
+            continue
         s = shared[plan.reads[name]]
         tables[name] = build_table(name, w, s.moments, cfg, transform=s.transform)
     return tables
 
 
 def encode(weights: dict, plan: LayerPlan, shared: dict, tables: dict, picks: dict, cfg: Config,
-           to_host: bool = True) -> dict:
+           to_host: bool = True, factors: dict | None = None) -> dict:
     """Packed ``HI2Tensor`` of every weight for the allocator's ``picks``."""
     reqs, names = [], []
     for name, w in weights.items():
@@ -81,7 +116,7 @@ def encode(weights: dict, plan: LayerPlan, shared: dict, tables: dict, picks: di
         reqs.append(EncodeRequest(w, s.moments, tables[name], picks[name], sigma=s.hessian.S,
                                   sigma_id=s.name, sigma_n=s.hessian.n))
         names.append(name)
-    out = encode_many(reqs, cfg, to_host=to_host)
+    out = encode_many(reqs, cfg, to_host=to_host, factors=factors)
     return dict(zip(names, out))
 
 
@@ -99,5 +134,5 @@ def llama_shapes(hidden: int = 4096, ffn: int = 11008) -> tuple[dict, dict]:
     return w, x
 
 
-__all__ = ["SharedInput", "LayerPlan", "accumulate", "finish_statistics", "tabulate", "encode",
+__all__ = ["SharedInput", "LayerPlan", "accumulate", "finish_statistics", "start_factors", "tabulate", "encode",
            "llama_plan", "llama_shapes", "Config", "TensorTable", "HI2Tensor"]

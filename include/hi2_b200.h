@@ -118,6 +118,31 @@ int hi2_gptq_round(float* wc, int64_t n_rows, int64_t k, float* err1, uint8_t* c
                    int n_units, const int64_t* unit_rows_host, const int64_t* u_host,
                    void* stream);
 
+/* The same column loop with the trailing update on the tensor cores: every operand split into
+ * two TF32 numbers (hi + lo), three tcgen05 products with fp32 accumulation, accuracy of an fp32
+ * FMA chain.  u_split_host[u] is the device address of a [2, k, k] fp32 array holding the hi and
+ * lo parts of the TRANSPOSE of unit u's factor (hi2_split_tf32_transposed); err_split is caller scratch [2, n_rows, 128];
+ * *status (device int32) is cleared and receives HI2_ERR_TIMEOUT if a bounded wait ran out. */
+int hi2_gptq_round_tc(float* wc, int64_t n_rows, int64_t k, float* err1, float* err_split,
+                      uint8_t* codes, const float* lo, const float* st, int64_t ldp,
+                      const int32_t* row_grp, const int64_t* u_ptrs, const int32_t* blk,
+                      const float* nmax, float* comp, int n_units, const int64_t* unit_rows_host,
+                      const int64_t* u_split_host, int32_t* status, void* stream);
+
+/* One trailing update on the tensor cores: wc[:, i1+128:] -= err @ u[i1:i1+128, i1+128:] with
+ * err_split [2, n_rows, 128] the TF32 parts of err and u_split [2, k, k] those of u^T.  *status is NOT
+ * cleared here (the caller zeroes it once). */
+int hi2_gptq_lazy_update_tc(float* wc, int64_t n_rows, int64_t k, int64_t i1, const float* err_split,
+                            const float* u_split, int32_t* status, void* stream);
+
+/* x = hi + lo with hi = tf32(x), lo = tf32(x - hi), round to nearest; n a multiple of 4.  Prepares
+ * the operands of hi2_gptq_round_tc.  No counterpart in the reference. */
+int hi2_split_tf32(const float* x, float* hi, float* lo, int64_t n, void* stream);
+/* The same split of x^T: x [rows, cols] -> hi, lo [cols, rows] (the factor operand of the
+ * tensor-core trailing update is kept transposed so that both operands are K-major). */
+int hi2_split_tf32_transposed(const float* x, float* hi, float* lo, int64_t rows, int64_t cols,
+                              void* stream);
+
 /* hi2/hessian.py:331-338 (_finish): sse[r] = sum_j d[j] * (fp16(lo + code*step) - w[r, j])^2
  * with the decoded ladders lo/st [n_rows, ldp] of block size `block`. */
 int hi2_ladder_sse(const uint8_t* codes, const float* w, int64_t ldw, const float* d,

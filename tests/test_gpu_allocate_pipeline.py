@@ -102,7 +102,7 @@ def test_layer_end_to_end_against_oracle():
     stats = ColumnStats.from_second_moment(h.S, h.n)
     table = build_table("w", w.to(DEV), stats, cfg)
     assert rel_close(table.col_scale.float(), ref["s16"].float(), 1e-3)
-    assert abs(table.energy - ref["table"].energy) <= 1e-3 * ref["table"].energy
+    assert abs(float(table.energy) - ref["table"].energy) <= 1e-3 * ref["table"].energy
     tot_ref = ref["table"].sse.sum(1)
     assert rel_close(table.sse.sum(1), tot_ref, 2e-3)
     alloc = allocate_global([table], 3.0)
