@@ -146,7 +146,11 @@ def factor_for(sigma, sigma_n, col_scale, had, cfg: Config):
     if cfg.act_order:
         raise NotImplementedError("prefactoring with act_order: let encode_many factorise")
     hs, d = transform_sigma(sigma, col_scale, had, denom=float(max(sigma_n, 1)), return_diag=True)
-    return d, FactorJob(hs, cfg.damp), hs
+    d_ready = torch.cuda.Event()
+    d_ready.record()
+    job = FactorJob(hs, cfg.damp)
+    job.d_ready = d_ready
+    return d, job, hs
 
 
 def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool = True,
@@ -161,6 +165,7 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
     # on side streams so the factorisations overlap the tables
     ready = factors or {}
     factors = {}
+    waits: dict = {}
     pieces: dict[int, list] = {}
     jobs, where, refine_with = [], [], []
     stored: dict[int, torch.Tensor] = {}
@@ -174,10 +179,12 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
         if use_gptq:
             fk = _factor_key(r, ri)
             if fk not in factors and r.sigma_id in ready:
+                # started earlier on a side stream: order after it on the device, never on the host,
+                # so the narrow matrices are rounded while the widest factor is still being computed
                 d, job, hs = ready[r.sigma_id]
-                u = job.result()
-                torch.cuda.current_stream(dev).wait_stream(job.stream)
-                factors[fk] = (d, u, None, hs if cfg.refine_passes else None)
+                torch.cuda.current_stream(dev).wait_event(job.d_ready)
+                factors[fk] = (d, job.first_attempt(), None, hs if cfg.refine_passes else None)
+                waits[fk] = job
             if fk not in factors:
                 hs, d = transform_sigma(r.sigma.to(dev), t.col_scale, had, denom=float(max(r.sigma_n, 1)),
                                         return_diag=True)
@@ -208,6 +215,13 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
                 out.append((rows, enc.codes, enc.params, enc.consts))
     want = any(reqs[ri].comp_out is not None for ri, _ in where)
     encs = encode_jobs_gptq(jobs, cfg.effort, comp=want) if jobs else []
+    if any(not job.succeeded() for job in waits.values()):
+        # a first attempt met a non-positive pivot: redo everything on the synchronous path, which
+        # retries with more damping (hi2/hessian.py:78-86)
+        return encode_many(reqs, cfg, to_host=to_host, factors=None)
+    if cfg.refine_passes:
+        for job in waits.values():
+            torch.cuda.current_stream().wait_event(job.done)
     if any(h is not None for h in refine_with):
         from .refine import refine_groups
 

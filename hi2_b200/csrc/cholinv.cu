@@ -50,51 +50,67 @@ reverse_store_kernel(const double* __restrict__ x, int64_t k, float* __restrict_
   u[idx] = (float)x[(k - 1 - i) * k + (k - 1 - j)];
 }
 
+// 1 / sqrt(v) in fp64 from the fp32 estimate and three Newton steps (the fp64 square root and
+// division are ~60-instruction sequences on the critical path of every column of a leaf; this
+// is ~15).  Outside fp32's normal range the plain expression is used.
+__device__ __forceinline__ double inv_sqrt(double v) {
+  if (!(v > 1e-30 && v < 1e30)) return 1.0 / sqrt(v);
+  double y = (double)rsqrtf((float)v);
+  const double h = 0.5 * v;
+#pragma unroll
+  for (int it = 0; it < 3; ++it) y = fma(y, fma(-h * y, y, 0.5), y);  // y += y * (0.5 - h y^2)
+  return y;
+}
+
 // Factorise the n x n (n <= 64) diagonal block at `off` (lower part of a, leading dim ld) and
-// write its inverse, zeros above the diagonal included, to the same place of x.
+// write its inverse, zeros above the diagonal included, to the same place of x.  One thread block:
+// 256 threads as a 16 x 16 grid for the trailing updates of the factorisation (two barriers per
+// column), then as 64 columns x 4 partial sums for the row-by-row triangular inverse (the four
+// partial sums of a column sit in adjacent lanes and meet by shuffle, one barrier per row).
 __global__ void __launch_bounds__(256)
 leaf_kernel(const double* __restrict__ a, double* __restrict__ x, int64_t ld, int64_t off, int n,
             int32_t* info) {
   extern __shared__ double leaf_smem[];
   double (*L)[LDL] = reinterpret_cast<double (*)[LDL]>(leaf_smem);
   double (*X)[LDL] = reinterpret_cast<double (*)[LDL]>(leaf_smem + NB * LDL);
-  const int tid = threadIdx.x;
+  __shared__ double inv_diag[NB];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const double* src = a + off * ld + off;
   for (int idx = tid; idx < NB * NB; idx += 256) {
-    const int i = idx / NB, j = idx % NB;
+    const int i = idx >> 6, j = idx & 63;
     L[i][j] = (i < n && j <= i) ? src[(int64_t)i * ld + j] : 0.0;
     X[i][j] = 0.0;
   }
   __syncthreads();
   for (int j = 0; j < n; ++j) {
-    double piv = L[j][j];
-    if (!(piv > 0.0)) {  // also catches NaN
+    double piv = L[j][j];  // final: every update of (j, j) was followed by a barrier
+    if (!(piv > 0.0)) {    // also catches NaN
       if (tid == 0) atomicCAS(info, 0, (int32_t)(off + j + 1));
       piv = 1.0;
     }
-    const double dj = sqrt(piv);
-    __syncthreads();  // everyone has read L[j][j]
-    for (int i = j + tid; i < n; i += 256) L[i][j] = (i == j) ? dj : L[i][j] / dj;
+    const double inv = inv_sqrt(piv);  // L[j][j] itself stays un-rooted; 1/sqrt is kept instead
+    if (tid == 0) inv_diag[j] = inv;
+    for (int i = j + 1 + tid; i < n; i += 256) L[i][j] *= inv;
     __syncthreads();
-    // trailing update of the lower part: (i, c) with j < c <= i < n
-    const int rem = n - j - 1;
-    for (int idx = tid; idx < rem * rem; idx += 256) {
-      const int i = j + 1 + idx / rem, c = j + 1 + idx % rem;
-      if (c <= i) L[i][c] = fma(-L[i][j], L[c][j], L[i][c]);
+    for (int i = j + 1 + ty; i < n; i += 16) {
+      const double lij = L[i][j];
+      for (int c = j + 1 + tx; c <= i; c += 16) L[i][c] = fma(-lij, L[c][j], L[i][c]);
     }
     __syncthreads();
   }
-  // X = L^-1 by forward substitution, one column per thread
-  if (tid < n) {
-    const int c = tid;
-    X[c][c] = 1.0 / L[c][c];
-    for (int i = c + 1; i < n; ++i) {
-      double acc = 0.0;
-      for (int q = c; q < i; ++q) acc = fma(L[i][q], X[q][c], acc);
-      X[i][c] = -acc / L[i][i];
-    }
-  }
+  // X = L^-1, row by row: X[i][c] = -(sum_{q=c}^{i-1} L[i][q] X[q][c]) / L[i][i], X[i][i] = 1 / L[i][i]
+  const int c = tid >> 2, part = tid & 3;
+  if (tid < n) X[tid][tid] = inv_diag[tid];
   __syncthreads();
+  for (int i = 1; i < n; ++i) {
+    double acc = 0.0;
+    if (c < i)
+      for (int q = c + part; q < i; q += 4) acc = fma(L[i][q], X[q][c], acc);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (part == 0 && c < i) X[i][c] = -acc * inv_diag[i];
+    __syncthreads();
+  }
   double* dst = x + off * ld + off;
   for (int idx = tid; idx < n * n; idx += 256) {
     const int i = idx / n, j = idx % n;
@@ -115,7 +131,7 @@ int product(bool trans_b, int64_t m, int64_t n, int64_t kk, double alpha, const 
   GemmArgs<double, double, double> p;
   p.m = m, p.n = n, p.kk = kk, p.alpha = alpha, p.beta = beta;
   p.a = a, p.lda = ld, p.b = b, p.ldb = ld, p.c = c, p.ldc = ld, p.flags = flags;
-  return launch_gemm<double, double, double, 8, 4, 16>(false, trans_b, p, stream, "inverse_factor");
+  return launch_gemm_async<double, 8, 4, 16>(false, trans_b, p, stream, "inverse_factor");
 }
 
 int factor(const Plan& pl, int64_t off, int64_t n) {

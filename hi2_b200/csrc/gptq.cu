@@ -5,7 +5,7 @@
 // that owns it; its scaled error reaches the other lanes with one shuffle and every lane
 // subtracts e * U[j, c] from its columns c > i.  Rows of U are read as one 128-bit load per lane
 // (a contiguous 512-byte line per warp, served from L1/L2 since every warp of the same factor
-// walks the same rows) and fetched four rows ahead of their use, so the dependent chain per
+// walks the same rows) and fetched two rows ahead of their use, so the dependent chain per
 // column is shuffle + ~10 arithmetic instructions.  Each product, sum and quotient is rounded
 // on its own (the library is built without FMA contraction) and wq is rounded to fp16 before the
 // error is formed, so given the same inputs the codes equal those of the column-by-column loop.
@@ -25,7 +25,8 @@ namespace {
 constexpr int LMAX = 128;
 constexpr int ROWS_PER_CTA = 8;
 
-__global__ void __launch_bounds__(ROWS_PER_CTA * 32)
+template <bool WITH_COMP>
+__global__ void __launch_bounds__(ROWS_PER_CTA * 32, 3)
 gptq_block_kernel(const float* __restrict__ wc, int64_t n_rows, int64_t k, int64_t i1, int len,
                   float* __restrict__ err1, uint8_t* __restrict__ codes,
                   const float* __restrict__ lo, const float* __restrict__ st, int64_t ldp,
@@ -65,28 +66,25 @@ gptq_block_kernel(const float* __restrict__ wc, int64_t n_rows, int64_t k, int64
     rc_st[s] = make_recip((st_c[s] == 0.0f) ? 1.0f : st_c[s]);
   }
 
-  // rows i1 .. i1+len-1 of U, this lane's four columns
+  // rows i1 .. i1+len-1 of U, this lane's four columns, held two rows ahead of their use in a
+  // ring of four registers-quads: rows i, i+1 are in ring[0..1] when a group of four steps starts,
+  // rows i+2, i+3 are requested then, and the first two rows of the next group as soon as steps
+  // 0 and 1 have consumed theirs
   const float* urow = u + i1 * k + i1 + c0;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 ahead[4];
-#pragma unroll
-  for (int s = 0; s < 4; ++s)
-    ahead[s] = mine ? *reinterpret_cast<const float4*>(urow + (int64_t)s * k) : zero4;
+  auto fetch = [&](int r) {
+    return (mine && r < len) ? *reinterpret_cast<const float4*>(urow + (int64_t)r * k) : zero4;
+  };
+  float4 ring[4];
+  ring[0] = fetch(0), ring[1] = fetch(1);
 
   for (int i = 0; i < len; i += 4) {
-    float4 cur[4];
-#pragma unroll
-    for (int s = 0; s < 4; ++s) cur[s] = ahead[s];
-    if (i + 4 < len) {
-#pragma unroll
-      for (int s = 0; s < 4; ++s)
-        ahead[s] = mine ? *reinterpret_cast<const float4*>(urow + (int64_t)(i + 4 + s) * k) : zero4;
-    }
+    ring[2] = fetch(i + 2), ring[3] = fetch(i + 3);
     const int owner = i >> 2;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const int ii = i + s;
-      const float us[4] = {cur[s].x, cur[s].y, cur[s].z, cur[s].w};
+      const float us[4] = {ring[s].x, ring[s].y, ring[s].z, ring[s].w};
+      if (s == 2) ring[0] = fetch(i + 4), ring[1] = fetch(i + 5);
       // every lane evaluates slot s of its own quad; only the owner's result is used
       const float col = w[s], lo_j = lo_c[s], st_j = st_c[s];
       const float safe = (st_j == 0.0f) ? 1.0f : st_j;
@@ -97,10 +95,14 @@ gptq_block_kernel(const float* __restrict__ wc, int64_t n_rows, int64_t k, int64
       const float wq = round_f16(lo_j + q * st_j);
       const float e_own = div_by(col - wq, udiag[s], rc_u[s]);
       const float e = __shfl_sync(0xffffffffu, e_own, owner);
-      if (lane == owner) q_keep[s] = q, e_keep[s] = e_own, col_keep[s] = col;
+      if (lane == owner) {
+        q_keep[s] = q, e_keep[s] = e_own;
+        if (WITH_COMP) col_keep[s] = col;
+      }
+      // all four columns, as the reference updates w1[:, i:]: columns up to this one are never
+      // read again (and U is upper triangular, so their factor entries are zero anyway)
 #pragma unroll
-      for (int t = 0; t < 4; ++t)
-        if (c0 + t > ii) w[t] = w[t] - e * us[t];
+      for (int t = 0; t < 4; ++t) w[t] = w[t] - e * us[t];
     }
   }
 
@@ -109,7 +111,7 @@ gptq_block_kernel(const float* __restrict__ wc, int64_t n_rows, int64_t k, int64
         make_float4(e_keep[0], e_keep[1], e_keep[2], e_keep[3]);
     *reinterpret_cast<uchar4*>(codes + row * k + i1 + c0) =
         make_uchar4((uint8_t)q_keep[0], (uint8_t)q_keep[1], (uint8_t)q_keep[2], (uint8_t)q_keep[3]);
-    if (comp != nullptr)
+    if (WITH_COMP)
       *reinterpret_cast<float4*>(comp + row * k + i1 + c0) =
           make_float4(col_keep[0], col_keep[1], col_keep[2], col_keep[3]);
   }
@@ -120,9 +122,14 @@ int launch_block(const float* wc, int64_t n_rows, int64_t k, int64_t i1, int len
                  const int32_t* row_grp, const int64_t* u_ptrs, const int32_t* blk,
                  const float* nmax, float* comp, cudaStream_t stream) {
   const unsigned grid = (unsigned)ceil_div(n_rows, ROWS_PER_CTA);
-  gptq_block_kernel<<<grid, ROWS_PER_CTA * 32, 0, stream>>>(wc, n_rows, k, i1, len, err1, codes, lo,
-                                                            st, ldp, row_grp, u_ptrs, blk, nmax,
-                                                            comp);
+  if (comp != nullptr)
+    gptq_block_kernel<true><<<grid, ROWS_PER_CTA * 32, 0, stream>>>(wc, n_rows, k, i1, len, err1, codes,
+                                                                    lo, st, ldp, row_grp, u_ptrs, blk,
+                                                                    nmax, comp);
+  else
+    gptq_block_kernel<false><<<grid, ROWS_PER_CTA * 32, 0, stream>>>(wc, n_rows, k, i1, len, err1, codes,
+                                                                     lo, st, ldp, row_grp, u_ptrs, blk,
+                                                                     nmax, comp);
   return check_launch("gptq_block");
 }
 
@@ -135,7 +142,7 @@ int launch_lazy(float* wc, int64_t n_rows, int64_t k, int64_t i1, int64_t i2, co
   p.b = u + i1 * k + i2, p.ldb = k;
   p.c = wc + i2, p.ldc = k;
   p.flags = 0;
-  return launch_gemm<float, float, float, 8, 8, 8>(false, false, p, stream, "gptq_lazy_update");
+  return launch_gemm_async<float, 8, 8, 16>(false, false, p, stream, "gptq_lazy_update");
 }
 
 int check_block_args(const float* wc, int64_t n_rows, int64_t k, int64_t i1, int len,
@@ -277,6 +284,6 @@ extern "C" int hi2_gemm_f32(int trans_a, int trans_b, int64_t m, int64_t n, int6
   GemmArgs<float, float, float> p;
   p.m = m, p.n = n, p.kk = kk, p.alpha = alpha, p.beta = beta;
   p.a = a, p.lda = lda, p.b = b, p.ldb = ldb, p.c = c, p.ldc = ldc, p.flags = 0;
-  return launch_gemm<float, float, float, 8, 8, 8>(trans_a != 0, trans_b != 0, p,
-                                                   static_cast<cudaStream_t>(stream), "gemm_f32");
+  return launch_gemm_async<float, 8, 8, 16>(trans_a != 0, trans_b != 0, p,
+                                            static_cast<cudaStream_t>(stream), "gemm_f32");
 }

@@ -18,24 +18,47 @@ struct GridSpec {
   int g;
 };
 
+// Weighted error of a block under ladder (lo, step).  The codes are rint((x - lo) / safe); one
+// correctly rounded reciprocal of `safe` serves the whole block: (x - lo) * r is within
+// 1.8e-7 * |q| of the IEEE quotient q, so the two round to the same integer unless the product
+// lies that close to a half-integer inside the ladder (outside it both clamp to the same end).
+// The block keeps the smallest distance to a half-integer it met; in the rare case (one warp
+// iteration in 10^2..10^3) that it is below the bound, the block is redone with IEEE divisions,
+// so the result is always the one the divisions give.
 template <int B>
-__device__ __forceinline__ float block_error(const float (&x)[B], const float* __restrict__ dd,
-                                             float lo, float step, float nmax) {
+__device__ __forceinline__ float block_error(const float (&x)[B], const float* __restrict__ xs,
+                                             const float* __restrict__ dd, float lo, float step,
+                                             float nmax, float near_half) {
   const float safe = (step == 0.0f) ? 1.0f : step;
-  const Recip rc = make_recip(safe);  // one reciprocal serves the block (see rint_div)
-  float err = 0.0f;
+  const Recip rc = make_recip(safe);
+  float err = 0.0f, margin = 1.0f;
 #pragma unroll
   for (int t = 0; t < B; ++t) {
-    float q = rint_div(x[t] - lo, safe, rc);
+    const float tt = (x[t] - lo) * rc.r;
+    float q = rintf(tt);
+    margin = fminf(margin, fabsf(fabsf(tt - q) - 0.5f));
     q = fminf(fmaxf(q, 0.0f), nmax);
     const float diff = (lo + q * step) - x[t];
     err += __ldg(dd + t) * (diff * diff);
+  }
+  if (!rc.fast || !(margin >= near_half)) {
+    // rare: redo the block with IEEE divisions, re-reading the weights (xs, an L1/L2 hit) so
+    // that the register copy x[] is never indexed dynamically
+    err = 0.0f;
+#pragma unroll 1
+    for (int t = 0; t < B; ++t) {
+      const float xv = __ldg(xs + t);
+      float q = rintf(__fdiv_rn(xv - lo, safe));
+      q = fminf(fmaxf(q, 0.0f), nmax);
+      const float diff = (lo + q * step) - xv;
+      err += __ldg(dd + t) * (diff * diff);
+    }
   }
   return err;
 }
 
 template <int B>
-__global__ void __launch_bounds__(256, (B == 64 ? 2 : 1))  // B = 64: 118 registers instead of 160, two blocks per SM
+__global__ void __launch_bounds__(256, (B == 16 ? 4 : 2))  // register caps 64 / 128 / 128: occupancy matters more than the spare registers
 fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, int64_t n_rows,
            int64_t nb, GridSpec grid, int refits, float nmax, float* __restrict__ lo_out,
            float* __restrict__ st_out, float* __restrict__ err_out) {
@@ -57,13 +80,14 @@ fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d
 #pragma unroll
   for (int t = 1; t < B; ++t) mn = fminf(mn, x[t]), mx = fmaxf(mx, x[t]);
   const float span = mx - mn;
+  const float near_half = 2.5e-7f * (nmax + 2.0f);  // see block_error
 
   float best_lo = 0.0f, best_st = 0.0f, best_err = 0.0f;
   for (int gi = 0; gi < grid.g; ++gi) {
     const float lo = mn + grid.v[gi] * span;
     for (int gj = 0; gj < grid.g; ++gj) {
       const float step = __fdiv_rn((mx - grid.v[gj] * span) - lo, nmax);
-      const float err = block_error<B>(x, dd, lo, step, nmax);
+      const float err = block_error<B>(x, src, dd, lo, step, nmax, near_half);
       if ((gi | gj) == 0 || err < best_err) best_lo = lo, best_st = step, best_err = err;
     }
   }
@@ -71,10 +95,12 @@ fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d
   for (int it = 0; it < refits; ++it) {
     const float safe = (best_st == 0.0f) ? 1.0f : best_st;
     const Recip rc = make_recip(safe);
-    float sd = 0.f, sc = 0.f, scc = 0.f, sw = 0.f, scw = 0.f, sum = 0.f;
+    float sd = 0.f, sc = 0.f, scc = 0.f, sw = 0.f, scw = 0.f, sum = 0.f, margin = 1.0f;
 #pragma unroll
     for (int t = 0; t < B; ++t) {
-      float c = rint_div(x[t] - best_lo, safe, rc);
+      const float tt = (x[t] - best_lo) * rc.r;
+      float c = rintf(tt);
+      margin = fminf(margin, fabsf(fabsf(tt - c) - 0.5f));
       c = fminf(fmaxf(c, 0.0f), nmax);
       const float dt = __ldg(dd + t), dc = dt * c;
       sd += dt;
@@ -84,11 +110,27 @@ fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d
       scw += dc * x[t];
       sum += x[t];
     }
+    if (!rc.fast || !(margin >= near_half)) {  // rare: the same sums with IEEE divisions
+      sd = sc = scc = sw = scw = sum = 0.0f;
+#pragma unroll 1
+      for (int t = 0; t < B; ++t) {
+        const float xv = __ldg(src + t);
+        float c = rintf(__fdiv_rn(xv - best_lo, safe));
+        c = fminf(fmaxf(c, 0.0f), nmax);
+        const float dt = __ldg(dd + t), dc = dt * c;
+        sd += dt;
+        sc += dc;
+        scc += dc * c;
+        sw += dt * xv;
+        scw += dc * xv;
+        sum += xv;
+      }
+    }
     const float det = sd * scc - sc * sc;
     const bool ok = fabsf(det) > 1e-20f;
     const float step = ok ? __fdiv_rn(sd * scw - sc * sw, det) : 0.0f;
     const float lo = ok ? __fdiv_rn(sw - step * sc, fmaxf(sd, 1e-20f)) : __fdiv_rn(sum, (float)B);
-    const float err = block_error<B>(x, dd, lo, step, nmax);
+    const float err = block_error<B>(x, src, dd, lo, step, nmax, near_half);
     if (err < best_err && step > 0.0f) best_lo = lo, best_st = step, best_err = err;
   }
 

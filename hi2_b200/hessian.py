@@ -139,6 +139,18 @@ class FactorJob:
         self.stream = torch.cuda.current_stream(self.dev)
         self.attempt = 0
         self._launch()
+        self.done = torch.cuda.Event()  # the first attempt has finished on the device
+        self.done.record(self.stream)
+
+    def first_attempt(self) -> torch.Tensor:
+        """``U`` of the first attempt WITHOUT waiting for it: consumers order themselves after
+        ``self.done`` on their stream and call :meth:`succeeded` once the work is enqueued."""
+        return self.u
+
+    def succeeded(self) -> bool:
+        """Whether the first attempt met no non-positive pivot (synchronises with it)."""
+        self.done.synchronize()
+        return int(self.info.item()) == 0 and bool(torch.isfinite(self.u.diagonal()).all())
 
     def _launch(self) -> None:
         self.lam = (self.damp * self.mean * 10**self.attempt).to(torch.float32).reshape(1)
@@ -182,6 +194,7 @@ class GptqJob:
     nbits: int
     block: int
     perm: torch.Tensor | None = None
+    wait: torch.cuda.Event | None = None  # ``u`` is complete once this event has passed
 
 
 @dataclass
@@ -228,6 +241,8 @@ def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool, split
     """All ``units`` (same K, same device) through one enqueue of the column loop.  ``splits``
     caches the TF32 split of each distinct factor over one :func:`encode_jobs_gptq` call."""
     dev, k = units[0].wc.device, units[0].wc.shape[1]
+    for ev in {id(jobs[x.job].wait): jobs[x.job].wait for x in units if jobs[x.job].wait is not None}.values():
+        torch.cuda.current_stream(dev).wait_event(ev)  # factors still in flight on a side stream
     sizes = [x.rows for x in units]
     total = sum(sizes)
     if len(units) == 1:
