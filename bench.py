@@ -160,6 +160,14 @@ class Job:
         self.copy_stream = None
         self.stage_ms: dict = {}
 
+    def input_order(self):
+        """Widest input first (longest factorisation), then by the rows that read it, so the input
+        that arrives last over PCIe has the least work hanging on it."""
+        rows = {n: 0 for n in self.widths}
+        for w, (r, _) in self.shapes.items():
+            rows[self.plan.reads[w]] += r
+        return sorted(self.widths, key=lambda n: (-self.widths[n], -rows[n]))
+
     # bytes one rank moves per step in the end-to-end measurement
     def h2d_bytes(self):
         n = sum(w.numel() * w.element_size() for w in self.weights.values())
@@ -189,14 +197,14 @@ class Job:
                 for name, w in self.weights.items():
                     w.copy_(self.host["w"][name], non_blocking=True)
                 ready["w"] = self.copy_stream.record_event()
-                for name in sorted(self.widths, key=lambda n: -self.widths[n]):  # the order of use
+                for name in self.input_order():  # the order of use
                     for layer, xs in enumerate(self.inputs):
                         xs[name].copy_(self.host["x"][layer][name], non_blocking=True)
                         ready[(layer, name)] = self.copy_stream.record_event()
         cur = torch.cuda.current_stream(self.device)
         # Inputs are taken widest first: the K = 11008 factorisation is the longest chain, so it
         # starts earliest and runs on its side stream beside everything that follows.
-        order = sorted(self.widths, key=lambda n: -self.widths[n])
+        order = self.input_order()
         self._mark(marks, "hessian")
         shared_all = [dict() for _ in self.inputs]
         pending, factors, tables = [], {}, {}
@@ -235,12 +243,8 @@ class Job:
         tag = f"L{self.rank}."
         for name, t in tables.items():
             t.name = tag + name
-        if self.world == 1:
-            everything = list(tables.values())
-        else:  # a few bytes per row: every rank allocates over every table and keeps its own picks
-            local = [dict(name=t.name, shape=t.shape, had=t.had, sse=t.sse.cpu(), candidates=t.candidates,
-                          energy=float(t.energy), n_tokens=t.n_tokens, col_scale=t.col_scale) for t in tables.values()]
-            everything = [TensorTable(**{**d, "sse": d["sse"].to(self.device)}) for d in hd.gather_tables(local)]
+        # a few bytes per row: every rank allocates over every table and keeps its own picks
+        everything = hd.gather_error_tables(list(tables.values()), TensorTable)
         alloc = allocate_global(everything, self.cfg["bpw"])
         picks = {name: alloc.picks[tag + name] for name in tables}
         self._mark(marks, "encode")

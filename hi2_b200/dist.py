@@ -98,6 +98,45 @@ def gather_tables(local: list) -> list:
     return [t for part in box for t in part]
 
 
+def gather_error_tables(tables: list, make):
+    """All ranks' error tables for the global allocation, rank order then local order.
+
+    Only what the allocator reads crosses the wire: one small pickled record per table (name,
+    shape, candidates, energy, token count, whether a smoothing vector is stored) and the ``sse``
+    values themselves as ONE padded fp32 tensor per rank (``all_gather`` on the tables' device: NCCL
+    for CUDA tensors, gloo for CPU ones).  ``make(**fields)`` builds a table object; local tables
+    are returned as they are."""
+    if world_size() == 1:
+        return list(tables)
+    meta = [dict(name=t.name, shape=tuple(t.shape), candidates=list(t.candidates), energy=float(t.energy),
+                 n_tokens=t.n_tokens, scaled=t.col_scale is not None) for t in tables]
+    box: list = [None] * world_size()
+    dist.all_gather_object(box, meta)
+    cmax = max(len(m["candidates"]) for part in box for m in part)
+    rmax = max(sum(m["shape"][0] for m in part) for part in box)
+    dev = tables[0].sse.device if tables else torch.device("cpu")
+    mine = torch.full((cmax, rmax), float("inf"), dtype=torch.float32, device=dev)
+    off = 0
+    for t in tables:
+        mine[: t.sse.shape[0], off : off + t.sse.shape[1]] = t.sse
+        off += t.sse.shape[1]
+    parts = [torch.empty_like(mine) for _ in range(world_size())]
+    dist.all_gather(parts, mine)
+    out = []
+    for r, (part, buf) in enumerate(zip(box, parts)):
+        if r == rank():
+            out.extend(tables)
+            continue
+        off = 0
+        for m in part:
+            rows, c = m["shape"][0], len(m["candidates"])
+            out.append(make(name=m["name"], shape=m["shape"], had=None, sse=buf[:c, off : off + rows],
+                            candidates=m["candidates"], energy=m["energy"], n_tokens=m["n_tokens"],
+                            col_scale=torch.empty(0) if m["scaled"] else None))
+            off += rows
+    return out
+
+
 def barrier() -> None:
     if world_size() > 1:
         dist.barrier()

@@ -202,8 +202,8 @@ int hi2_transform_sigma(const float* sigma, float denom, const uint16_t* col_sca
 
 /* hi2/hessian.py:71-86 inverse_factor, one damping attempt: u = upper Cholesky factor of
  * (hs + *lam * I)^-1 with lam a device fp32 scalar.  *info (device int, caller zeroes it) is
- * set to 1 + index of the first non-positive pivot; u is then unspecified.  Workspace: fp64
- * scratch of hi2_inverse_factor_workspace_bytes(k). */
+ * set to 1 + index of the first non-positive pivot; u is then unspecified.  Workspace: fp32
+ * scratch of hi2_inverse_factor_workspace_bytes(k) = 8 k^2 bytes. */
 size_t hi2_inverse_factor_workspace_bytes(int64_t k);
 int hi2_inverse_factor(const float* hs, const float* lam, int64_t k, float* u, void* workspace,
                        size_t workspace_bytes, int32_t* info, void* stream);

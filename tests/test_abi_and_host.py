@@ -43,7 +43,7 @@ def test_argument_checks_need_no_device():
     assert b"multiple of 16" in lib.hi2_last_error()
     assert lib.hi2_pack_codes(None, None, 1, 15, 2, None, None) == _lib.ERR_ARG
     assert lib.hi2_gptq_lazy_update(None, 0, 128, 0, 128, None, None, None) == _lib.OK
-    assert lib.hi2_inverse_factor_workspace_bytes(1024) == 1024 * 1024 * 16
+    assert lib.hi2_inverse_factor_workspace_bytes(1024) == 1024 * 1024 * 8
     assert lib.hi2_hessian_workspace_bytes(100, 64, _lib.BF16) == 0  # small: FMA path, no scratch
     need = lib.hi2_hessian_workspace_bytes(262144, 4096, _lib.BF16)
     assert need > 0 and need % 4 == 0
@@ -103,6 +103,19 @@ assert hd.all_reduce_second_moment(s, part.shape[0]) == tokens
 assert torch.allclose(s, full, rtol=1e-5, atol=1e-4)
 tabs = hd.gather_tables([{"name": f"r{rank}", "sse": torch.full((2, 3), float(rank))}])
 assert [t["name"] for t in tabs] == [f"r{i}" for i in range(world)]
+from types import SimpleNamespace as NS
+local = [NS(name=f"r{rank}.a", shape=(3 + rank, 64), candidates=[(2, 16), (4, 16)], energy=1.0 + rank, n_tokens=5,
+            col_scale=None if rank else torch.ones(64), sse=torch.full((2, 3 + rank), float(rank))),
+         NS(name=f"r{rank}.b", shape=(2, 32), candidates=[(2, 16)], energy=2.0, n_tokens=5, col_scale=None,
+            sse=torch.full((1, 2), 10.0 + rank))]
+every = hd.gather_error_tables(local, lambda **kw: NS(**kw))
+assert [t.name for t in every] == ["r0.a", "r0.b", "r1.a", "r1.b"]
+assert every[2 * rank] is local[0]
+for r in range(world):
+    a, b = every[2 * r], every[2 * r + 1]
+    assert tuple(a.sse.shape) == (2, 3 + r) and bool((a.sse == float(r)).all()) and a.energy == 1.0 + r
+    assert tuple(b.sse.shape) == (1, 2) and bool((b.sse == 10.0 + r).all())
+    assert (a.col_scale is not None) == (r == 0) and b.col_scale is None
 hd.barrier()
 print("ok", rank)
 """
