@@ -394,9 +394,23 @@ def run_reference(args, cfg):
     print(json.dumps(line), flush=True)
 
 
-# measured with ncu on the second-moment kernel (profiles/): DRAM bytes per token-column pair
-# read, filled in after a capture; None means "no capture yet"
-HESSIAN_TRAFFIC_BYTES_PER_LAUNCH = None
+# ncu capture of the second-moment kernel at 32768 tokens x 4096 columns
+# (profiles/hessian_tc_kernel_k4096_32k_tokens.md): DRAM reads were 2.08 x the bytes of X (L2 absorbs
+# the rest of the tile re-reads), DRAM writes the per-item output tiles.  Reads grow in proportion
+# to the tokens, the tiles do not, so a full-size launch is scaled from those two figures.
+HESSIAN_READ_FACTOR = 2.08
+
+
+def hessian_traffic(widths, tokens, elem_bytes=2):
+    """Estimated DRAM bytes per launch, averaged over the launches of one step."""
+    total = 0.0
+    for k in widths.values():
+        nib, njb = -(-k // 128), -(-k // 256)
+        tiles = sum(njb - (ib >> 1) for ib in range(nib))
+        kblocks = -(-tokens // 64)
+        splits = max(1, min(-(-148 * 6 // tiles), max(1, kblocks // 64)))
+        total += HESSIAN_READ_FACTOR * tokens * k * elem_bytes + splits * tiles * 128 * 256 * 4
+    return total / max(1, len(widths))
 
 
 def mem_available_bytes() -> int:
@@ -488,7 +502,9 @@ def run_ours(args, cfg):
         "frac": achieved / pk["tensor"], "peak_source": f"{pk['source']}, sustained (kernel timed inside a long step)",
         "effective": algo / hess_s / 1e12,
         "note": "achieved counts the flops issued (upper-triangle 128x256 tiles); effective counts 2*T*K^2",
-        "traffic": HESSIAN_TRAFFIC_BYTES_PER_LAUNCH,
+        "traffic": hessian_traffic(job.widths, cfg["tokens"]),
+        "traffic_note": "bytes per launch, scaled from an ncu capture at 32768 tokens (reads 2.08 x X, plus item tiles)",
+        "algorithmic_bytes": sum(cfg["tokens"] * k * 2 + 4 * k * k for k in job.widths.values()) / max(1, len(job.widths)),
         "launch_ms": hess_s * 1e3 / max(1, len(job.widths) * world),
     }
     cpu = None

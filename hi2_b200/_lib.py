@@ -62,6 +62,7 @@ SIGNATURES = {
     "hi2_inverse_factor_workspace_bytes": (_Z, [_L]),
     "hi2_inverse_factor": (_I, [_P, _P, _L, _P, _P, _Z, _P, _P]),
     "hi2_allocate_solve": (_I, [_P, _P, _I, _L, _D, _P, _P, _P]),
+    "hi2_allocate_bits": (_I, [_P, _P, _I, _L, _P, _I, _P, _P]),
 }
 
 _lock = threading.Lock()

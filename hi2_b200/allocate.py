@@ -88,6 +88,18 @@ class _Flat:
         )
         return picks, float(self.total.item())
 
+    def bits_of(self, lams: list[float]) -> list[float]:
+        """Total picked bits under each of up to 8 multipliers, one launch and one read-back."""
+        import ctypes
+
+        totals = torch.zeros(len(lams), dtype=torch.float64, device=self.dev)
+        arr = (ctypes.c_double * len(lams))(*lams)
+        _lib.call(
+            "hi2_allocate_bits", _lib.ptr(self.cost), _lib.ptr(self.bits), self.cost.shape[0], self.rows,
+            arr, len(lams), _lib.ptr(totals), _lib.stream(self.dev),
+        )
+        return totals.tolist()
+
     def split(self, picks):
         return {name: picks[a:b].clone() for name, a, b in self.spans}
 
@@ -132,12 +144,34 @@ def allocate_global(tables, target_bpw: float, sensitivity: dict | None = None,
     best = flat.solve(lo)
     if best[1] <= budget:  # even the most accurate one fits
         return done(best[0], best[1], lo, True)
+    # The reference bisects one multiplier per step.  The next three steps can only visit the 7
+    # midpoints of a depth-3 tree, so their bit totals are fetched in one launch and the steps are
+    # then taken on the host exactly as the reference takes them (same Python-float midpoints).
     best_lam = hi
-    for _ in range(iters):
-        mid = (lo * hi) ** 0.5
-        p, b = flat.solve(mid)
-        if b <= budget:
-            hi, picks, bits_total, best_lam = mid, p, b, mid
-        else:
-            lo = mid
+    left = iters
+    while left > 0:
+        depth = min(3, left)
+        nodes = {(): (lo, hi)}  # path of outcomes (True = fits) -> bracket before that step
+        lams, order = [], []
+        for level in range(depth):
+            for path in [q for q in nodes if len(q) == level]:
+                a, b = nodes[path]
+                mid = (a * b) ** 0.5
+                order.append(path)
+                lams.append(mid)
+                nodes[path + (True,)] = (a, mid)
+                nodes[path + (False,)] = (mid, b)
+        totals = dict(zip(order, zip(lams, flat.bits_of(lams))))
+        path = ()
+        for _ in range(depth):
+            mid, b = totals[path]
+            fits = b <= budget
+            if fits:
+                hi, bits_total, best_lam = mid, b, mid
+            else:
+                lo = mid
+            path = path + (fits,)
+        left -= depth
+    if best_lam != lam_hi:
+        picks, bits_total = flat.solve(best_lam)
     return done(picks, bits_total, best_lam, True)
