@@ -424,6 +424,9 @@ def mem_available_bytes() -> int:
 
 
 def run_ours(args, cfg):
+    # NCCL prints its version banner on stdout when NCCL_DEBUG asks for it; stdout carries the one
+    # JSON line, so the banner goes to stderr unless the caller chose a file already
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     import torch.distributed as dist
 
     from hi2_b200 import _lib

@@ -58,6 +58,7 @@ SIGNATURES = {
     "hi2_hessian_status": (_I, [_P, _P]),
     "hi2_hessian_accumulate_noalloc": (_I, [_P, _I, _L, _L, _P, _P, _P]),
     "hi2_group_moments": (_I, [_P, _L, _P, _P]),
+    "hi2_group_moments_update": (_I, [_P, _I, _L, _L, _P, _P]),
     "hi2_transform_sigma": (_I, [_P, _F, _P, _P, _L, _P, _P, _P]),
     "hi2_inverse_factor_workspace_bytes": (_Z, [_L]),
     "hi2_inverse_factor": (_I, [_P, _P, _L, _P, _P, _Z, _P, _P]),

@@ -125,8 +125,74 @@ group_moments_kernel(const float* __restrict__ s, int64_t k, double* __restrict_
   g[idx] += (double)s[(grp * 16 + i) * k + grp * 16 + j];
 }
 
+// Group moments straight from activations (hi2/stats.py:27-33): a thread block takes a slab of
+// up to 4096 tokens (the reference's chunk) and 8 groups (128 columns); the slab passes through
+// shared memory 64 tokens at a time, lane l of warp g owns row l/2 and eight columns of group g's
+// 16 x 16 block.  Products are summed in fp32 over 64 tokens, the partial sums in fp64, and the slab's
+// sum is added to the fp64 total with one atomic per entry (the reference sums 4096 tokens in fp32
+// with a blocked einsum before widening; a serial fp32 sum that long would lose two more digits).
+template <typename TX>
+__global__ void __launch_bounds__(256)
+group_moments_update_kernel(const TX* __restrict__ x, int64_t tokens, int64_t k, double* __restrict__ g) {
+  __shared__ float xs[64][128 + 4];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t col0 = (int64_t)blockIdx.x * 128;
+  const int64_t t_begin = (int64_t)blockIdx.y * 4096;
+  const int64_t t_end = t_begin + 4096 < tokens ? t_begin + 4096 : tokens;
+  const int row_i = lane >> 1, j0 = (lane & 1) * 8;
+  double total[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) total[j] = 0.0;
+  for (int64_t t0 = t_begin; t0 < t_end; t0 += 64) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    for (int idx = tid; idx < 64 * 128; idx += 256) {
+      const int tt = idx >> 7, c = idx & 127;
+      float v = 0.0f;
+      if (t0 + tt < t_end && col0 + c < k) v = (float)x[(t0 + tt) * k + col0 + c];
+      xs[tt][c] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int tt = 0; tt < 64; ++tt) {
+      const float a = xs[tt][warp * 16 + row_i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(a, xs[tt][warp * 16 + j0 + j], acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) total[j] += (double)acc[j];
+    __syncthreads();
+  }
+  const int64_t grp = (col0 >> 4) + warp;
+  if (grp * 16 < k) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(g + grp * 256 + row_i * 16 + j0 + j, total[j]);
+  }
+}
+
 }  // namespace
 }  // namespace hi2
+
+extern "C" int hi2_group_moments_update(const void* x, int dtype, int64_t tokens, int64_t k, double* g,
+                                        void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(k > 0 && k % 16 == 0, "group_moments_update: k must be a positive multiple of 16");
+  HI2_REQUIRE(tokens >= 0, "group_moments_update: negative token count");
+  if (tokens == 0) return HI2_OK;
+  HI2_REQUIRE(x && g, "group_moments_update: null pointer");
+  dim3 grid((unsigned)ceil_div(k, 128), (unsigned)ceil_div(tokens, 4096));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == HI2_BF16)
+    group_moments_update_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), tokens, k, g);
+  else if (dtype == HI2_F16)
+    group_moments_update_kernel<<<grid, 256, 0, s>>>(static_cast<const __half*>(x), tokens, k, g);
+  else if (dtype == HI2_F32)
+    group_moments_update_kernel<<<grid, 256, 0, s>>>(static_cast<const float*>(x), tokens, k, g);
+  else
+    return fail(HI2_ERR_ARG, "group_moments_update: dtype must be F16, BF16 or F32");
+  return check_launch("group_moments_update");
+}
 
 extern "C" int hi2_transform_sigma(const float* sigma, float denom, const uint16_t* col_scale,
                                    const uint8_t* had, int64_t k, float* hs, float* diag,

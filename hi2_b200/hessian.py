@@ -45,6 +45,18 @@ def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
     return buf
 
 
+_side_streams: dict = {}
+
+
+def _side_stream(dev: torch.device, i: int) -> torch.cuda.Stream:
+    """Side streams are created once per device and reused (the caching allocator pools memory
+    per stream)."""
+    key = (dev.index, i)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(dev)
+    return _side_streams[key]
+
+
 class HessianStats:
     """Full second moment ``sum x x^T`` of a Linear's input (fp32, ``[K, K]``)."""
 
@@ -237,9 +249,10 @@ def _prepare(ji: int, job: GptqJob, s: int, step_rows: int, effort: str) -> _Uni
 TC_MIN_K = 512
 
 
-def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool, splits: dict) -> None:
+def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool, splits: dict, checks: list) -> None:
     """All ``units`` (same K, same device) through one enqueue of the column loop.  ``splits``
-    caches the TF32 split of each distinct factor over one :func:`encode_jobs_gptq` call."""
+    caches the TF32 split of each distinct factor over one :func:`encode_jobs_gptq` call;
+    ``checks`` collects the device status words to be read once everything is enqueued."""
     dev, k = units[0].wc.device, units[0].wc.shape[1]
     for ev in {id(jobs[x.job].wait): jobs[x.job].wait for x in units if jobs[x.job].wait is not None}.values():
         torch.cuda.current_stream(dev).wait_event(ev)  # factors still in flight on a side stream
@@ -273,10 +286,8 @@ def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool, split
             if u.data_ptr() not in splits:
                 splits[u.data_ptr()] = (u, gptq_kernel.split_tf32_transposed(u))  # keeps u alive with its split
             parts.append(splits[u.data_ptr()][1])
-        status = gptq_kernel.gptq_round_tc(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp,
-                                           offs, parts)
-        if int(status.item()):
-            raise RuntimeError("gptq trailing update: a bounded device-side wait ran out")
+        checks.append(gptq_kernel.gptq_round_tc(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp,
+                                                offs, parts))
     else:
         gptq_kernel.gptq_round(wc, err1, codes, lo, st, row_grp, u_ptrs, blk, nmax, comp, offs, us)
     for x, o, n in zip(units, offs, sizes):
@@ -340,12 +351,28 @@ def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str |
         if bl[-1] and sum(y.wc.numel() for y in bl[-1]) + x.wc.numel() > BATCH_ELEMS:
             bl.append([])
         bl[-1].append(x)
+    # Widths are independent column loops of many short launches; each width after the first runs
+    # on a side stream so that, e.g., the 86 blocks of a 4096 x 11008 matrix overlap the batches of
+    # the 4096-wide ones.  Status words are read only after everything is enqueued.
     splits: dict = {}
-    for bl in batches.values():
-        for batch in bl:
-            _round_units(batch, jobs, comp, splits)
-            for x in batch:
-                x.wc = None
+    checks: list = []
+    joins = []
+    for gi, ((dev, _k), bl) in enumerate(batches.items()):
+        main = torch.cuda.current_stream(dev)
+        side = main if gi == 0 else _side_stream(dev, gi)
+        if side is not main:
+            side.wait_stream(main)
+        with torch.cuda.stream(side):
+            for batch in bl:
+                _round_units(batch, jobs, comp, splits, checks)
+                for x in batch:
+                    x.wc = None
+        if side is not main:
+            joins.append((main, side))
+    for main, side in joins:
+        main.wait_stream(side)
+    if any(int(st.item()) for st in checks):
+        raise RuntimeError("gptq trailing update: a bounded device-side wait ran out")
     per_job: list[list[Encoded]] = [[] for _ in jobs]
     for x in units:
         per_job[x.job].append(_finish(x, jobs[x.job]))

@@ -1,0 +1,116 @@
+"""Mixture-of-experts statistics on the device (hi2/moe.py:31-56, 152-156, 188-207;
+hi2/layerwise.py:231-257).
+
+The encode path treats every expert projection as its own matrix: its second moment sums only the
+tokens routed to it, gate and up of one expert share that sum, and an expert that saw too few
+tokens borrows the pooled sum of its layer for the missing ones.  This module holds that logic for
+accumulators that live in HBM (``HessianStats`` / ``ColumnStats``); checkpoint surgery (unfusing
+3-D expert parameters) is not part of the encode path and is not here.
+"""
+
+from __future__ import annotations
+
+import re
+
+import torch
+
+from .hessian import HessianStats
+from .stats import ColumnStats
+
+_EXPERT = re.compile(r"^(.*?\bexperts)\.(\d+)\.([^.]+)(?:\.weight)?$")
+# projections of one expert that always see the same input (gate/up; Mixtral w1/w3)
+_SAME_INPUT = {"up_proj": "gate_proj", "w3": "w1"}
+
+
+def expert_parts(name: str):
+    """``(group prefix, expert index, projection)`` of ``...experts.<E>.<proj>[.weight]``, else None."""
+    m = _EXPERT.match(name)
+    return None if m is None else (m.group(1), int(m.group(2)), m.group(3))
+
+
+def group_key(name: str) -> str:
+    """The name with the expert index replaced by ``*``: one key per layer and projection."""
+    p = expert_parts(name)
+    return name if p is None else f"{p[0]}.*.{p[2]}"
+
+
+def sibling_leader(name: str):
+    """For an expert ``up_proj`` (``w3``) the ``gate_proj`` (``w1``) whose input it shares."""
+    p = expert_parts(name)
+    if p is None or p[2] not in _SAME_INPUT:
+        return None
+    return f"{p[0]}.{p[1]}.{_SAME_INPUT[p[2]]}"
+
+
+def blend(own_sum, own_n: int, avg_sum, avg_n: int, need: int):
+    """``own + (need - n) * avg / avg_n`` and the new token count ``need``."""
+    fill = (need - own_n) / max(avg_n, 1)
+    return own_sum + fill * avg_sum.to(own_sum.device), need
+
+
+def accumulate_routed(x: torch.Tensor, top_k_index: torch.Tensor, hess: list, stats: list | None = None):
+    """Add to expert ``e``'s accumulators the tokens of ``x [T, K]`` whose ``top_k_index [T, k]``
+    names ``e`` (each token once per expert, as the expert's Linear hook sees it)."""
+    x = x.reshape(-1, x.shape[-1])
+    idx = top_k_index.reshape(x.shape[0], -1)
+    for e, h in enumerate(hess):
+        rows = (idx == e).any(1).nonzero().squeeze(1)
+        if rows.numel() == 0:
+            continue
+        xe = x.index_select(0, rows)
+        if h is not None:
+            h.update(xe)
+        if stats is not None and stats[e] is not None:
+            stats[e].update(xe)
+
+
+def top_up(stats: dict, hess: dict | None, k_of: dict, min_tokens: float):
+    """Top the leaders of every expert group up to ``min_tokens x widest input`` tokens with the
+    group's pooled sums; returns the set of leaders that borrowed (hi2/layerwise.py:231-257)."""
+    borrowed: set[str] = set()
+    if min_tokens <= 0:
+        return borrowed
+    width: dict[tuple, int] = {}
+    for n, k in k_of.items():
+        p = expert_parts(n)
+        if p is not None:
+            width[p[:2]] = max(width.get(p[:2], 0), k)
+    groups: dict[str, list[str]] = {}
+    for ld in stats:
+        if expert_parts(ld) is not None:
+            groups.setdefault(group_key(ld), []).append(ld)
+    for lds in groups.values():
+        tot_n = sum(stats[ld].n for ld in lds)
+        tot_s = sum(stats[ld].S for ld in lds)
+        tot_h = sum(hess[ld].S for ld in lds) if hess else None
+        for ld in lds:
+            need = int(min_tokens * width[expert_parts(ld)[:2]])
+            if stats[ld].n >= need or tot_n == 0:
+                continue
+            st = stats[ld]
+            st.S, st.n = blend(st.S, st.n, tot_s, tot_n, need)
+            if hess:
+                h = hess[ld]
+                h.S, h.n = blend(h.S, h.n, tot_h, tot_n, need)
+            borrowed.add(ld)
+    return borrowed
+
+
+def expert_weights(tables: dict, share_floor: float = 0.05) -> dict:
+    """Allocation multiplier per expert tensor: ``max(n_e / mean(n), share_floor) / E``."""
+    groups: dict[str, list[str]] = {}
+    for name in tables:
+        if expert_parts(name) is not None:
+            groups.setdefault(group_key(name), []).append(name)
+    out: dict[str, float] = {}
+    for names in groups.values():
+        ns = [tables[n].n_tokens for n in names]
+        mean = sum(ns) / len(ns)
+        for n, c in zip(names, ns):
+            share = c / mean if mean > 0 else 1.0
+            out[n] = max(share, share_floor) / len(names)
+    return out
+
+
+__all__ = ["expert_parts", "group_key", "sibling_leader", "blend", "accumulate_routed", "top_up",
+           "expert_weights", "HessianStats", "ColumnStats"]

@@ -1,8 +1,9 @@
 """Per-group second moments on B200 (interface of hi2/stats.py:16-64).
 
 hi2 keeps, next to the full second moment, the 16x16 diagonal blocks of it in fp64
-(``ColumnStats``): enough for the exact diagonal in the rotated basis.  Here they are read out
-of the accumulated second moment (``HessianStats.S``) instead of being summed a second time.
+(``ColumnStats``): enough for the exact diagonal in the rotated basis.  When the full second moment
+is accumulated anyway they are read out of it (``from_second_moment``); ``update`` sums them from
+activations directly for callers that keep no full second moment (data-free tables, nearest rounding).
 """
 
 from __future__ import annotations
@@ -37,12 +38,17 @@ class ColumnStats:
 
     @torch.no_grad()
     def update(self, x: torch.Tensor) -> None:
-        """Accumulate from activations ``x [..., K]`` (through a temporary second moment)."""
-        from .hessian import HessianStats
-
-        h = HessianStats(self.k, self.S.device)
-        h.update(x)
-        self.add_second_moment(h.S, h.n)
+        """Accumulate from activations ``x [..., K]`` (fp32 sums per 4096 tokens, fp64 total)."""
+        dev = _lib.need_cuda(self.S)
+        x = x.reshape(-1, self.k)
+        if x.device != dev:
+            x = x.to(dev)
+        if x.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            x = x.float()
+        x = x.contiguous()
+        _lib.call("hi2_group_moments_update", _lib.ptr(x), _lib.DTYPES[x.dtype], x.shape[0], self.k,
+                  _lib.ptr(self.S), _lib.stream(dev))
+        self.n += x.shape[0]
 
     def merge(self, other: "ColumnStats") -> None:
         self.S += other.S.to(self.S.device)

@@ -194,6 +194,10 @@ int hi2_hessian_accumulate_noalloc(const void* x, int dtype, int64_t tokens, int
 /* hi2/stats.py:27-33 ColumnStats.update, taken from the second moment: g [k/16, 16, 16] fp64
  * += the 16x16 diagonal blocks of s. */
 int hi2_group_moments(const float* s, int64_t k, double* g, void* stream);
+/* The same blocks accumulated straight from activations x [tokens, k] (F16/BF16/F32): fp32 sums
+ * per run of 4096 tokens, fp64 total, as hi2/stats.py:27-33 does. */
+int hi2_group_moments_update(const void* x, int dtype, int64_t tokens, int64_t k, double* g,
+                             void* stream);
 
 /* hi2/hessian.py:50-68 transform_sigma: hs = sym(T (sigma/denom) T^T), T = R diag(1/col_scale).
  * col_scale fp16 [k] or null, had u8 [k/16], diag (fp32 [k], may be null) receives diag(hs). */

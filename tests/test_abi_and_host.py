@@ -135,3 +135,26 @@ def test_two_gloo_ranks_reduce_and_gather(tmp_path):
     for p, o in zip(procs, outs):
         assert p.returncode == 0, o
         assert "ok" in o
+
+
+def test_expert_names_and_allocation_weights():
+    """hi2/moe.py:31-56, 188-207 (tests/test_moe.py:236-250 checks the same split)."""
+    from types import SimpleNamespace
+
+    from hi2_b200 import moe
+
+    n = "model.layers.3.mlp.experts.12.up_proj.weight"
+    assert moe.expert_parts(n) == ("model.layers.3.mlp.experts", 12, "up_proj")
+    assert moe.group_key(n) == "model.layers.3.mlp.experts.*.up_proj"
+    assert moe.sibling_leader(n) == "model.layers.3.mlp.experts.12.gate_proj"
+    assert moe.expert_parts("model.layers.3.mlp.gate.weight") is None
+    assert moe.sibling_leader("model.layers.3.mlp.experts.12.down_proj") is None
+    tables = {f"l.experts.{e}.down_proj": SimpleNamespace(n_tokens=c)
+              for e, c in enumerate([300, 100, 0, 0])}
+    tables["l.attn.q_proj"] = SimpleNamespace(n_tokens=400)
+    w = moe.expert_weights(tables)
+    assert "l.attn.q_proj" not in w
+    assert w["l.experts.0.down_proj"] == 3.0 / 4 and w["l.experts.1.down_proj"] == 1.0 / 4
+    assert w["l.experts.2.down_proj"] == 0.05 / 4
+    own, need = moe.blend(torch.ones(2, 2), 10, torch.full((2, 2), 8.0), 40, 30)
+    assert need == 30 and torch.equal(own, torch.full((2, 2), 5.0))

@@ -88,8 +88,25 @@ def test_group_moments_and_diag(golden):
     inv = 1.0 / st["s16"].float()
     assert rel_close(c.diag(st["had"].to(DEV), inv.to(DEV)), st["diag_rot_inv"], 1e-5)
     c2 = ColumnStats(64, DEV)
-    c2.update(st["x"].to(DEV))
-    assert torch.equal(c2.S, c.S) and c2.n == c.n
+    c2.update(st["x"][:300].to(DEV))
+    c2.update(st["x"][300:].to(DEV))
+    assert c2.n == c.n and _norm_err(torch.block_diag(*c2.S.cpu()), blocks) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_group_moments_from_activations(dtype):
+    """Tokens beyond one 4096-run, K not a multiple of the 128-column block of a thread block."""
+    from hi2_b200.stats import ColumnStats
+
+    x = activations(9000, 208, 3, dtype=dtype)
+    c = ColumnStats(208, DEV)
+    c.update(x.to(DEV))
+    o = po.GroupMoments(208)
+    o.update(x)
+    assert c.n == o.n
+    assert _norm_err(torch.block_diag(*c.S.cpu()), torch.block_diag(*o.S)) < 1e-6
+    flags = torch.ones(13, dtype=torch.uint8)
+    assert rel_close(c.diag(flags.to(DEV)), o.diag(flags), 1e-5)
 
 
 def test_transform_sigma_fixture(golden):
