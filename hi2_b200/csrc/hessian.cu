@@ -10,8 +10,9 @@
 //     stage, descriptors advanced by 2 KiB per 16 tokens.
 //   * Only tiles that touch the upper triangle are computed; the strict lower triangle is
 //     mirrored afterwards, so S is exactly symmetric.
-//   * A work item is (tile, token split).  Items are ordered split-major so the CTAs resident at
-//     one time read the same token range and X streams through L2 once per wave.
+//   * A work item is (tile, token split).  Items are ordered split-major, and inside a split in
+//     bands of 16 row blocks (decode_tile), so the CTAs resident at one time read the same token
+//     range of a few thousand columns and X streams through L2 about once per wave.
 //   * Tensor-memory accumulation runs over 1024 tokens at a time into one of two 256-column
 //     buffers; eight epilogue warps drain a finished buffer into fp32 REGISTER accumulators
 //     (round-to-nearest adds) while the next 1024 tokens accumulate in the other buffer.  This
@@ -166,22 +167,43 @@ struct TcParams {
   int64_t kblocks;  // ceil(tokens / BKT)
   int splits;
   int tiles;
+  int nib;          // row blocks: ceil(k / BM)
   int njb;          // column blocks: ceil(k / BN)
   int fmt;          // 0 fp16, 1 bf16
 };
 
-// Tile number -> (row block, column block) over the tiles that touch the upper triangle:
-// row block ib owns column blocks floor(ib / 2) .. njb - 1.
-__device__ __forceinline__ void decode_tile(int tile, int njb, int& ib, int& jb) {
-  int i = 0;
-  while (true) {
-    const int cnt = njb - (i >> 1);
-    if (tile < cnt) break;
-    tile -= cnt;
-    ++i;
+// Scratch slot of tile (row block ib, column block jb) over the tiles that touch the upper
+// triangle, row-major: row block ib owns column blocks floor(ib / 2) .. njb - 1.
+__host__ __device__ __forceinline__ int tile_slot(int ib, int jb, int njb) {
+  const int half = ib >> 1;
+  return ib * njb - (half * (half - 1) + ((ib & 1) ? half : 0)) + (jb - half);
+}
+
+// Schedule position -> (row block, column block).  Tiles are visited in bands of BAND row blocks,
+// column block by column block inside a band, so that the ~148 tiles in flight at any moment
+// cover about BAND x 128 + (148 / BAND) x 256 columns of X instead of all of them: with K = 11008
+// a token of X is 22 KB, and the CTAs' token positions drift apart by thousands of tokens, so the
+// row-major order overflowed L2 and ran at the speed of HBM.
+#ifndef HI2_HESSIAN_BAND
+#define HI2_HESSIAN_BAND 16
+#endif
+constexpr int BAND = HI2_HESSIAN_BAND;
+__device__ __forceinline__ void decode_tile(int pos, int nib, int njb, int& ib, int& jb) {
+  for (int i0 = 0; i0 < nib; i0 += BAND) {
+    const int rows = (nib - i0 < BAND) ? nib - i0 : BAND;
+    for (int j = i0 >> 1; j < njb; ++j) {
+      // row blocks of the band with floor(ib / 2) <= j, i.e. ib <= 2 j + 1
+      int cnt = 2 * j + 2 - i0;
+      if (cnt > rows) cnt = rows;
+      if (pos < cnt) {
+        ib = i0 + pos;
+        jb = j;
+        return;
+      }
+      pos -= cnt;
+    }
   }
-  ib = i;
-  jb = (i >> 1) + tile;
+  ib = 0, jb = 0;  // not reached: pos < tiles
 }
 
 // Ten warps: the register file is four partitions of 16384, so two partitions hold three warps
@@ -219,9 +241,9 @@ hessian_tc_kernel(const __grid_constant__ CUtensorMap map, const TcParams p) {
     uint32_t phase = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-      const int tile = item % p.tiles, split = item / p.tiles;
+      const int split = item / p.tiles;
       int ib, jb;
-      decode_tile(tile, p.njb, ib, jb);
+      decode_tile(item % p.tiles, p.nib, p.njb, ib, jb);
       const int64_t kb0 = p.kblocks * split / p.splits, kb1 = p.kblocks * (split + 1) / p.splits;
       for (int64_t kb = kb0; kb < kb1; ++kb) {
         if (!(ok = mbar_wait(&ctl->empty[stage], phase ^ 1, ctl, p.status))) break;
@@ -303,7 +325,10 @@ hessian_tc_kernel(const __grid_constant__ CUtensorMap map, const TcParams p) {
         if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
       }
       if (ok) {
-        float* dst = p.scratch + ((size_t)item * TILE_ELEMS) + (size_t)row * BN + half * 128;
+        int ib, jb;
+        decode_tile(item % p.tiles, p.nib, p.njb, ib, jb);
+        const size_t slot = (size_t)split * p.tiles + tile_slot(ib, jb, p.njb);
+        float* dst = p.scratch + slot * TILE_ELEMS + (size_t)row * BN + half * 128;
 #pragma unroll
         for (int i = 0; i < 128; i += 4)
           *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
@@ -328,10 +353,7 @@ hessian_reduce_kernel(const float* __restrict__ scratch, int splits, int tiles, 
   const int64_t i = blockIdx.y;
   if (j >= k || j < i) return;
   const int ib = (int)(i / BM), jb = (int)(j / BN);
-  // tiles before row block ib: sum_{r<ib} (njb - r/2)
-  const int half = ib >> 1;
-  int before = ib * njb - (half * (half - 1) + ((ib & 1) ? half : 0));
-  const int tile = before + (jb - half);
+  const int tile = tile_slot(ib, jb, njb);
   const size_t off = (size_t)tile * TILE_ELEMS + (size_t)(i % BM) * BN + (size_t)(j % BN);
   float sum = 0.0f;
   for (int sp = 0; sp < splits; ++sp) sum += scratch[(size_t)sp * tiles * TILE_ELEMS + off];
@@ -421,7 +443,7 @@ int accumulate_tc(const void* x, int dtype, int64_t tokens, int64_t k, float* s,
     return fail(HI2_ERR_LAUNCH, "hessian_accumulate: memset failed");
   TcParams p;
   p.scratch = scratch, p.status = status, p.k = k, p.kblocks = pl.kblocks;
-  p.splits = pl.splits, p.tiles = pl.tiles, p.njb = pl.njb, p.fmt = dtype == HI2_BF16 ? 1 : 0;
+  p.splits = pl.splits, p.tiles = pl.tiles, p.njb = pl.njb, p.nib = (int)ceil_div(k, BM), p.fmt = dtype == HI2_BF16 ? 1 : 0;
   const int items = pl.tiles * pl.splits;
   int device = 0, sms = 148;
   cudaGetDevice(&device);
@@ -592,7 +614,7 @@ extern "C" int hi2_hessian_accumulate_noalloc(const void* x, int dtype, int64_t 
     return fail(HI2_ERR_LAUNCH, "hessian_accumulate_noalloc: memset failed");
   TcParams p;
   p.scratch = tiles, p.status = reinterpret_cast<int*>(status), p.k = k, p.kblocks = pl.kblocks;
-  p.splits = pl.splits, p.tiles = pl.tiles, p.njb = pl.njb, p.fmt = dtype == HI2_BF16 ? 1 : 0;
+  p.splits = pl.splits, p.tiles = pl.tiles, p.njb = pl.njb, p.nib = (int)ceil_div(k, BM), p.fmt = dtype == HI2_BF16 ? 1 : 0;
   const int items = pl.tiles * pl.splits;
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
