@@ -211,10 +211,10 @@ class Job:
         mine = shared_all[self.rank]
         if ready is not None:
             cur.wait_event(ready["w"])
-        def finish_input(name):  # statistics, tables and (on a side stream) the factor of one input
+        def finish_input(name):  # statistics, the factor (on a side stream) and the tables of one input
             L.finish_statistics(mine, self.qcfg, only=name)
-            L.tabulate(self.weights, self.plan, mine, self.qcfg, only=name, into=tables)
             L.start_factors(mine, self.qcfg, self.device, only=name, into=factors)
+            L.tabulate(self.weights, self.plan, mine, self.qcfg, only=name, into=tables)
 
         for name in order:
             for layer, xs in enumerate(self.inputs):
@@ -236,8 +236,11 @@ class Job:
             for work in pending:
                 work.wait()
             self._mark(marks, "tables")
+            for name in order:  # every factorisation starts before the first table kernel
+                L.finish_statistics(mine, self.qcfg, only=name)
+                L.start_factors(mine, self.qcfg, self.device, only=name, into=factors)
             for name in order:
-                finish_input(name)
+                L.tabulate(self.weights, self.plan, mine, self.qcfg, only=name, into=tables)
         tables = {name: tables[name] for name in self.weights}
         self._mark(marks, "allocate")
         tag = f"L{self.rank}."

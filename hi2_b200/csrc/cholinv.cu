@@ -27,6 +27,12 @@
 #include "gemm.cuh"
 
 namespace hi2 {
+// lazy_tc.cu
+int launch_gemm_tc(int64_t m, int64_t n, int64_t kk, const float* a_hi, const float* a_lo, const float* b_hi,
+                   const float* b_lo, int64_t ldk, float* c, int64_t ldc, int flags, int* status,
+                   cudaStream_t stream);
+int launch_split_block(const float* x, int64_t ldx, int64_t rows, int64_t cols, float* hi, float* lo,
+                       int64_t ldo, bool transposed, cudaStream_t stream);
 namespace {
 
 constexpr int NB = 64;
@@ -66,18 +72,35 @@ __device__ __forceinline__ double inv_sqrt(double v) {
   return y;
 }
 
+// 1 / v in fp64 from the fp32 estimate and three Newton steps.
+__device__ __forceinline__ double recip(double v) {
+  if (!(v > 1e-30 && v < 1e30)) return 1.0 / v;
+  double y = (double)__frcp_rn((float)v);
+#pragma unroll
+  for (int it = 0; it < 3; ++it) y = fma(y, fma(-v, y, 1.0), y);  // y += y * (1 - v y)
+  return y;
+}
+
 // Factorise the n x n (n <= 64) diagonal block at `off` (lower part of a, leading dim ld) and
 // write its inverse, zeros above the diagonal included, to the same place of x (fp32 in memory,
-// fp64 inside the block).  One thread block:
-// 256 threads as a 16 x 16 grid for the trailing updates of the factorisation (two barriers per
-// column), then as 64 columns x 4 partial sums for the row-by-row triangular inverse (the four
-// partial sums of a column sit in adjacent lanes and meet by shuffle, one barrier per row).
+// fp64 inside the block).  One thread block of 256 threads.
+//
+// Factorisation: right-looking with UNSCALED columns, so a column costs one barrier: after step j
+// the entries below the diagonal of column j hold the Schur-updated a_ij and the true factor is
+// l_ij = a_ij / sqrt(p_j) with p_j the updated pivot; the trailing update needs only
+// a_ij a_cj / p_j.  The 64 square roots are taken side by side after the loop.
+//
+// Inverse: column c of X = L^-1 belongs to four adjacent lanes, lane `part` keeping
+// X[c + part + 4 r][c], r = 0..15, in registers.  Row i = c + d of the column is
+// -(sum_{q < i} L[i][q] X[q][c]) / L[i][i]; the loop over d is unrolled so every register index
+// is static, the four partial sums meet by shuffle, and no barrier is needed at all.
 __global__ void __launch_bounds__(256)
 leaf_kernel(const float* __restrict__ a, float* __restrict__ x, int64_t ld, int64_t off, int n,
             int32_t* info) {
   extern __shared__ double leaf_smem[];
   double (*L)[LDL] = reinterpret_cast<double (*)[LDL]>(leaf_smem);
   double (*X)[LDL] = reinterpret_cast<double (*)[LDL]>(leaf_smem + NB * LDL);
+  __shared__ double pivot[NB];
   __shared__ double inv_diag[NB];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const float* src = a + off * ld + off;
@@ -86,6 +109,7 @@ leaf_kernel(const float* __restrict__ a, float* __restrict__ x, int64_t ld, int6
     L[i][j] = (i < n && j <= i) ? (double)src[(int64_t)i * ld + j] : 0.0;
     X[i][j] = 0.0;
   }
+  if (tid < NB) pivot[tid] = 1.0;
   __syncthreads();
   for (int j = 0; j < n; ++j) {
     double piv = L[j][j];  // final: every update of (j, j) was followed by a barrier
@@ -93,29 +117,53 @@ leaf_kernel(const float* __restrict__ a, float* __restrict__ x, int64_t ld, int6
       if (tid == 0) atomicCAS(info, 0, (int32_t)(off + j + 1));
       piv = 1.0;
     }
-    const double inv = inv_sqrt(piv);  // L[j][j] itself stays un-rooted; 1/sqrt is kept instead
-    if (tid == 0) inv_diag[j] = inv;
-    for (int i = j + 1 + tid; i < n; i += 256) L[i][j] *= inv;
-    __syncthreads();
+    if (tid == 0) pivot[j] = piv;
+    const double rp = recip(piv);
     for (int i = j + 1 + ty; i < n; i += 16) {
-      const double lij = L[i][j];
+      const double lij = L[i][j] * rp;
       for (int c = j + 1 + tx; c <= i; c += 16) L[i][c] = fma(-lij, L[c][j], L[i][c]);
     }
     __syncthreads();
   }
-  // X = L^-1, row by row: X[i][c] = -(sum_{q=c}^{i-1} L[i][q] X[q][c]) / L[i][i], X[i][i] = 1 / L[i][i]
-  const int c = tid >> 2, part = tid & 3;
-  if (tid < n) X[tid][tid] = inv_diag[tid];
+  if (tid < NB) inv_diag[tid] = tid < n ? inv_sqrt(pivot[tid]) : 0.0;
   __syncthreads();
-  for (int i = 1; i < n; ++i) {
-    double acc = 0.0;
-    if (c < i)
-      for (int q = c + part; q < i; q += 4) acc = fma(L[i][q], X[q][c], acc);
+  for (int idx = tid; idx < NB * NB; idx += 256) {  // the true factor below the diagonal
+    const int i = idx >> 6, j = idx & 63;
+    if (j < i) L[i][j] *= inv_diag[j];
+  }
+  __syncthreads();
+
+  const int c = tid >> 2, part = tid & 3;
+  double xr[16];
+#pragma unroll
+  for (int r = 0; r < 16; ++r) xr[r] = 0.0;
+  if (part == 0) xr[0] = inv_diag[c];
+#pragma unroll
+  for (int d = 1; d < NB; ++d) {
+    const int i = c + d;  // rows past the block read the zero padding of L and stay zero
+    double acc0 = 0.0, acc1 = 0.0;
+    if (i < NB) {
+#pragma unroll
+      for (int r = 0; r <= (d >> 2); ++r) {
+        // q = c + part + 4 r < i  <=>  part + 4 r < d
+        if (4 * r + 3 < d || part + 4 * r < d) {
+          const double l = L[i][c + part + 4 * r];
+          if (r & 1) acc1 = fma(l, xr[r], acc1);
+          else acc0 = fma(l, xr[r], acc0);
+        }
+      }
+    }
+    double acc = acc0 + acc1;
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    if (part == 0 && c < i) X[i][c] = -acc * inv_diag[i];
-    __syncthreads();
+    if (part == (d & 3)) xr[d >> 2] = (i < NB) ? -acc * inv_diag[i] : 0.0;
   }
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const int i = c + part + 4 * r;
+    if (i < NB) X[i][c] = xr[r];
+  }
+  __syncthreads();
   float* dst = x + off * ld + off;
   for (int idx = tid; idx < n * n; idx += 256) {
     const int i = idx / n, j = idx % n;
@@ -126,10 +174,29 @@ leaf_kernel(const float* __restrict__ a, float* __restrict__ x, int64_t ld, int6
 struct Plan {
   float* a;
   float* x;
+  float* split;  // TF32 parts of the operands of one tensor-core product (4 n1^2 floats)
+  int* status;   // raised by a tensor-core product whose bounded wait ran out
   int64_t k;
   int32_t* info;
   cudaStream_t stream;
 };
+
+constexpr int GT_KB_LE_J = 1, GT_KB_GE_J = 2, GT_KA_LE_I = 4, GT_LOWER_OUT = 8, GT_NEGATE = 16, GT_ADD = 32;
+
+// Products at least this large on both output sides go to the tensor cores (3xTF32, fp32-grade);
+// below it a 128 x 256 tile grid no longer fills the SMs and the FMA kernel is as fast.
+#ifndef HI2_FACTOR_TC_MIN
+#define HI2_FACTOR_TC_MIN 1024
+#endif
+
+int64_t top_half(int64_t n) { return ((ceil_div(n, (int64_t)64) + 1) / 2) * 64; }
+size_t split_floats(int64_t k) {
+  const int64_t n1 = top_half(k);
+  return k >= 2 * HI2_FACTOR_TC_MIN ? (size_t)(4 * n1 * n1) : 0;
+}
+__global__ void merge_status_kernel(const int* status, int32_t* info) {
+  if (*status != 0) *info = -1;
+}
 
 int product(bool trans_b, int64_t m, int64_t n, int64_t kk, float alpha, const float* a,
             const float* b, float beta, float* c, int64_t ld, int flags, cudaStream_t stream) {
@@ -154,6 +221,35 @@ int factor(const Plan& pl, int64_t off, int64_t n) {
   float* x11 = pl.x + off * ld + off;
   float* x21 = pl.x + (off + n1) * ld + off;
   float* x22 = pl.x + (off + n1) * ld + off + n1;
+  if (n2 >= HI2_FACTOR_TC_MIN && pl.split != nullptr) {
+    // Tensor-core path.  Operands are split into TF32 parts first (K-major; the right-hand
+    // operands of T = W X11 and X21 = -X22 T are split transposed).  n1 >= n2 and n1 is a multiple
+    // of 64, so four parts of n1 x n1 floats hold any pair of operands of this level; deeper
+    // levels reuse the same scratch once this level's product has consumed it (one stream).
+    const int64_t part = n1 * n1;
+    float *ah = pl.split, *al = ah + part, *bh = al + part, *bl = bh + part;
+    const int64_t l1 = n1, l2 = ceil_div(n2, (int64_t)32) * 32;  // leading dimensions for kk = n1, n2
+    // W (in the X21 slot) = A21 X11^T
+    if ((rc = launch_split_block(a21, ld, n2, n1, ah, al, l1, false, pl.stream)) != HI2_OK) return rc;
+    if ((rc = launch_split_block(x11, ld, n1, n1, bh, bl, l1, false, pl.stream)) != HI2_OK) return rc;
+    rc = launch_gemm_tc(n2, n1, n1, ah, al, bh, bl, l1, x21, ld, GT_KB_LE_J, pl.status, pl.stream);
+    if (rc != HI2_OK) return rc;
+    // A22 -= W W^T (lower tiles)
+    if ((rc = launch_split_block(x21, ld, n2, n1, ah, al, l1, false, pl.stream)) != HI2_OK) return rc;
+    rc = launch_gemm_tc(n2, n2, n1, ah, al, ah, al, l1, a22, ld, GT_LOWER_OUT | GT_NEGATE | GT_ADD, pl.status,
+                        pl.stream);
+    if (rc != HI2_OK) return rc;
+    // T (in the A21 slot) = W X11
+    if ((rc = launch_split_block(x11, ld, n1, n1, bh, bl, l1, true, pl.stream)) != HI2_OK) return rc;
+    rc = launch_gemm_tc(n2, n1, n1, ah, al, bh, bl, l1, a21, ld, GT_KB_GE_J, pl.status, pl.stream);
+    if (rc != HI2_OK) return rc;
+    rc = factor(pl, off + n1, n2);
+    if (rc != HI2_OK) return rc;
+    // X21 = -X22 T
+    if ((rc = launch_split_block(x22, ld, n2, n2, ah, al, l2, false, pl.stream)) != HI2_OK) return rc;
+    if ((rc = launch_split_block(a21, ld, n2, n1, bh, bl, l2, true, pl.stream)) != HI2_OK) return rc;
+    return launch_gemm_tc(n2, n1, n2, ah, al, bh, bl, l2, x21, ld, GT_KA_LE_I | GT_NEGATE, pl.status, pl.stream);
+  }
   // W (in the X21 slot) = A21 X11^T
   rc = product(true, n2, n1, n1, 1.0f, a21, x11, 0.0f, x21, ld, GEMM_KB_LE_J, pl.stream);
   if (rc != HI2_OK) return rc;
@@ -173,7 +269,8 @@ int factor(const Plan& pl, int64_t off, int64_t n) {
 }  // namespace hi2
 
 extern "C" size_t hi2_inverse_factor_workspace_bytes(int64_t k) {
-  return k > 0 ? (size_t)k * (size_t)k * 2 * sizeof(float) : 0;
+  if (k <= 0) return 0;
+  return ((size_t)k * (size_t)k * 2 + hi2::split_floats(k)) * sizeof(float) + 256;
 }
 
 extern "C" int hi2_inverse_factor(const float* hs, const float* lam, int64_t k, float* u,
@@ -192,9 +289,14 @@ extern "C" int hi2_inverse_factor(const float* hs, const float* lam, int64_t k, 
       return fail(HI2_ERR_LAUNCH, "inverse_factor: cannot reserve shared memory");
   }
   Plan pl;
-  pl.a = static_cast<float*>(workspace);
+  // layout: one status word (256 bytes), A, X, then the TF32 parts
+  pl.status = static_cast<int*>(workspace);
+  pl.a = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
   pl.x = pl.a + k * k;
+  pl.split = split_floats(k) ? pl.x + k * k : nullptr;
   pl.k = k, pl.info = info, pl.stream = s;
+  if (cudaMemsetAsync(pl.status, 0, 256, s) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "inverse_factor: memset failed");
   const unsigned grid = (unsigned)ceil_div(k * k, 256);
   reverse_damp_kernel<<<grid, 256, 0, s>>>(hs, lam, k, pl.a);
   int rc = check_launch("inverse_factor reverse");
@@ -203,6 +305,7 @@ extern "C" int hi2_inverse_factor(const float* hs, const float* lam, int64_t k, 
     return fail(HI2_ERR_LAUNCH, "inverse_factor: memset failed");
   rc = factor(pl, 0, k);
   if (rc != HI2_OK) return rc;
+  if (pl.split != nullptr) merge_status_kernel<<<1, 1, 0, s>>>(pl.status, info);
   reverse_store_kernel<<<grid, 256, 0, s>>>(pl.x, k, u);
   return check_launch("inverse_factor store");
 }

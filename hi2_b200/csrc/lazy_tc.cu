@@ -252,6 +252,233 @@ lazy_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// General product on the same pipeline, for the inverse factor's large steps:
+//
+//     C[m, n] (+)= (+-) A[m, kk] . Bt[n, kk]^T
+//
+// A and Bt are given as their TF32 parts (K-major, leading dimension ldk), C is fp32 with its own
+// leading dimension.  Triangular operands are expressed as reduction ranges per tile (the same
+// flags as gemm.cuh): the skipped range holds exact zeros, so taking whole 32-wide stages of it
+// changes nothing.  The result is stored (beta = 0) or added (beta = 1) by TMA, which clips the
+// boxes at the edge of C, so m and n need no alignment.
+constexpr int GT_KB_LE_J = 1, GT_KB_GE_J = 2, GT_KA_LE_I = 4, GT_LOWER_OUT = 8, GT_NEGATE = 16, GT_ADD = 32;
+
+struct GParams {
+  int* status;
+  int row_tiles, col_tiles;
+  int kk;
+  int flags;
+};
+
+__device__ __forceinline__ void mma_tf32_d(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tma_store(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(s32(src)), "r"(x), "r"(y) : "memory");
+}
+
+// Reduction stages [s0, s1) of tile (tr, tc), or s0 >= s1 for a tile that is not computed.
+__device__ __forceinline__ void tile_range(const GParams& p, int tr, int tc, int& s0, int& s1) {
+  int k0 = 0, k1 = p.kk;
+  if (p.flags & GT_KB_LE_J) k1 = min(k1, (tc + 1) * LN);
+  if (p.flags & GT_KA_LE_I) k1 = min(k1, (tr + 1) * LM);
+  if (p.flags & GT_KB_GE_J) k0 = tc * LN;
+  s0 = k0 / KSTAGE;
+  s1 = (k1 + KSTAGE - 1) / KSTAGE;
+  if (s1 <= s0) s1 = s0 + 1;  // an empty range still yields a (zero) tile
+  if ((p.flags & GT_LOWER_OUT) && tc * LN > tr * LM + LM - 1) s1 = s0;
+}
+
+__global__ void __launch_bounds__(L_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+               const __grid_constant__ CUtensorMap map_bhi, const __grid_constant__ CUtensorMap map_blo,
+               const __grid_constant__ CUtensorMap map_c, const GParams p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_c = smem + (size_t)LSTAGES * LSTAGE_BYTES;
+  LControl* ctl = reinterpret_cast<LControl*>(stage_c + 2 * C_BOX);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < LSTAGES; ++s) bar_init(&ctl->full[s], 1), bar_init(&ctl->empty[s], 1);
+    for (int b = 0; b < 2; ++b) bar_init(&ctl->acc_full[b], 1), bar_init(&ctl->acc_empty[b], 4);
+    ctl->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&ctl->tmem_base)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int tiles = p.row_tiles * p.col_tiles;
+
+  if (warp == 4 && lane == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int tr = tile % p.row_tiles, tc = tile / p.row_tiles;  // neighbours share the B tile
+      int s0, s1;
+      tile_range(p, tr, tc, s0, s1);
+      for (int ks = s0; ks < s1; ++ks) {
+        if (!(ok = bar_wait(&ctl->empty[stage], phase ^ 1, ctl, p.status))) break;
+        bar_expect(&ctl->full[stage], LSTAGE_BYTES);
+        uint8_t* dst = smem + (size_t)stage * LSTAGE_BYTES;
+        tma_load(dst, &map_ahi, &ctl->full[stage], ks * KSTAGE, tr * LM);
+        tma_load(dst + A_BOX, &map_alo, &ctl->full[stage], ks * KSTAGE, tr * LM);
+        tma_load(dst + 2 * A_BOX, &map_bhi, &ctl->full[stage], ks * KSTAGE, tc * LN);
+        tma_load(dst + 2 * A_BOX + B_PART, &map_blo, &ctl->full[stage], ks * KSTAGE, tc * LN);
+        if (++stage == LSTAGES) stage = 0, phase ^= 1;
+      }
+    }
+    if (!ok) {
+      const long long t0 = clock64();
+      while (clock64() - t0 < 2000000LL) {
+      }
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.flags & GT_NEGATE) ? (1u << 13) : 0u) |
+                           ((uint32_t)(LN >> 3) << 17) | ((uint32_t)(LM >> 4) << 24);
+    int stage = 0;
+    uint32_t phase = 0, n = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int tr = tile % p.row_tiles, tc = tile / p.row_tiles;
+      int s0, s1;
+      tile_range(p, tr, tc, s0, s1);
+      if (s1 <= s0) continue;
+      const int buf = n & 1;
+      if (!(ok = bar_wait(&ctl->acc_empty[buf], ((n >> 1) & 1) ^ 1, ctl, p.status))) break;
+      fence_after();
+      const uint32_t d_tmem = tmem_base + buf * LN;
+      for (int ks = s0; ks < s1 && ok; ++ks) {
+        if (!(ok = bar_wait(&ctl->full[stage], phase, ctl, p.status))) break;
+        fence_after();
+        const uint32_t sa = s32(smem + (size_t)stage * LSTAGE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < KSTAGE / 8; ++kk) {
+          const uint64_t ahi = desc_kmajor(sa + kk * 32), alo = desc_kmajor(sa + A_BOX + kk * 32);
+          const uint64_t bhi = desc_kmajor(sa + 2 * A_BOX + kk * 32);
+          const uint64_t blo = desc_kmajor(sa + 2 * A_BOX + B_PART + kk * 32);
+          mma_tf32_d(d_tmem, ahi, bhi, idesc, (ks > s0 || kk > 0) ? 1u : 0u);
+          mma_tf32_d(d_tmem, alo, bhi, idesc, 1u);
+          mma_tf32_d(d_tmem, ahi, blo, idesc, 1u);
+        }
+        commit_to(&ctl->empty[stage]);
+        if (++stage == LSTAGES) stage = 0, phase ^= 1;
+      }
+      if (ok) commit_to(&ctl->acc_full[buf]);
+      ++n;
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------ epilogue
+    uint32_t n = 0, chunk_no = 0;
+    bool ok = true;
+    const bool add = (p.flags & GT_ADD) != 0;
+    uint8_t* my_boxes = stage_c + warp * (2 * C_BOX / 4);  // two 4 KiB boxes per warp
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int tr = tile % p.row_tiles, tc = tile / p.row_tiles;
+      int s0, s1;
+      tile_range(p, tr, tc, s0, s1);
+      if (s1 <= s0) continue;
+      const int buf = n & 1;
+      if (!(ok = bar_wait(&ctl->acc_full[buf], (n >> 1) & 1, ctl, p.status))) break;
+      fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * LN;
+      for (int c = 0; c < LN / 32; ++c, ++chunk_no) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c * 32, v);
+        uint8_t* box = my_boxes + (chunk_no & 1) * (C_BOX / 4);
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+        uint8_t* rowp = box + lane * 128;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) =
+              make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          if (add) tma_reduce_add(&map_c, box, tc * LN + c * 32, tr * LM + warp * 32);
+          else tma_store(&map_c, box, tc * LN + c * 32, tr * LM + warp * 32);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      fence_before();
+      __syncwarp();
+      if (lane == 0) bar_arrive(&ctl->acc_empty[buf]);
+      ++n;
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// TF32 parts of a [rows, cols] block with leading dimension ldx, written with leading dimension ldo.
+__global__ void __launch_bounds__(256)
+split_block_kernel(const float* __restrict__ x, int64_t ldx, int64_t rows, int64_t cols,
+                   float* __restrict__ hi, float* __restrict__ lo, int64_t ldo) {
+  const int64_t c4 = cols / 4;  // cols is a multiple of 4
+  const int64_t total = rows * c4, stride = (int64_t)gridDim.x * 256;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += stride) {
+    const int64_t r = i / c4, c = (i % c4) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
+    const float in[4] = {v.x, v.y, v.z, v.w};
+    float h[4], l[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      uint32_t hb, lb;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(in[t]));
+      h[t] = __uint_as_float(hb);
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(in[t] - h[t]));
+      l[t] = __uint_as_float(lb);
+    }
+    *reinterpret_cast<float4*>(hi + r * ldo + c) = make_float4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<float4*>(lo + r * ldo + c) = make_float4(l[0], l[1], l[2], l[3]);
+  }
+}
+
+// The same for the transpose: x [rows, cols] (ldx) -> hi, lo [cols, rows] (ldo).
+__global__ void __launch_bounds__(256)
+split_block_transposed_kernel(const float* __restrict__ x, int64_t ldx, int64_t rows, int64_t cols,
+                              float* __restrict__ hi, float* __restrict__ lo, int64_t ldo) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+  for (int i = ty; i < 32; i += 8)
+    tile[i][tx] = (r0 + i < rows && c0 + tx < cols) ? x[(r0 + i) * ldx + c0 + tx] : 0.0f;
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    if (c0 + i < cols && r0 + tx < rows) {
+      const float v = tile[tx][i];
+      uint32_t hb, lb;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v));
+      const float h = __uint_as_float(hb);
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(v - h));
+      hi[(c0 + i) * ldo + r0 + tx] = h;
+      lo[(c0 + i) * ldo + r0 + tx] = __uint_as_float(lb);
+    }
+  }
+}
+
 // hi = tf32(x), lo = tf32(x - hi), both round-to-nearest (ties away): x = hi + lo + O(2^-22 |x|)
 __global__ void __launch_bounds__(256)
 split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int64_t n4) {
@@ -352,6 +579,47 @@ int launch_lazy_tc(float* wc, int64_t n_rows, int64_t k, int64_t i1, const float
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   lazy_tc_kernel<<<tiles < sms ? tiles : sms, L_THREADS, L_SMEM, stream>>>(mah, mal, mbh, mbl, mc, p);
   return check_launch("gptq_lazy_update (tcgen05)");
+}
+
+// C[m, n] (ldc) = or += (+-) A . Bt^T with A = a_hi + a_lo [m, kk], Bt = b_hi + b_lo [n, kk], both with
+// leading dimension ldk (a multiple of 4 floats).  flags: GT_* above.  All bases 16-byte aligned.
+int launch_gemm_tc(int64_t m, int64_t n, int64_t kk, const float* a_hi, const float* a_lo, const float* b_hi,
+                   const float* b_lo, int64_t ldk, float* c, int64_t ldc, int flags, int* status,
+                   cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || kk <= 0) return HI2_OK;
+  if (encoder() == nullptr) return fail(HI2_ERR_DRIVER, "gemm_tc: cuTensorMapEncodeTiled unavailable");
+  CUtensorMap mah, mal, mbh, mbl, mc;
+  if (!make_map(&mah, a_hi, kk, m, ldk, 32, LM) || !make_map(&mal, a_lo, kk, m, ldk, 32, LM) ||
+      !make_map(&mbh, b_hi, kk, n, ldk, 32, LN) || !make_map(&mbl, b_lo, kk, n, ldk, 32, LN) ||
+      !make_map(&mc, c, n, m, ldc, 32, 32))
+    return fail(HI2_ERR_DRIVER, "gemm_tc: cuTensorMapEncodeTiled failed");
+  if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L_SMEM) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "gemm_tc: cannot reserve shared memory");
+  GParams p;
+  p.status = status;
+  p.row_tiles = (int)ceil_div(m, LM);
+  p.col_tiles = (int)ceil_div(n, LN);
+  p.kk = (int)kk, p.flags = flags;
+  const int tiles = p.row_tiles * p.col_tiles;
+  int device = 0, sms = 148;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  gemm_tc_kernel<<<tiles < sms ? tiles : sms, L_THREADS, L_SMEM, stream>>>(mah, mal, mbh, mbl, mc, p);
+  return check_launch("gemm_tc");
+}
+
+int launch_split_block(const float* x, int64_t ldx, int64_t rows, int64_t cols, float* hi, float* lo,
+                       int64_t ldo, bool transposed, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return HI2_OK;
+  if (transposed) {
+    dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)ceil_div(rows, 32));
+    split_block_transposed_kernel<<<grid, 256, 0, stream>>>(x, ldx, rows, cols, hi, lo, ldo);
+  } else {
+    int64_t blocks = ceil_div(rows * (cols / 4), 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    split_block_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, ldx, rows, cols, hi, lo, ldo);
+  }
+  return check_launch("split_block");
 }
 
 int launch_split_tf32(const float* x, float* hi, float* lo, int64_t n, cudaStream_t stream) {

@@ -176,6 +176,8 @@ class FactorJob:
         with torch.cuda.stream(self.stream):
             while True:
                 last = int(self.info.item())
+                if last < 0:
+                    raise RuntimeError("inverse_factor: a bounded device-side wait ran out")
                 if last == 0 and bool(torch.isfinite(self.u.diagonal()).all()):
                     self.ws = None
                     return self.u

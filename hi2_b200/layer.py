@@ -73,7 +73,9 @@ def _side_stream(device, i: int) -> torch.cuda.Stream:
     stream, so a fresh stream every step would strand the factorisation scratch of the last one."""
     key = (torch.device(device).index, i)
     if key not in _side_streams:
-        _side_streams[key] = torch.cuda.Stream(device)
+        # high priority: the factorisation is a long chain of small kernels beside table kernels
+        # that fill every SM, and a chain link should not queue behind a full grid
+        _side_streams[key] = torch.cuda.Stream(device, priority=-1)
     return _side_streams[key]
 
 

@@ -206,8 +206,10 @@ int hi2_transform_sigma(const float* sigma, float denom, const uint16_t* col_sca
 
 /* hi2/hessian.py:71-86 inverse_factor, one damping attempt: u = upper Cholesky factor of
  * (hs + *lam * I)^-1 with lam a device fp32 scalar.  *info (device int, caller zeroes it) is
- * set to 1 + index of the first non-positive pivot; u is then unspecified.  Workspace: fp32
- * scratch of hi2_inverse_factor_workspace_bytes(k) = 8 k^2 bytes. */
+ * set to 1 + index of the first non-positive pivot, or to -1 when a bounded device-side wait of
+ * the tensor-core products ran out; u is then unspecified.  Workspace:
+ * hi2_inverse_factor_workspace_bytes(k) bytes, 16-byte aligned (8 k^2 for the two fp32 work
+ * matrices, plus about 4 k^2 for the TF32 operand parts when k >= 2048). */
 size_t hi2_inverse_factor_workspace_bytes(int64_t k);
 int hi2_inverse_factor(const float* hs, const float* lam, int64_t k, float* u, void* workspace,
                        size_t workspace_bytes, int32_t* info, void* stream);

@@ -43,7 +43,8 @@ def test_argument_checks_need_no_device():
     assert b"multiple of 16" in lib.hi2_last_error()
     assert lib.hi2_pack_codes(None, None, 1, 15, 2, None, None) == _lib.ERR_ARG
     assert lib.hi2_gptq_lazy_update(None, 0, 128, 0, 128, None, None, None) == _lib.OK
-    assert lib.hi2_inverse_factor_workspace_bytes(1024) == 1024 * 1024 * 8
+    assert lib.hi2_inverse_factor_workspace_bytes(1024) == 1024 * 1024 * 8 + 256
+    assert lib.hi2_inverse_factor_workspace_bytes(4096) == 4096 * 4096 * 8 + 4 * 2048 * 2048 * 4 + 256
     assert lib.hi2_hessian_workspace_bytes(100, 64, _lib.BF16) == 0  # small: FMA path, no scratch
     need = lib.hi2_hessian_workspace_bytes(262144, 4096, _lib.BF16)
     assert need > 0 and need % 4 == 0
