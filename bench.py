@@ -220,7 +220,7 @@ class Job:
             for layer, xs in enumerate(self.inputs):
                 if ready is not None:
                     cur.wait_event(ready[(layer, name)])
-                L.accumulate({name: xs[name]}, self.device, into=shared_all[layer])
+                L.accumulate({name: xs[name]}, self.device, into=shared_all[layer], defer_check=True)
                 s = shared_all[layer][name]  # partial sum of this rank's tokens -> the layer's owner
                 n, work = hd.reduce_second_moment(s.hessian.S, s.hessian.n, hd.owner_of(layer, self.world),
                                                   async_op=True)
@@ -252,6 +252,9 @@ class Job:
         picks = {name: alloc.picks[tag + name] for name in tables}
         self._mark(marks, "encode")
         packed = L.encode(self.weights, self.plan, mine, tables, picks, self.qcfg, to_host=to_host, factors=factors)
+        for sh in shared_all:  # partial sums taken for other ranks' layers: settle their status too
+            for s in sh.values():
+                s.hessian.check()
         self._mark(marks, "end")
         self.last = dict(marks=marks, alloc=alloc, packed=packed)
         return packed

@@ -1,14 +1,9 @@
 // Fixed-ladder GPTQ rounding (hi2/gptq_kernel.py:59-127, hi2/hessian.py:267-315).
 //
-// Block kernel: one WARP per row.  A lane keeps four consecutive columns of the row's 128-column
-// segment in registers together with their ladder (lo, step).  Column i is rounded by the lane
-// that owns it; its scaled error reaches the other lanes with one shuffle and every lane
-// subtracts e * U[j, c] from its columns c > i.  Rows of U are read as one 128-bit load per lane
-// (a contiguous 512-byte line per warp, served from L1/L2 since every warp of the same factor
-// walks the same rows) and fetched two rows ahead of their use, so the dependent chain per
-// column is shuffle + ~10 arithmetic instructions.  Each product, sum and quotient is rounded
-// on its own (the library is built without FMA contraction) and wq is rounded to fp16 before the
-// error is formed, so given the same inputs the codes equal those of the column-by-column loop.
+// Block kernel: one LANE per row (see gptq_block_kernel).  Each product, sum and quotient is
+// rounded on its own (the library is built without FMA contraction) and wq is rounded to fp16
+// before the error is formed, so given the same inputs the codes equal those of the
+// column-by-column loop.
 //
 // Trailing update: wc[:, i2:] -= err1 @ U[i1:i2, i2:] in fp32 FMA arithmetic (gemm.cuh).
 #include "gemm.cuh"
@@ -23,97 +18,242 @@ int launch_split_tf32(const float* x, float* hi, float* lo, int64_t n, cudaStrea
 namespace {
 
 constexpr int LMAX = 128;
-constexpr int ROWS_PER_CTA = 8;
+constexpr int ROWS_PER_CTA = 64;  // one lane per row; three thread blocks (and staged factor blocks) per SM
+
+// One LANE per row.  The row's segment of up to 128 columns lives in registers as 64 pairs and
+// moves down by one pair every two steps, so the columns being rounded are always the first
+// pair, every register index is static and two steps are a compact loop body.  The updates use
+// a packed fp32 multiply for two columns at a time (see sub_scaled):
+// new pair[t] = pair[t+1] - eA * U[j, ..] - eB * U[j+1, ..].  The block
+// U[i1:i1+len, i1:i1+len] is staged in shared memory with every row already shifted to the
+// column its first pair starts at, where U[j, c] is the same address for every lane (a
+// broadcast), and the dependent chain of a column carries no shuffle.  The loop is
+// software-pipelined: the error of column j is applied while column j+1 is rounded from the one
+// value it needs, and so on, so the chains run inside the updates instead of between them.  The
+// live width shrinks in four phases (128, 96, 64, 32 registers) as the columns are used up.
+// Rows of one thread block that read different factors (a block that straddles two tensors) are
+// served one factor after the other.
+constexpr int U_DIAG = LMAX * LMAX;          // diagonal U[j, j] (padded with ones)
+constexpr int U_NEXT = U_DIAG + 2 * LMAX;    // U[j, j+1]
+constexpr int U_STAGE_FLOATS = U_NEXT + LMAX;
+
+// pair - e * (u0, u1) with the product and the difference rounded separately.  The product is one
+// packed multiply; the two additions stay scalar on purpose: a packed multiply feeding a packed
+// add is contracted into a packed FMA by the assembler even with contraction switched off, and
+// a fused update no longer gives the codes of the reference's separately rounded one.
+__device__ __forceinline__ float2 sub_scaled(float2 w, float2 neg_e, float u0, float u1) {
+  const float2 p = __fmul2_rn(neg_e, make_float2(u0, u1));
+  return make_float2(w.x + p.x, w.y + p.y);
+}
+
+struct Ladder {
+  float lo, st;
+};
+
+// Code and scaled error of one column (hi2/gptq_kernel.py:88-101): exactly the IEEE quotients
+// the reference forms.  The fast path (one reciprocal product per division) is computed
+// unconditionally and redone with true divisions in the rare unsafe case, so the common path is
+// straight-line code.
+__device__ __forceinline__ void round_column(float col, Ladder p, float ud, float nm, float& q_out, float& e_out) {
+  const float safe = (p.st == 0.0f) ? 1.0f : p.st;
+  const Recip rs = make_recip(safe), ru = make_recip(ud);
+  const float a = col - p.lo;
+  const float t = a * rs.r;
+  float q = rintf(t);
+  const bool near = fabsf(fabsf(t - q) - 0.5f) < 2.5e-4f && fabsf(t) < 1024.0f;
+  if (!rs.fast || !ru.fast || near) {  // rare
+    q = rintf(__fdiv_rn(a, safe));
+    q = (q < 0.0f) ? 0.0f : q;
+    q = (q > nm) ? nm : q;
+    if (p.st == 0.0f) q = 0.0f;
+    const float wq = round_f16(p.lo + q * p.st);
+    q_out = q;
+    e_out = __fdiv_rn(col - wq, ud);
+    return;
+  }
+  q = (q < 0.0f) ? 0.0f : q;
+  q = (q > nm) ? nm : q;
+  if (p.st == 0.0f) q = 0.0f;
+  const float wq = round_f16(p.lo + q * p.st);
+  const float num = col - wq;
+  const float q0 = num * ru.r;
+  q_out = q;
+  e_out = fmaf(fmaf(-q0, ud, num), ru.r, q0);
+}
+
+// Per-row state between steps.  Everything that a load fills is addressed by column modulo 4 with
+// the step loop unrolled four times, so a value in flight is never moved: a register copy of it
+// would wait for the load and put its latency back on every step.
+template <bool WITH_COMP>
+struct RowState {
+  int j;      // the column whose error is applied next (a multiple of 4 between iterations)
+  float e;    // its scaled error
+  float ev[4], cv[4];  // outputs of the current quad of columns
+  uint32_t qk;
+  Ladder p[4];  // ladders of columns j+1 .. j+4
+  int b[4];     // block indices of columns j+5 .. j+8
+};
+
+// Steps while more than W - 32 columns remain (W registers live: w[0] holds columns s.j, s.j+1).
+template <int W, bool WITH_COMP>
+__device__ __forceinline__ void run_phase(float2 (&w)[LMAX / 2], RowState<WITH_COMP>& s, int len, float nm,
+                                          const float* __restrict__ u_stage, const int32_t* __restrict__ brow,
+                                          const float* __restrict__ lorow, const float* __restrict__ strow,
+                                          bool live, float* err_row, uint8_t* code_row, float* comp_row) {
+  const int last = len - 1;
+  constexpr int P = W / 2;  // live pairs
+#pragma unroll 1
+  while (len - s.j > W - 32 && s.j < len) {
+    const int j0 = s.j;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int j = j0 + 2 * h;                      // even: the column whose error is known
+      const float* ua = u_stage + j * LMAX;          // ua[t] = U[j, j+2+t]
+      const float* ub = ua + LMAX;                   // ub[t] = U[j+1, j+2+t]
+      const float ea = s.e;
+      // column j+1: one scalar update, then its rounding (overlaps the packed updates below)
+      const float cb = w[0].y - ea * u_stage[U_NEXT + j];
+      float qb, eb;
+      round_column(cb, s.p[(2 * h + 1) & 3], u_stage[U_DIAG + j + 1], nm, qb, eb);
+      const float2 na = make_float2(-ea, -ea);
+#pragma unroll
+      for (int t = 0; t + 1 < P; t += 2) {
+        const float4 v = *reinterpret_cast<const float4*>(ua + 2 * t);
+        w[t] = sub_scaled(w[t + 1], na, v.x, v.y);
+        if (t + 2 < P) w[t + 1] = sub_scaled(w[t + 2], na, v.z, v.w);
+      }
+      w[P - 1] = make_float2(0.0f, 0.0f);
+      // column j+2 (ignored past the last column)
+      const float4 fb = *reinterpret_cast<const float4*>(ub);
+      const float ca = w[0].x - eb * fb.x;
+      float qa, ea2;
+      round_column(ca, s.p[(2 * h + 2) & 3], u_stage[U_DIAG + j + 2], nm, qa, ea2);
+      const float2 nb = make_float2(-eb, -eb);
+      w[0] = sub_scaled(w[0], nb, fb.x, fb.y);
+      if (1 < P) w[1] = sub_scaled(w[1], nb, fb.z, fb.w);
+#pragma unroll
+      for (int t = 2; t < P; t += 2) {
+        const float4 v = *reinterpret_cast<const float4*>(ub + 2 * t);
+        w[t] = sub_scaled(w[t], nb, v.x, v.y);
+        if (t + 1 < P) w[t + 1] = sub_scaled(w[t + 1], nb, v.z, v.w);
+      }
+      // outputs of columns j+1 and j+2 (slot 3 completes the quad j0 .. j0+3, slot 0 opens the next)
+      const int sb = (2 * h + 1) & 3, sa = (2 * h + 2) & 3;
+      s.ev[sb] = eb;
+      if (WITH_COMP) s.cv[sb] = cb;
+      s.qk = (s.qk >> 8) | ((uint32_t)qb << 24);
+      if (sb == 3 && live) {
+        *reinterpret_cast<float4*>(err_row + j0) = make_float4(s.ev[0], s.ev[1], s.ev[2], s.ev[3]);
+        *reinterpret_cast<uint32_t*>(code_row + j0) = s.qk;
+        if (WITH_COMP) *reinterpret_cast<float4*>(comp_row + j0) = make_float4(s.cv[0], s.cv[1], s.cv[2], s.cv[3]);
+      }
+      s.ev[sa] = ea2;
+      if (WITH_COMP) s.cv[sa] = ca;
+      s.qk = (s.qk >> 8) | ((uint32_t)qa << 24);
+      // ladders of columns j+5 and j+6 into the slots just used, block indices of j+9 and j+10 behind them
+      s.p[sb].lo = lorow[s.b[sb]], s.p[sb].st = strow[s.b[sb]];
+      s.b[sb] = brow[min(j + 9, last)];
+      s.p[sa].lo = lorow[s.b[sa]], s.p[sa].st = strow[s.b[sa]];
+      s.b[sa] = brow[min(j + 10, last)];
+      s.e = ea2;
+    }
+    s.j = j0 + 4;
+  }
+}
 
 template <bool WITH_COMP>
-__global__ void __launch_bounds__(ROWS_PER_CTA * 32, 3)
+__global__ void __launch_bounds__(ROWS_PER_CTA, 3)
 gptq_block_kernel(const float* __restrict__ wc, int64_t n_rows, int64_t k, int64_t i1, int len,
                   float* __restrict__ err1, uint8_t* __restrict__ codes,
                   const float* __restrict__ lo, const float* __restrict__ st, int64_t ldp,
                   const int32_t* __restrict__ row_grp, const int64_t* __restrict__ u_ptrs,
                   const int32_t* __restrict__ blk, const float* __restrict__ nmax,
                   float* __restrict__ comp) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
-  if (row >= n_rows) return;  // whole warp
-  const int c0 = lane * 4;
-  const bool mine = c0 < len;  // len is a multiple of 16: a quad is entirely inside or outside
+  extern __shared__ float4 u_stage4[];
+  float* u_stage = reinterpret_cast<float*>(u_stage4);
+  __shared__ unsigned long long next_factor;
+
+  const int64_t row_raw = (int64_t)blockIdx.x * ROWS_PER_CTA + threadIdx.x;
+  const bool live = row_raw < n_rows;
+  const int64_t row = live ? row_raw : n_rows - 1;  // spare lanes shadow the last row and store nothing
   const int g = row_grp[row];
-  const float* __restrict__ u = reinterpret_cast<const float*>(u_ptrs[g]);
+  const unsigned long long my_factor = (unsigned long long)u_ptrs[g];
   const float nm = nmax[g];
-
-  float w[4] = {0.f, 0.f, 0.f, 0.f}, lo_c[4] = {0.f, 0.f, 0.f, 0.f}, st_c[4] = {0.f, 0.f, 0.f, 0.f};
-  if (mine) {
-    const float4 v = *reinterpret_cast<const float4*>(wc + row * k + i1 + c0);
-    w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
-    const int4 b = *reinterpret_cast<const int4*>(blk + (int64_t)g * k + i1 + c0);
-    const int bs[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int s = 0; s < 4; ++s) lo_c[s] = lo[row * ldp + bs[s]], st_c[s] = st[row * ldp + bs[s]];
-  }
-  float q_keep[4] = {0.f, 0.f, 0.f, 0.f}, e_keep[4] = {0.f, 0.f, 0.f, 0.f},
-        col_keep[4] = {0.f, 0.f, 0.f, 0.f};
-  // Reciprocals of the two divisors of a column, taken off the dependent chain: the ladder
-  // step of the column's block and the diagonal entry of U.  rint_div / div_by give exactly the
-  // IEEE quotients the reference forms.
-  Recip rc_st[4], rc_u[4];
-  float udiag[4];
-#pragma unroll
-  for (int s = 0; s < 4; ++s) {
-    const int64_t j = i1 + c0 + s;
-    udiag[s] = mine ? u[j * k + j] : 1.0f;
-    rc_u[s] = make_recip(udiag[s]);
-    rc_st[s] = make_recip((st_c[s] == 0.0f) ? 1.0f : st_c[s]);
-  }
-
-  // rows i1 .. i1+len-1 of U, this lane's four columns, held two rows ahead of their use in a
-  // ring of four registers-quads: rows i, i+1 are in ring[0..1] when a group of four steps starts,
-  // rows i+2, i+3 are requested then, and the first two rows of the next group as soon as steps
-  // 0 and 1 have consumed theirs
-  const float* urow = u + i1 * k + i1 + c0;
+  const float* wrow = wc + row * k + i1;
+  const int32_t* brow = blk + (int64_t)g * k + i1;
+  const float* lorow = lo + row * ldp;
+  const float* strow = st + row * ldp;
+  float* err_row = err1 + row * len;
+  uint8_t* code_row = codes + row * k + i1;
+  float* comp_row = WITH_COMP ? comp + row * k + i1 : nullptr;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  auto fetch = [&](int r) {
-    return (mine && r < len) ? *reinterpret_cast<const float4*>(urow + (int64_t)r * k) : zero4;
-  };
-  float4 ring[4];
-  ring[0] = fetch(0), ring[1] = fetch(1);
+  const int last = len - 1;
 
-  for (int i = 0; i < len; i += 4) {
-    ring[2] = fetch(i + 2), ring[3] = fetch(i + 3);
-    const int owner = i >> 2;
-#pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const float us[4] = {ring[s].x, ring[s].y, ring[s].z, ring[s].w};
-      if (s == 2) ring[0] = fetch(i + 4), ring[1] = fetch(i + 5);
-      // every lane evaluates slot s of its own quad; only the owner's result is used
-      const float col = w[s], lo_j = lo_c[s], st_j = st_c[s];
-      const float safe = (st_j == 0.0f) ? 1.0f : st_j;
-      float q = rint_div(col - lo_j, safe, rc_st[s]);
-      q = (q < 0.0f) ? 0.0f : q;
-      q = (q > nm) ? nm : q;
-      if (st_j == 0.0f) q = 0.0f;
-      const float wq = round_f16(lo_j + q * st_j);
-      const float e_own = div_by(col - wq, udiag[s], rc_u[s]);
-      const float e = __shfl_sync(0xffffffffu, e_own, owner);
-      if (lane == owner) {
-        q_keep[s] = q, e_keep[s] = e_own;
-        if (WITH_COMP) col_keep[s] = col;
+  bool done = false;
+  while (true) {
+    if (threadIdx.x == 0) next_factor = ~0ull;
+    __syncthreads();
+    if (!done) atomicMin(&next_factor, my_factor);
+    __syncthreads();
+    const unsigned long long factor = next_factor;
+    if (factor == ~0ull) break;
+    {
+      // u_stage[j][t] = U[i1+j, i1+first(j)+t] with first(j) = j+2 for even j and j+1 for odd j (zero
+      // past the segment); then the diagonal and U[j, j+1]
+      const float* src = reinterpret_cast<const float*>(factor) + i1 * k + i1;
+      for (int idx = threadIdx.x; idx < LMAX * LMAX / 4; idx += ROWS_PER_CTA)
+        u_stage4[idx] = zero4;
+      __syncthreads();
+      const int quads = len / 4;
+      for (int idx = threadIdx.x; idx < len * quads; idx += ROWS_PER_CTA) {
+        const int j = idx / quads, c = (idx % quads) * 4;
+        const int first = j + 2 - (j & 1);
+        if (c + 3 < first) continue;
+        const float4 v = *reinterpret_cast<const float4*>(src + j * k + c);
+        float* dst = u_stage + j * LMAX + (c - first);
+        if (c >= first) dst[0] = v.x;
+        if (c + 1 >= first) dst[1] = v.y;
+        if (c + 2 >= first) dst[2] = v.z;
+        dst[3] = v.w;
       }
-      // all four columns, as the reference updates w1[:, i:]: columns up to this one are never
-      // read again (and U is upper triangular, so their factor entries are zero anyway)
-#pragma unroll
-      for (int t = 0; t < 4; ++t) w[t] = w[t] - e * us[t];
+      for (int idx = threadIdx.x; idx < 2 * LMAX; idx += ROWS_PER_CTA)
+        u_stage[U_DIAG + idx] = idx < len ? src[idx * k + idx] : 1.0f;
+      for (int idx = threadIdx.x; idx < LMAX; idx += ROWS_PER_CTA)
+        u_stage[U_NEXT + idx] = idx + 1 < len ? src[idx * k + idx + 1] : 0.0f;
     }
-  }
-
-  if (mine) {
-    *reinterpret_cast<float4*>(err1 + row * len + c0) =
-        make_float4(e_keep[0], e_keep[1], e_keep[2], e_keep[3]);
-    *reinterpret_cast<uchar4*>(codes + row * k + i1 + c0) =
-        make_uchar4((uint8_t)q_keep[0], (uint8_t)q_keep[1], (uint8_t)q_keep[2], (uint8_t)q_keep[3]);
-    if (WITH_COMP)
-      *reinterpret_cast<float4*>(comp + row * k + i1 + c0) =
-          make_float4(col_keep[0], col_keep[1], col_keep[2], col_keep[3]);
+    __syncthreads();
+    if (!done && my_factor == factor) {
+      done = true;
+      float2 w[LMAX / 2];
+#pragma unroll
+      for (int q = 0; q < LMAX / 4; ++q) {
+        const float4 v = (4 * q < len) ? *reinterpret_cast<const float4*>(wrow + 4 * q) : zero4;
+        w[2 * q] = make_float2(v.x, v.y), w[2 * q + 1] = make_float2(v.z, v.w);
+      }
+      RowState<WITH_COMP> s;
+      s.j = 0, s.qk = 0;
+      auto ladder = [&](int c) {
+        const int b = brow[min(c, last)];
+        Ladder p;
+        p.lo = lorow[b], p.st = strow[b];
+        return p;
+      };
+#pragma unroll
+      for (int c = 1; c <= 4; ++c) s.p[c & 3] = ladder(c), s.b[c & 3] = brow[min(c + 4, last)];
+      {  // column 0 opens the pipeline
+        float q0, e0;
+        round_column(w[0].x, ladder(0), u_stage[U_DIAG], nm, q0, e0);
+        s.ev[0] = e0, s.ev[1] = s.ev[2] = s.ev[3] = 0.0f;
+        s.cv[0] = w[0].x, s.cv[1] = s.cv[2] = s.cv[3] = 0.0f;
+        s.qk = (uint32_t)q0 << 24;
+        s.e = e0;
+      }
+      run_phase<128, WITH_COMP>(w, s, len, nm, u_stage, brow, lorow, strow, live, err_row, code_row, comp_row);
+      run_phase<96, WITH_COMP>(w, s, len, nm, u_stage, brow, lorow, strow, live, err_row, code_row, comp_row);
+      run_phase<64, WITH_COMP>(w, s, len, nm, u_stage, brow, lorow, strow, live, err_row, code_row, comp_row);
+      run_phase<32, WITH_COMP>(w, s, len, nm, u_stage, brow, lorow, strow, live, err_row, code_row, comp_row);
+    }
+    __syncthreads();  // the staged block is replaced in the next round
   }
 }
 
@@ -122,14 +262,16 @@ int launch_block(const float* wc, int64_t n_rows, int64_t k, int64_t i1, int len
                  const int32_t* row_grp, const int64_t* u_ptrs, const int32_t* blk,
                  const float* nmax, float* comp, cudaStream_t stream) {
   const unsigned grid = (unsigned)ceil_div(n_rows, ROWS_PER_CTA);
+  const int smem = U_STAGE_FLOATS * (int)sizeof(float);
+  if (cudaFuncSetAttribute(gptq_block_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+      cudaFuncSetAttribute(gptq_block_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "gptq_block: cannot reserve shared memory");
   if (comp != nullptr)
-    gptq_block_kernel<true><<<grid, ROWS_PER_CTA * 32, 0, stream>>>(wc, n_rows, k, i1, len, err1, codes,
-                                                                    lo, st, ldp, row_grp, u_ptrs, blk,
-                                                                    nmax, comp);
+    gptq_block_kernel<true><<<grid, ROWS_PER_CTA, smem, stream>>>(wc, n_rows, k, i1, len, err1, codes, lo, st,
+                                                               ldp, row_grp, u_ptrs, blk, nmax, comp);
   else
-    gptq_block_kernel<false><<<grid, ROWS_PER_CTA * 32, 0, stream>>>(wc, n_rows, k, i1, len, err1, codes,
-                                                                     lo, st, ldp, row_grp, u_ptrs, blk,
-                                                                     nmax, comp);
+    gptq_block_kernel<false><<<grid, ROWS_PER_CTA, smem, stream>>>(wc, n_rows, k, i1, len, err1, codes, lo, st,
+                                                                ldp, row_grp, u_ptrs, blk, nmax, comp);
   return check_launch("gptq_block");
 }
 

@@ -64,12 +64,26 @@ class HessianStats:
         self.k = k
         self.S = torch.zeros(k, k, dtype=torch.float32, device=device)
         self.n = 0
+        self._unchecked: list = []  # status words of launches whose outcome nobody has read yet
+
+    def check(self) -> None:
+        """Raise if a launch made with ``defer_check=True`` gave up on a bounded device-side wait
+        (synchronises with those launches)."""
+        pending, self._unchecked = self._unchecked, []
+        for word in pending:
+            status = int(word.item())
+            if status:
+                raise RuntimeError(
+                    f"hessian_accumulate: a bounded device-side wait ran out (status {status})"
+                )
 
     @torch.no_grad()
-    def update(self, x: torch.Tensor, chunk: int = 4096) -> None:
+    def update(self, x: torch.Tensor, chunk: int = 4096, defer_check: bool = False) -> None:
         """``S += x^T x`` for ``x [..., K]``.  bf16 / fp16 activations feed the tensor cores
         directly (their products are exact in fp32); anything else is taken as fp32.  ``chunk``
-        is accepted for compatibility: the kernel splits the tokens itself."""
+        is accepted for compatibility: the kernel splits the tokens itself.  The tensor-core
+        kernel leaves a status word; reading it costs a synchronisation, which callers that
+        pipeline several inputs postpone with ``defer_check=True`` and settle with :meth:`check`."""
         del chunk
         dev = _lib.need_cuda(self.S)
         x = x.reshape(-1, self.k)
@@ -90,11 +104,9 @@ class HessianStats:
             _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.stream(dev),
         )
         if ws is not None:
-            status = int(ws[:4].view(torch.int32).item())
-            if status:
-                raise RuntimeError(
-                    f"hessian_accumulate: a bounded device-side wait ran out (status {status})"
-                )
+            self._unchecked.append(ws[:4].view(torch.int32).clone())  # the scratch is shared
+            if not defer_check:
+                self.check()
         self.n += tokens
 
     def merge(self, other: "HessianStats") -> None:

@@ -41,15 +41,16 @@ class LayerPlan:
     reads: dict = field(default_factory=dict)
 
 
-def accumulate(inputs: dict, device, into: dict | None = None) -> dict:
+def accumulate(inputs: dict, device, into: dict | None = None, defer_check: bool = False) -> dict:
     """``{input name: activations [tokens, k]}`` -> ``{input name: SharedInput}`` with the second
-    moment summed (``into`` continues earlier sums: more tokens, or another rank's shard)."""
+    moment summed (``into`` continues earlier sums: more tokens, or another rank's shard).  With
+    ``defer_check`` the launches are not waited for; :func:`encode` settles their status."""
     out = into if into is not None else {}
     for name, x in inputs.items():
         k = x.shape[-1]
         if name not in out:
             out[name] = SharedInput(name, k, HessianStats(k, device))
-        out[name].hessian.update(x)
+        out[name].hessian.update(x, defer_check=defer_check)
     return out
 
 
@@ -113,6 +114,8 @@ def encode(weights: dict, plan: LayerPlan, shared: dict, tables: dict, picks: di
            to_host: bool = True, factors: dict | None = None) -> dict:
     """Packed ``HI2Tensor`` of every weight for the allocator's ``picks``."""
     reqs, names = [], []
+    for s in shared.values():
+        s.hessian.check()
     for name, w in weights.items():
         s = shared[plan.reads[name]]
         reqs.append(EncodeRequest(w, s.moments, tables[name], picks[name], sigma=s.hessian.S,
