@@ -35,7 +35,7 @@ def test_routed_second_moments_match_oracle():
         o.update(xe)
         assert hess[ei].n == o.n == stats[ei].n
         err = (hess[ei].S.cpu().double() - o.S.double()).norm() / o.S.double().norm()
-        assert err < 2e-6
+        assert err < 1e-5  # both sides sum in fp32; the same bar as the dense second-moment tests
         og = po.GroupMoments(k)
         og.update(xe)
         assert (stats[ei].S.cpu() - og.S).norm() / og.S.norm() < 1e-6
