@@ -18,47 +18,52 @@ struct GridSpec {
   int g;
 };
 
-// Weighted error of a block under ladder (lo, step).  The codes are rint((x - lo) / safe); one
-// correctly rounded reciprocal of `safe` serves the whole block: (x - lo) * r is within
-// 1.8e-7 * |q| of the IEEE quotient q, so the two round to the same integer unless the product
-// lies that close to a half-integer inside the ladder (outside it both clamp to the same end).
-// The block keeps the smallest distance to a half-integer it met; in the rare case (one warp
-// iteration in 10^2..10^3) that it is below the bound, the block is redone with IEEE divisions,
-// so the result is always the one the divisions give.
-template <int B>
-__device__ __forceinline__ float block_error(const float (&x)[B], const float* __restrict__ xs,
-                                             const float* __restrict__ dd, float lo, float step,
-                                             float nmax, float near_half) {
+// Codes are rint((x - lo) / safe) with an IEEE division in the reference.  Here one correctly
+// rounded reciprocal of `safe` serves the block and every quotient is finished with Markstein's
+// fused correction (div_by), which yields the correctly rounded quotient itself, so rint sees the
+// very number the division would give.  Divisors outside the range the correction covers
+// (rc.fast false: tiny, huge, or a significand of all ones) take true divisions.
+//
+// WIDE (blocks of 16 and 32): the column weights d and the differences x - lo of the current grid
+// row are kept in registers next to x, which removes one load and one subtraction per element
+// and pass; a block of 64 has no registers to spare for that.
+template <int B, bool WIDE>
+struct BlockRegs {
+  float x[B];
+  float d[WIDE ? B : 1];
+  float a[WIDE ? B : 1];  // x - lo of the current lo
+};
+
+template <int B, bool WIDE>
+__device__ __forceinline__ float block_error(const BlockRegs<B, WIDE>& r, const float* __restrict__ dd,
+                                             bool a_valid, float lo, float step, float nmax) {
   const float safe = (step == 0.0f) ? 1.0f : step;
   const Recip rc = make_recip(safe);
-  float err = 0.0f, margin = 1.0f;
+  float err = 0.0f;
+  if (rc.fast) {
 #pragma unroll
-  for (int t = 0; t < B; ++t) {
-    const float tt = (x[t] - lo) * rc.r;
-    float q = rintf(tt);
-    margin = fminf(margin, fabsf(fabsf(tt - q) - 0.5f));
-    q = fminf(fmaxf(q, 0.0f), nmax);
-    const float diff = (lo + q * step) - x[t];
-    err += __ldg(dd + t) * (diff * diff);
-  }
-  if (!rc.fast || !(margin >= near_half)) {
-    // rare: redo the block with IEEE divisions, re-reading the weights (xs, an L1/L2 hit) so
-    // that the register copy x[] is never indexed dynamically
-    err = 0.0f;
-#pragma unroll 1
     for (int t = 0; t < B; ++t) {
-      const float xv = __ldg(xs + t);
-      float q = rintf(__fdiv_rn(xv - lo, safe));
+      const float num = (WIDE && a_valid) ? r.a[t] : r.x[t] - lo;
+      const float q0 = num * rc.r;
+      float q = rintf(fmaf(fmaf(-q0, safe, num), rc.r, q0));
       q = fminf(fmaxf(q, 0.0f), nmax);
-      const float diff = (lo + q * step) - xv;
-      err += __ldg(dd + t) * (diff * diff);
+      const float diff = (lo + q * step) - r.x[t];
+      err += (WIDE ? r.d[t] : __ldg(dd + t)) * (diff * diff);
+    }
+  } else {
+#pragma unroll
+    for (int t = 0; t < B; ++t) {
+      float q = rintf(__fdiv_rn(r.x[t] - lo, safe));
+      q = fminf(fmaxf(q, 0.0f), nmax);
+      const float diff = (lo + q * step) - r.x[t];
+      err += (WIDE ? r.d[t] : __ldg(dd + t)) * (diff * diff);
     }
   }
   return err;
 }
 
-template <int B>
-__global__ void __launch_bounds__(256, (B == 16 ? 4 : 2))  // register caps 64 / 128 / 128: occupancy matters more than the spare registers
+template <int B, bool WIDE>
+__global__ void __launch_bounds__(256, (B == 16 ? 3 : 2))
 fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, int64_t n_rows,
            int64_t nb, GridSpec grid, int refits, float nmax, float* __restrict__ lo_out,
            float* __restrict__ st_out, float* __restrict__ err_out) {
@@ -70,24 +75,32 @@ fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d
   const float* src = w + (live ? row : n_rows - 1) * ldw + blk * B;
   const float* dd = d + blk * B;
 
-  float x[B];
+  BlockRegs<B, WIDE> r;
 #pragma unroll
   for (int t = 0; t < B; t += 4) {
     const float4 v = *reinterpret_cast<const float4*>(src + t);
-    x[t] = v.x, x[t + 1] = v.y, x[t + 2] = v.z, x[t + 3] = v.w;
+    r.x[t] = v.x, r.x[t + 1] = v.y, r.x[t + 2] = v.z, r.x[t + 3] = v.w;
+    if (WIDE) {
+      const float4 dv = __ldg(reinterpret_cast<const float4*>(dd + t));
+      r.d[t] = dv.x, r.d[t + 1] = dv.y, r.d[t + 2] = dv.z, r.d[t + 3] = dv.w;
+    }
   }
-  float mn = x[0], mx = x[0];
+  float mn = r.x[0], mx = r.x[0];
 #pragma unroll
-  for (int t = 1; t < B; ++t) mn = fminf(mn, x[t]), mx = fmaxf(mx, x[t]);
+  for (int t = 1; t < B; ++t) mn = fminf(mn, r.x[t]), mx = fmaxf(mx, r.x[t]);
   const float span = mx - mn;
-  const float near_half = 2.5e-7f * (nmax + 2.0f);  // see block_error
+  const Recip rc_n = make_recip(nmax);  // nmax is 3, 15 or 255: div_by is the IEEE quotient
 
   float best_lo = 0.0f, best_st = 0.0f, best_err = 0.0f;
   for (int gi = 0; gi < grid.g; ++gi) {
     const float lo = mn + grid.v[gi] * span;
+    if (WIDE) {
+#pragma unroll
+      for (int t = 0; t < B; ++t) r.a[t] = r.x[t] - lo;
+    }
     for (int gj = 0; gj < grid.g; ++gj) {
-      const float step = __fdiv_rn((mx - grid.v[gj] * span) - lo, nmax);
-      const float err = block_error<B>(x, src, dd, lo, step, nmax, near_half);
+      const float step = div_by((mx - grid.v[gj] * span) - lo, nmax, rc_n);
+      const float err = block_error<B, WIDE>(r, dd, true, lo, step, nmax);
       if ((gi | gj) == 0 || err < best_err) best_lo = lo, best_st = step, best_err = err;
     }
   }
@@ -95,42 +108,31 @@ fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d
   for (int it = 0; it < refits; ++it) {
     const float safe = (best_st == 0.0f) ? 1.0f : best_st;
     const Recip rc = make_recip(safe);
-    float sd = 0.f, sc = 0.f, scc = 0.f, sw = 0.f, scw = 0.f, sum = 0.f, margin = 1.0f;
+    float sd = 0.f, sc = 0.f, scc = 0.f, sw = 0.f, scw = 0.f, sum = 0.f;
 #pragma unroll
     for (int t = 0; t < B; ++t) {
-      const float tt = (x[t] - best_lo) * rc.r;
-      float c = rintf(tt);
-      margin = fminf(margin, fabsf(fabsf(tt - c) - 0.5f));
+      const float num = r.x[t] - best_lo;
+      float c;
+      if (rc.fast) {
+        const float q0 = num * rc.r;
+        c = rintf(fmaf(fmaf(-q0, safe, num), rc.r, q0));
+      } else {
+        c = rintf(__fdiv_rn(num, safe));
+      }
       c = fminf(fmaxf(c, 0.0f), nmax);
-      const float dt = __ldg(dd + t), dc = dt * c;
+      const float dt = WIDE ? r.d[t] : __ldg(dd + t), dc = dt * c;
       sd += dt;
       sc += dc;
       scc += dc * c;
-      sw += dt * x[t];
-      scw += dc * x[t];
-      sum += x[t];
-    }
-    if (!rc.fast || !(margin >= near_half)) {  // rare: the same sums with IEEE divisions
-      sd = sc = scc = sw = scw = sum = 0.0f;
-#pragma unroll 1
-      for (int t = 0; t < B; ++t) {
-        const float xv = __ldg(src + t);
-        float c = rintf(__fdiv_rn(xv - best_lo, safe));
-        c = fminf(fmaxf(c, 0.0f), nmax);
-        const float dt = __ldg(dd + t), dc = dt * c;
-        sd += dt;
-        sc += dc;
-        scc += dc * c;
-        sw += dt * xv;
-        scw += dc * xv;
-        sum += xv;
-      }
+      sw += dt * r.x[t];
+      scw += dc * r.x[t];
+      sum += r.x[t];
     }
     const float det = sd * scc - sc * sc;
     const bool ok = fabsf(det) > 1e-20f;
     const float step = ok ? __fdiv_rn(sd * scw - sc * sw, det) : 0.0f;
     const float lo = ok ? __fdiv_rn(sw - step * sc, fmaxf(sd, 1e-20f)) : __fdiv_rn(sum, (float)B);
-    const float err = block_error<B>(x, src, dd, lo, step, nmax, near_half);
+    const float err = block_error<B, WIDE>(r, dd, false, lo, step, nmax);
     if (err < best_err && step > 0.0f) best_lo = lo, best_st = step, best_err = err;
   }
 
@@ -151,7 +153,7 @@ int launch_fit(const float* w, int64_t ldw, const float* d, const float* grid_ho
   dim3 grid((unsigned)ceil_div(n_rows, 32), (unsigned)ceil_div(nb, 8));
   const float nmax = (float)(n - 1);
 #define HI2_FIT(BB)                                                                              \
-  fit_kernel<BB><<<grid, 256, 0, stream>>>(w, ldw, d, n_rows, nb, spec, refits, nmax, lo, st, err)
+  fit_kernel<BB, (BB <= 32)><<<grid, 256, 0, stream>>>(w, ldw, d, n_rows, nb, spec, refits, nmax, lo, st, err)
   if (block == 16) HI2_FIT(16);
   if (block == 32) HI2_FIT(32);
   if (block == 64) HI2_FIT(64);
