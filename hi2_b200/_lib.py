@@ -132,6 +132,16 @@ def stream(device=None):
     return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def upload(t: torch.Tensor, dev: torch.device, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``t`` on ``dev`` as a contiguous tensor of ``dtype``.  A host tensor goes through pinned
+    memory with a non-blocking copy: a plain ``.to(device)`` of pageable memory makes the host wait
+    for everything already queued on the stream, which stalls a pipeline for a few bytes of flags."""
+    dtype = dtype or t.dtype
+    if t.is_cuda:
+        return t.to(dev, dtype).contiguous()
+    return t.to(dtype).contiguous().pin_memory().to(dev, non_blocking=True)
+
+
 def need_cuda(*tensors: torch.Tensor) -> torch.device:
     """All tensors on one CUDA device; this package has no CPU path."""
     dev = None

@@ -45,10 +45,10 @@ def fwht_groups(x: torch.Tensor, flags: torch.Tensor, col_scale: torch.Tensor | 
     out_dtype = out_dtype or x.dtype
     xc = x.contiguous()
     y = torch.empty(xc.shape, dtype=out_dtype, device=dev)
-    fl = flags.to(device=dev, dtype=torch.uint8).contiguous()
+    fl = _lib.upload(flags, dev, torch.uint8)
     cs = None
     if col_scale is not None:
-        cs = col_scale.to(device=dev, dtype=torch.float32).contiguous()
+        cs = _lib.upload(col_scale, dev, torch.float32)
     rows = xc.numel() // k
     _lib.call(
         "hi2_rotate_groups", _lib.ptr(xc), _lib.DTYPES[x.dtype], _lib.ptr(y), _lib.DTYPES[out_dtype],

@@ -130,8 +130,8 @@ def transform_sigma(sigma: torch.Tensor, col_scale: torch.Tensor | None, had: to
     diag = torch.empty(k, dtype=torch.float32, device=dev) if return_diag else None
     cs = None
     if col_scale is not None:
-        cs = col_scale.to(dev, torch.float16).contiguous()
-    flags = had.to(dev, torch.uint8).contiguous()
+        cs = _lib.upload(col_scale, dev, torch.float16)
+    flags = _lib.upload(had, dev, torch.uint8)
     if flags.numel() != k // GROUP:
         raise ValueError(f"had has {flags.numel()} entries, expected {k // GROUP}")
     _lib.call(
@@ -281,13 +281,13 @@ def _round_units(units: list[_Unit], jobs: list[GptqJob], want_comp: bool, split
     offs = [0]
     for n in sizes:
         offs.append(offs[-1] + n)
-    row_grp = torch.repeat_interleave(
+    row_grp = _lib.upload(torch.repeat_interleave(
         torch.arange(len(units), dtype=torch.int32), torch.tensor(sizes)
-    ).to(dev)
+    ), dev)
     us = [jobs[x.job].u.to(dev, torch.float32).contiguous() for x in units]
-    u_ptrs = torch.tensor([u.data_ptr() for u in us], dtype=torch.int64).to(dev)
+    u_ptrs = _lib.upload(torch.tensor([u.data_ptr() for u in us], dtype=torch.int64), dev)
     blk = torch.stack([x.blk_of for x in units]).contiguous()
-    nmax = torch.tensor([2 ** jobs[x.job].nbits - 1 for x in units], dtype=torch.float32).to(dev)
+    nmax = _lib.upload(torch.tensor([2 ** jobs[x.job].nbits - 1 for x in units], dtype=torch.float32), dev)
     codes = torch.empty(total, k, dtype=torch.uint8, device=dev)
     comp = torch.empty(total, k, dtype=torch.float32, device=dev) if want_comp else None
     err1 = torch.empty(total, BLOCK_COLUMNS, dtype=torch.float32, device=dev)
