@@ -350,41 +350,45 @@ def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str |
     ``BATCH_ELEMS`` weights) through one column loop.  With ``comp`` every result carries
     ``Encoded.comp``, the value each code was rounded from."""
     backend = backend or os.environ.get("HI2_GPTQ_BACKEND", "auto")
-    units: list[_Unit] = []
+    # Widths are independent column loops of many short launches.  The jobs of one width are
+    # prepared (ladders, parameter bytes) on the current stream and their column loop is then
+    # handed to a side stream, widest first, so that the preparation of the next width and, e.g.,
+    # the 86 blocks of a 4096 x 11008 matrix run beside the batches of the 4096-wide ones.
+    # Nothing a side stream reads is released before the streams are joined, and status words are
+    # read only after everything is enqueued.
+    by_width: dict[tuple, list[int]] = {}
     for ji, job in enumerate(jobs):
         _lib.need_cuda(job.w, job.u)
         _use_kernel(job.w.device, backend)
-        n_rows, k = job.w.shape
-        step_rows = max(1, ROW_ELEMS // k)
-        for s in range(0, n_rows, step_rows):
-            units.append(_prepare(ji, job, s, step_rows, effort))
-    batches: dict[tuple, list[list[_Unit]]] = {}
-    for x in units:
-        key = (x.wc.device, x.wc.shape[1])
-        bl = batches.setdefault(key, [[]])
-        if bl[-1] and sum(y.wc.numel() for y in bl[-1]) + x.wc.numel() > BATCH_ELEMS:
-            bl.append([])
-        bl[-1].append(x)
-    # Widths are independent column loops of many short launches; each width after the first runs
-    # on a side stream so that, e.g., the 86 blocks of a 4096 x 11008 matrix overlap the batches of
-    # the 4096-wide ones.  Status words are read only after everything is enqueued.
+        by_width.setdefault((job.w.device, job.w.shape[1]), []).append(ji)
+    units: list[_Unit] = []
     splits: dict = {}
     checks: list = []
     joins = []
-    for gi, ((dev, _k), bl) in enumerate(batches.items()):
+    for gi, ((dev, k), jis) in enumerate(sorted(by_width.items(), key=lambda kv: -kv[0][1])):
+        mine: list[_Unit] = []
+        step_rows = max(1, ROW_ELEMS // k)
+        for ji in jis:
+            for s in range(0, jobs[ji].w.shape[0], step_rows):
+                mine.append(_prepare(ji, jobs[ji], s, step_rows, effort))
+        units.extend(mine)
+        bl: list[list[_Unit]] = [[]]
+        for x in mine:
+            if bl[-1] and sum(y.wc.numel() for y in bl[-1]) + x.wc.numel() > BATCH_ELEMS:
+                bl.append([])
+            bl[-1].append(x)
         main = torch.cuda.current_stream(dev)
-        side = main if gi == 0 else _side_stream(dev, gi)
-        if side is not main:
-            side.wait_stream(main)
+        side = _side_stream(dev, gi + 1)
+        side.wait_stream(main)
         with torch.cuda.stream(side):
             for batch in bl:
                 _round_units(batch, jobs, comp, splits, checks)
-                for x in batch:
-                    x.wc = None
-        if side is not main:
-            joins.append((main, side))
+        joins.append((main, side))
     for main, side in joins:
         main.wait_stream(side)
+    for x in units:
+        x.wc = None
+    units.sort(key=lambda x: (x.job, x.s))
     if any(int(st.item()) for st in checks):
         raise RuntimeError("gptq trailing update: a bounded device-side wait ran out")
     per_job: list[list[Encoded]] = [[] for _ in jobs]
