@@ -404,7 +404,10 @@ def run_reference(args, cfg):
 # (profiles/hessian_tc_kernel_k4096_32k_tokens.md): DRAM reads were 2.08 x the bytes of X (L2 absorbs
 # the rest of the tile re-reads), DRAM writes the per-item output tiles.  Reads grow in proportion
 # to the tokens, the tiles do not, so a full-size launch is scaled from those two figures.
-HESSIAN_READ_FACTOR = 2.08
+# DRAM reads of the second-moment kernel as a multiple of the bytes of X, from ncu captures at
+# 32768 tokens: 1.78 at K = 4096 (X of a wave fits in L2), 6.2 at K = 11008 (banded tile schedule,
+# ~13 waves, the L2 absorbs about half of them)
+HESSIAN_READ_FACTOR = {4096: 1.78, 11008: 6.2}
 
 
 def hessian_traffic(widths, tokens, elem_bytes=2):
@@ -415,7 +418,8 @@ def hessian_traffic(widths, tokens, elem_bytes=2):
         tiles = sum(njb - (ib >> 1) for ib in range(nib))
         kblocks = -(-tokens // 64)
         splits = max(1, min(-(-148 * 6 // tiles), max(1, kblocks // 64)))
-        total += HESSIAN_READ_FACTOR * tokens * k * elem_bytes + splits * tiles * 128 * 256 * 4
+        factor = HESSIAN_READ_FACTOR.get(k, 1.78 if k <= 4096 else 6.2)
+        total += factor * tokens * k * elem_bytes + splits * tiles * 128 * 256 * 4
     return total / max(1, len(widths))
 
 
@@ -512,7 +516,7 @@ def run_ours(args, cfg):
         "effective": algo / hess_s / 1e12,
         "note": "achieved counts the flops issued (upper-triangle 128x256 tiles); effective counts 2*T*K^2",
         "traffic": hessian_traffic(job.widths, cfg["tokens"]),
-        "traffic_note": "bytes per launch, scaled from an ncu capture at 32768 tokens (reads 2.08 x X, plus item tiles)",
+        "traffic_note": "bytes per launch, scaled from ncu captures at 32768 tokens (reads 1.78 x X at K=4096, 6.2 x X at K=11008, plus item tiles)",
         "algorithmic_bytes": sum(cfg["tokens"] * k * 2 + 4 * k * k for k in job.widths.values()) / max(1, len(job.widths)),
         "launch_ms": hess_s * 1e3 / max(1, len(job.widths) * world),
     }
