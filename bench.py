@@ -103,7 +103,7 @@ class Clocks:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -397,7 +397,7 @@ def run_reference(args, cfg):
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ncu capture of the second-moment kernel at 32768 tokens x 4096 columns
@@ -434,9 +434,6 @@ def mem_available_bytes() -> int:
 
 
 def run_ours(args, cfg):
-    # NCCL prints its version banner on stdout when NCCL_DEBUG asks for it; stdout carries the one
-    # JSON line, so the banner goes to stderr unless the caller chose a file already
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     import torch.distributed as dist
 
     from hi2_b200 import _lib
@@ -542,10 +539,30 @@ def run_ours(args, cfg):
         "gpu_launches": launches, "clocks": clock_info,
     }
     del gptq_rows_per_s
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT = None  # the process's original stdout, kept for the one JSON line
+
+
+def guard_stdout():
+    """stdout carries exactly one JSON line.  Libraries print there too (NCCL writes its version
+    banner to file descriptor 1 when NCCL_DEBUG asks for it), so descriptor 1 is pointed at stderr
+    for the rest of the process and the line goes to a duplicate of the original."""
+    global _RESULT
+    sys.stdout.flush()
+    _RESULT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(line: dict):
+    out = _RESULT if _RESULT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 def main():
+    guard_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
