@@ -2,8 +2,9 @@
 
 The cost tables never leave the device: each multiplier of the bisection is one kernel launch
 (first-minimum argmin of ``cost + lam * bits`` in fp64 plus the exact sum of the picked bits) and
-eight bytes back to the host, which keeps the reference's bisection (geometric midpoints in
-Python floats, 80 iterations) and therefore its picks bit for bit.
+a few bytes back to the host, which keeps the reference's bisection (geometric midpoints in
+Python floats, 80 iterations) and therefore its picks bit for bit; five bisection steps share
+one launch and one read-back.
 """
 
 from __future__ import annotations
@@ -89,7 +90,7 @@ class _Flat:
         return picks, float(self.total.item())
 
     def bits_of(self, lams: list[float]) -> list[float]:
-        """Total picked bits under each of up to 8 multipliers, one launch and one read-back."""
+        """Total picked bits under each of up to 32 multipliers, one launch and one read-back."""
         import ctypes
 
         totals = torch.zeros(len(lams), dtype=torch.float64, device=self.dev)
@@ -105,17 +106,18 @@ class _Flat:
 
 
 def _summary(flat: _Flat, picks):
-    err = floor = 0.0
-    counts: dict[int, int] = {}
-    rows = 0
-    for (t, cost, _), (_, a, b) in zip(flat.per_table, flat.spans):
-        p = picks[a:b]
-        err += cost.gather(0, p[None])[0].sum().item()
-        floor += cost.min(0).values.sum().item()
-        for ci, (nb, _b) in enumerate(t.candidates):
-            counts[nb] = counts.get(nb, 0) + int((p == ci).sum())
-        rows += p.numel()
-    return err / max(floor, 1e-30), {nb: n / max(rows, 1) for nb, n in counts.items()}
+    """``(error / floor, fraction of rows by width)`` with two read-backs for all tables."""
+    err = flat.cost.gather(0, picks[None])[0].sum()
+    floor = flat.cost.min(0).values.sum()
+    widths = sorted({nb for t, _, _ in flat.per_table for nb, _ in t.candidates})
+    nbits = torch.cat([
+        torch.tensor([nb for nb, _ in t.candidates], device=flat.dev)[picks[a:b]]
+        for (t, _, _), (_, a, b) in zip(flat.per_table, flat.spans)
+    ])
+    counts = torch.stack([(nbits == nb).sum() for nb in widths])
+    head = torch.stack([err, floor]).tolist()
+    counts = counts.tolist()
+    return head[0] / max(head[1], 1e-30), {nb: n / max(flat.rows, 1) for nb, n in zip(widths, counts)}
 
 
 def allocate_global(tables, target_bpw: float, sensitivity: dict | None = None,
@@ -128,10 +130,11 @@ def allocate_global(tables, target_bpw: float, sensitivity: dict | None = None,
     budget = target_bpw * total_w - overhead
     flat = _Flat(tables, sens, dev)
 
-    lam_hi = 1.0
+    slopes = []
     for _t, cost, bits in flat.per_table:
         span_b = (bits.max() - bits.min()).clamp_min(1e-9)
-        lam_hi = max(lam_hi, 2 * ((cost.max(0).values - cost.min(0).values) / span_b).max().item())
+        slopes.append(2 * ((cost.max(0).values - cost.min(0).values) / span_b).max())
+    lam_hi = max(1.0, max(torch.stack(slopes).tolist()))  # one read-back for all tables
     lo, hi = lam_hi * 1e-12, lam_hi
 
     def done(p, b, lam, ok):
@@ -144,13 +147,13 @@ def allocate_global(tables, target_bpw: float, sensitivity: dict | None = None,
     best = flat.solve(lo)
     if best[1] <= budget:  # even the most accurate one fits
         return done(best[0], best[1], lo, True)
-    # The reference bisects one multiplier per step.  The next three steps can only visit the 7
-    # midpoints of a depth-3 tree, so their bit totals are fetched in one launch and the steps are
+    # The reference bisects one multiplier per step.  The next five steps can only visit the 31
+    # midpoints of a depth-5 tree, so their bit totals are fetched in one launch and the steps are
     # then taken on the host exactly as the reference takes them (same Python-float midpoints).
     best_lam = hi
     left = iters
     while left > 0:
-        depth = min(3, left)
+        depth = min(5, left)
         nodes = {(): (lo, hi)}  # path of outcomes (True = fits) -> bracket before that step
         lams, order = [], []
         for level in range(depth):

@@ -34,14 +34,14 @@ solve_kernel(const double* __restrict__ cost, const double* __restrict__ bits, i
   }
 }
 
-constexpr int MAX_LAMS = 8;
+constexpr int MAX_LAMS = 32;
 struct Lams {
   double v[MAX_LAMS];
   int n;
 };
 
-// Picked bits under several multipliers at once (no picks written): lets the host take three
-// bisection steps per round trip by evaluating the 7 multipliers the next three steps can reach.
+// Picked bits under several multipliers at once (no picks written): lets the host take five
+// bisection steps per round trip by evaluating the 31 multipliers the next five steps can reach.
 __global__ void __launch_bounds__(256)
 solve_many_kernel(const double* __restrict__ cost, const double* __restrict__ bits, int n_cand,
                   int64_t n_rows, Lams lams, double* totals) {
@@ -85,7 +85,7 @@ extern "C" int hi2_allocate_bits(const double* cost, const double* bits, int n_c
                                  const double* lams_host, int n_lams, double* totals, void* stream) {
   using namespace hi2;
   HI2_REQUIRE(n_cand >= 1 && n_rows >= 0, "allocate_bits: bad sizes");
-  HI2_REQUIRE(n_lams >= 1 && n_lams <= MAX_LAMS && lams_host, "allocate_bits: 1 to 8 multipliers");
+  HI2_REQUIRE(n_lams >= 1 && n_lams <= MAX_LAMS && lams_host, "allocate_bits: 1 to 32 multipliers");
   if (n_rows == 0) return HI2_OK;
   HI2_REQUIRE(cost && bits && totals, "allocate_bits: null pointer");
   Lams l;

@@ -222,9 +222,9 @@ int hi2_inverse_factor(const float* hs, const float* lam, int64_t k, float* u, v
 int hi2_allocate_solve(const double* cost, const double* bits, int n_cand, int64_t n_rows,
                        double lam, int64_t* picks, double* picked_bits, void* stream);
 
-/* The picked-bit totals of up to 8 multipliers in one launch (same arithmetic, no picks written):
+/* The picked-bit totals of up to 32 multipliers in one launch (same arithmetic, no picks written):
  * totals[i] (device doubles, caller zeroes them) += bits picked under lams_host[i].  Lets the host
- * take three steps of the reference's bisection per round trip. */
+ * take five steps of the reference's bisection per round trip (the 31 midpoints they can reach). */
 int hi2_allocate_bits(const double* cost, const double* bits, int n_cand, int64_t n_rows,
                       const double* lams_host, int n_lams, double* totals, void* stream);
 
