@@ -542,6 +542,137 @@ def run_ours(args, cfg):
     emit(line)
 
 
+# --------------------------------------------------------------------------------------------
+# per-kernel view: every hot kernel alone at the shapes of the workload, against the bound that
+# limits it (python bench.py --kernels); not the line the contract asks for, a table beside it
+# --------------------------------------------------------------------------------------------
+def run_kernels(args, cfg):
+    import torch
+
+    from hi2_b200 import _lib, gptq_kernel, ladder_kernel
+    from hi2_b200.encode import EFFORT
+    from hi2_b200.format import fwht_groups, pack_codes
+    from hi2_b200.hessian import HessianStats, inverse_factor, transform_sigma
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    _lib.load()
+    pk = peaks()
+    g = torch.Generator(device=dev).manual_seed(0)
+    # larger than L2, and long enough to write that the host has queued the timed call before it ends
+    flush = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=5, warm=3, cold=True):
+        for _ in range(warm):
+            fn()
+        total = 0.0
+        for _ in range(reps):
+            if cold:
+                flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / reps  # ms
+
+    rows_out = []
+
+    def add(name, bound, work, unit, ms, peak, note=""):
+        achieved = work / (ms * 1e-3)
+        rows_out.append(dict(kernel=name, bound=bound, ms=round(ms, 4), achieved=achieved, unit=unit, peak=peak,
+                             frac=achieved / peak if peak else None, note=note))
+
+    # denominators the driver does not measure: cuBLAS fp32 (FFMA) and TF32 products, 8192^3
+    a = torch.randn(8192, 8192, device=dev, generator=g)
+    b = torch.randn(8192, 8192, device=dev, generator=g)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    fp32_peak = 2 * 8192**3 / (timed(lambda: torch.matmul(a, b), cold=False) * 1e-3) / 1e12
+    torch.backends.cuda.matmul.allow_tf32 = True
+    tf32_peak = 2 * 8192**3 / (timed(lambda: torch.matmul(a, b), cold=False) * 1e-3) / 1e12
+    torch.backends.cuda.matmul.allow_tf32 = False
+    del a, b
+    lane_peak = fp32_peak / 2  # fp32 instructions per second (T lane-ops/s): an FMA is two flops
+
+    k, r_wide, k_wide = 4096, 11008, 11008
+    tokens = min(cfg["tokens"], 65536)
+    # second moment
+    for kk in (k, k_wide):
+        x = torch.randn(tokens, kk, device=dev, generator=g).bfloat16()
+        h = HessianStats(kk, dev)
+        ms = timed(lambda: h.update(x, defer_check=True), reps=3, warm=2)
+        h.check()
+        nib, njb = -(-kk // 128), -(-kk // 256)
+        tiles = sum(njb - (ib >> 1) for ib in range(nib))
+        add(f"hessian_tc K={kk} T={tokens}", "tensor (bf16)", 2.0 * tokens * tiles * 128 * 256 / 1e12, "TFLOP/s", ms,
+            pk["tensor_burst"], "issued flops, burst peak (timed alone)")
+        sig = h.S / h.n
+        if kk == k:
+            sigma_small = sig
+        del x, h
+        # basis change and inverse factor of the same input
+        s16 = (torch.rand(kk, device=dev, generator=g) + 0.5).half()
+        had = torch.ones(kk // 16, dtype=torch.uint8, device=dev)
+        ms = timed(lambda: transform_sigma(sig, s16, had, denom=1.0, return_diag=True))
+        add(f"transform_sigma K={kk}", "hbm", 8.0 * kk * kk / 1e9, "GB/s", ms, pk["hbm"])
+        hs = transform_sigma(sig, None, had)
+        ms = timed(lambda: inverse_factor(hs, 0.01), reps=3, warm=1, cold=False)
+        add(f"inverse_factor K={kk}", "fp32-grade flops", (2.0 / 3.0) * kk**3 / 1e12, "TFLOP/s", ms, fp32_peak,
+            "(2/3) K^3 against the cuBLAS fp32 peak; a chain of K/64 dependent leaves")
+        if kk == k:
+            u_small = inverse_factor(hs, 0.01)
+        del sig, hs
+    # rotation with the cast and the smoothing multiply fused
+    wb = (torch.randn(r_wide, k, device=dev, generator=g) * 0.02).bfloat16()
+    had = torch.ones(k // 16, dtype=torch.uint8, device=dev)
+    s32 = torch.rand(k, device=dev, generator=g) + 0.5
+    ms = timed(lambda: fwht_groups(wb, had, col_scale=s32, out_dtype=torch.float32))
+    add(f"rotate bf16->fp32 {r_wide}x{k}", "hbm", wb.numel() * 6.0 / 1e9, "GB/s", ms, pk["hbm"])
+    w = fwht_groups(wb, had, col_scale=s32, out_dtype=torch.float32)
+    d = torch.rand(k, device=dev, generator=g) + 0.05
+    eff = EFFORT["normal"]
+    ops_per_weight = 11 * len(eff["grid"]) ** 2 + 28 * eff["ls"] + 14  # fp32 operations of the reference's search
+    for block in (16, 32, 64):
+        ms = timed(lambda: ladder_kernel.fit(w, d, eff["grid"], eff["ls"], 4, block))
+        add(f"fit_kernel<{block}> INT2 {r_wide}x{k}", "fp32 instruction issue", w.numel() * ops_per_weight / 1e12,
+            "Tops/s", ms, lane_peak, f"{ops_per_weight} reference operations per weight; peak = cuBLAS fp32 flops / 2")
+    lo, st = ladder_kernel.fit(w, d, eff["grid"], eff["ls"], 4, 32)
+    ms = timed(lambda: ladder_kernel.quantize_rows(lo, st, 2, 32, k, w, d, want_codes=True, want_sse=True))
+    add(f"row_kernel<32> INT2 {r_wide}x{k}", "hbm", (w.numel() * 5.0 + lo.numel() * 10.0) / 1e9, "GB/s", ms, pk["hbm"],
+        "reads fp32 rows, writes codes, parameter bytes and sse")
+    q = ladder_kernel.quantize_rows(lo, st, 2, 32, k, w, d, want_codes=True, want_decoded=True, ldp=k // 16)
+    ms = timed(lambda: pack_codes(q["codes"], 2))
+    add(f"pack_codes INT2 {r_wide}x{k}", "hbm", w.numel() * 1.25 / 1e9, "GB/s", ms, pk["hbm"])
+    # GPTQ: one 128-column segment and its trailing update, then the whole column loop
+    n = r_wide
+    wc = w.clone()
+    codes = torch.empty(n, k, dtype=torch.uint8, device=dev)
+    err1 = torch.empty(n, 128, device=dev)
+    rg = torch.zeros(n, dtype=torch.int32, device=dev)
+    up = torch.tensor([u_small.data_ptr()], dtype=torch.int64, device=dev)
+    blk = (torch.arange(k, device=dev) // 32).to(torch.int32).reshape(1, k)
+    nm = torch.tensor([3.0], device=dev)
+    ms_blk = timed(lambda: gptq_kernel.gptq_block(wc, 0, 128, err1, codes, q["lo_d"], q["step_d"], rg, up, blk, nm),
+                   cold=False)
+    add(f"gptq_block N={n} (128 columns)", "dependent chain", n * 128 * 140.0 / 1e12, "Tops/s", ms_blk, lane_peak,
+        "140 reference operations per row and column")
+    parts = gptq_kernel.split_tf32_transposed(u_small)
+    ms_round = timed(lambda: gptq_kernel.gptq_round_tc(wc, err1, codes, q["lo_d"], q["step_d"], rg, up, blk, nm, None,
+                                                        [0, n], [parts]), reps=3, warm=1, cold=False)
+    lazy_flops = float(n) * k * k * (1 - 128.0 / k)
+    ms_lazy = ms_round - (k // 128) * ms_blk
+    add(f"lazy_tc (all {k // 128 - 1} trailing updates, N={n})", "tensor (3xTF32)", 3 * lazy_flops / 1e12, "TFLOP/s",
+        max(ms_lazy, 1e-3), tf32_peak, "three TF32 products per fp32-grade product; time = column loop minus segments")
+    rows_out.append(dict(kernel=f"GPTQ column loop N={n} K={k}", bound="chain + tensor", ms=round(ms_round, 3),
+                         achieved=n / (ms_round * 1e-3), unit="rows/s", peak=None, frac=None,
+                         note="segments + trailing updates"))
+    emit({"kernels": rows_out, "peaks": {"hbm_gbs": pk["hbm"], "bf16_tflops_burst": pk["tensor_burst"],
+                                         "bf16_tflops_sustained": pk["tensor"], "fp32_tflops_cublas": fp32_peak,
+                                         "tf32_tflops_cublas": tf32_peak, "source": pk["source"]},
+          "timing": "CUDA events, 3 warm-ups, L2 flushed before each timed call unless the input exceeds it"})
+
+
 _RESULT = None  # the process's original stdout, kept for the one JSON line
 
 
@@ -571,9 +702,12 @@ def main():
     ap.add_argument("--config", default="cfg2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--kernels", action="store_true", help="time every hot kernel alone against its bound")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
-    if args.impl == "reference":
+    if args.kernels:
+        run_kernels(args, cfg)
+    elif args.impl == "reference":
         run_reference(args, cfg)
     else:
         run_ours(args, cfg)

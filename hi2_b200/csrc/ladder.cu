@@ -178,8 +178,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 constexpr int ROW_THREADS = 256;
+constexpr int ROW_WARPS = ROW_THREADS / 32;
+constexpr int ROW_UN = 4;  // quads a lane loads before it computes
 
-// Dynamic shared memory: decoded lo[nb], step[nb].
+// One WARP per row: the row-wide extrema, the constants and the parameter bytes need only warp
+// shuffles, so no thread block barrier sits between the phases of a row and 64 rows are in flight
+// per SM.  Dynamic shared memory: per warp the decoded lo[nb], step[nb] of its row.
 template <int B>
 __global__ void __launch_bounds__(ROW_THREADS)
 row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
@@ -188,34 +192,23 @@ row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
            float* __restrict__ lo_d, float* __restrict__ st_d, int64_t ldp,
            uint8_t* __restrict__ codes, float* __restrict__ sse, float* __restrict__ energy) {
   extern __shared__ float dyn[];
-  __shared__ float red[3][ROW_THREADS / 32];
   const int64_t nb = k / B;
-  float* s_lo = dyn;
-  float* s_st = dyn + nb;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* s_lo = dyn + (size_t)warp * 2 * nb;
+  float* s_st = s_lo + nb;
 
-  for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+  for (int64_t row = (int64_t)blockIdx.x * ROW_WARPS + warp; row < n_rows; row += (int64_t)gridDim.x * ROW_WARPS) {
     const float* lo_r = lo_in + row * nb;
     const float* st_r = st_in + row * nb;
     // ---- row-wide extrema -----------------------------------------------------------------
     float mxst = -INFINITY, mnlo = INFINITY, mxlo = -INFINITY;
-    for (int64_t b = tid; b < nb; b += ROW_THREADS) {
+    for (int64_t b = lane; b < nb; b += 32) {
       const float s = st_r[b], l = lo_r[b];
       mxst = fmaxf(mxst, s < 0.0f ? 0.0f : s);
       mnlo = fminf(mnlo, l);
       mxlo = fmaxf(mxlo, l);
     }
     mxst = warp_max(mxst), mnlo = warp_min(mnlo), mxlo = warp_max(mxlo);
-    __syncthreads();  // previous row's readers of red[] and dyn[] are done
-    if (lane == 0) red[0][warp] = mxst, red[1][warp] = mnlo, red[2][warp] = mxlo;
-    __syncthreads();
-    mxst = red[0][0], mnlo = red[1][0], mxlo = red[2][0];
-#pragma unroll
-    for (int i = 1; i < ROW_THREADS / 32; ++i) {
-      mxst = fmaxf(mxst, red[0][i]);
-      mnlo = fminf(mnlo, red[1][i]);
-      mxlo = fmaxf(mxlo, red[2][i]);
-    }
     // ---- the three fp16 row constants -------------------------------------------------------
     const __half ss_h = __float2half_rn(__fdiv_rn(mxst, 255.0f));
     const float ss = __half2float(ss_h);
@@ -225,13 +218,14 @@ row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
     spread = spread < 0.0f ? 0.0f : spread;
     const __half ls_h = __float2half_rn(__fdiv_rn(spread, 255.0f));
     const float ls = __half2float(ls_h);
-    if (tid == 0 && consts != nullptr) {
+    if (lane == 0 && consts != nullptr) {
       consts[row * 3 + 0] = __half_as_ushort(lm_h);
       consts[row * 3 + 1] = __half_as_ushort(ls_h);
       consts[row * 3 + 2] = __half_as_ushort(ss_h);
     }
     // ---- parameter bytes and decoded ladders ------------------------------------------------
-    for (int64_t b = tid; b < nb; b += ROW_THREADS) {
+    __syncwarp();  // the previous row's readers of s_lo / s_st are done
+    for (int64_t b = lane; b < nb; b += 32) {
       float s = st_r[b];
       s = s < 0.0f ? 0.0f : s;
       float su = 0.0f, lu = 0.0f;
@@ -251,40 +245,59 @@ row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
       if (st_d != nullptr) st_d[row * ldp + b] = std_;
     }
     if (sse == nullptr && codes == nullptr && energy == nullptr) continue;
-    __syncthreads();
+    __syncwarp();
     // ---- nearest codes, weighted error, energy ------------------------------------------------
+    // A lane takes ROW_UN quads per trip, all loads first, to keep enough bytes in flight.  Codes are
+    // rint((w - lo) / step) with an IEEE division in the reference; the quotient is formed with the
+    // block's correctly rounded reciprocal and Markstein's fused correction, which gives the same
+    // correctly rounded number.
     const float* wr = w + row * ldw;
     float acc = 0.0f, en = 0.0f;
-    for (int64_t j = (int64_t)tid * 4; j < k; j += ROW_THREADS * 4) {
-      const float4 wv = *reinterpret_cast<const float4*>(wr + j);
-      const float4 dv = *reinterpret_cast<const float4*>(d + j);
-      const int64_t b = j / B;
-      const float lod = s_lo[b], std_ = s_st[b];
-      const float safe = (std_ == 0.0f) ? 1.0f : std_;
-      const float ws[4] = {wv.x, wv.y, wv.z, wv.w}, ds[4] = {dv.x, dv.y, dv.z, dv.w};
-      uint8_t cs[4];
+    for (int64_t j0 = (int64_t)lane * 4; j0 < k; j0 += 128 * ROW_UN) {
+      float4 wq[ROW_UN], dq[ROW_UN];
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        float c = (std_ == 0.0f) ? 0.0f : rintf(__fdiv_rn(ws[t] - lod, safe));
-        c = clamp_keep_nan(c, 0.0f, nmax);
-        const float diff = round_f16(lod + c * std_) - ws[t];
-        acc += ds[t] * (diff * diff);
-        en += ds[t] * (ws[t] * ws[t]);
-        cs[t] = (uint8_t)c;
+      for (int u = 0; u < ROW_UN; ++u) {
+        const int64_t j = j0 + u * 128;
+        if (j < k) {
+          wq[u] = *reinterpret_cast<const float4*>(wr + j);
+          dq[u] = *reinterpret_cast<const float4*>(d + j);
+        }
       }
-      if (codes != nullptr)
-        *reinterpret_cast<uchar4*>(codes + row * k + j) = make_uchar4(cs[0], cs[1], cs[2], cs[3]);
+#pragma unroll
+      for (int u = 0; u < ROW_UN; ++u) {
+        const int64_t j = j0 + u * 128;
+        if (j >= k) break;
+        const int64_t b = j / B;
+        const float lod = s_lo[b], std_ = s_st[b];
+        const float safe = (std_ == 0.0f) ? 1.0f : std_;
+        const Recip rc = make_recip(safe);
+        const float ws[4] = {wq[u].x, wq[u].y, wq[u].z, wq[u].w}, ds[4] = {dq[u].x, dq[u].y, dq[u].z, dq[u].w};
+        uint8_t cs[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float num = ws[t] - lod;
+          float c;
+          if (rc.fast) {
+            const float q0 = num * rc.r;
+            c = rintf(fmaf(fmaf(-q0, safe, num), rc.r, q0));
+          } else {
+            c = rintf(__fdiv_rn(num, safe));
+          }
+          if (std_ == 0.0f) c = 0.0f;
+          c = clamp_keep_nan(c, 0.0f, nmax);
+          const float diff = round_f16(lod + c * std_) - ws[t];
+          acc += ds[t] * (diff * diff);
+          en += ds[t] * (ws[t] * ws[t]);
+          cs[t] = (uint8_t)c;
+        }
+        if (codes != nullptr)
+          *reinterpret_cast<uchar4*>(codes + row * k + j) = make_uchar4(cs[0], cs[1], cs[2], cs[3]);
+      }
     }
     acc = warp_sum(acc), en = warp_sum(en);
-    __syncthreads();
-    if (lane == 0) red[0][warp] = acc, red[1][warp] = en;
-    __syncthreads();
-    if (tid == 0) {
-      float a = 0.0f, e = 0.0f;
-#pragma unroll
-      for (int i = 0; i < ROW_THREADS / 32; ++i) a += red[0][i], e += red[1][i];
-      if (sse != nullptr) sse[row] = a;
-      if (energy != nullptr) energy[row] = e;
+    if (lane == 0) {
+      if (sse != nullptr) sse[row] = acc;
+      if (energy != nullptr) energy[row] = en;
     }
   }
 }
@@ -380,14 +393,21 @@ extern "C" int hi2_quantize_rows(const float* lo, const float* step, const float
   }
   HI2_REQUIRE((lo_d == nullptr && step_d == nullptr) || ldp >= k / block, "quantize_rows: ldp");
   const int64_t nb = k / block;
-  const size_t smem = (size_t)(2 * nb) * sizeof(float);
-  HI2_REQUIRE(smem <= 48 * 1024, "quantize_rows: k too large for the ladder cache");
-  const unsigned grid = (unsigned)(n_rows < 148 * 16 ? n_rows : 148 * 16);
+  const size_t smem = (size_t)ROW_WARPS * (2 * nb) * sizeof(float);
+  HI2_REQUIRE(smem <= 200 * 1024, "quantize_rows: k too large for the ladder cache");
+  const int64_t want = ceil_div(n_rows, (int64_t)ROW_WARPS);
+  const unsigned grid = (unsigned)(want < 148 * 8 ? want : 148 * 8);
   const float nmax = (float)((1 << nbits) - 1);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-#define HI2_ROW(BB)                                                                             \
-  row_kernel<BB><<<grid, ROW_THREADS, smem, s>>>(lo, step, w, ldw, d, nmax, n_rows, k, params,  \
-                                                 consts, lo_d, step_d, ldp, codes, sse, energy)
+#define HI2_ROW(BB)                                                                                    \
+  do {                                                                                                 \
+    if (smem > 48 * 1024 &&                                                                            \
+        cudaFuncSetAttribute(row_kernel<BB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != \
+            cudaSuccess)                                                                               \
+      return fail(HI2_ERR_LAUNCH, "quantize_rows: cannot reserve shared memory");                      \
+    row_kernel<BB><<<grid, ROW_THREADS, smem, s>>>(lo, step, w, ldw, d, nmax, n_rows, k, params,       \
+                                                   consts, lo_d, step_d, ldp, codes, sse, energy);     \
+  } while (0)
   if (block == 16) HI2_ROW(16);
   if (block == 32) HI2_ROW(32);
   if (block == 64) HI2_ROW(64);

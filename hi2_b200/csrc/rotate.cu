@@ -7,6 +7,8 @@
 // shuffle.  Every output is the left-to-right sum over k = 0..15 of x_k * (+-1/4): the products
 // are exact, so the result equals a row-times-matrix product accumulated in ascending k, which
 // is what the reference's CPU product gives bit for bit (a radix-2 butterfly does not).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace hi2 {
@@ -127,41 +129,49 @@ __device__ __forceinline__ void rotate_quad(const C mine[4], int lane, C out[4])
 }
 
 // Tin == Tout (C = compute type of the pair) or Tin half/bf16 with Tout float.
+// A lane takes UN quads per trip and issues all their loads before the first shuffle, so that
+// enough bytes are in flight per SM to cover the latency of HBM (one 8- or 16-byte load per lane
+// at a time left the kernel at about half of the copy bandwidth).
+constexpr int ROT_UN = 4;
+
 template <typename Tin, typename Tout, bool kSameType>
 __global__ void __launch_bounds__(256)
 rotate_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, const uint8_t* __restrict__ flags,
               const float* __restrict__ col_scale, int64_t quads, int groups_per_row) {
+  using C = typename std::conditional<kSameType, typename Quad<Tin>::C, float>::type;
   const int lane = threadIdx.x & 31;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   // every lane of a warp runs the same number of iterations: quads is rounded up to a warp
   const int64_t limit = (quads + 31) & ~(int64_t)31;
-  for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < limit; q += stride) {
-    const bool live = q < quads;
-    const int64_t qq = live ? q : quads - 1;
-    const int64_t group = qq >> 2;
-    const int g = (int)(group % groups_per_row);
-    const bool flagged = flags[g] != 0;
-    if constexpr (kSameType) {
-      using C = typename Quad<Tin>::C;
-      C mine[4], out[4];
-      Quad<Tin>::load(x + qq * 4, mine);
-      if constexpr (sizeof(Tin) == 4) {
+  for (int64_t q0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q0 < limit; q0 += stride * ROT_UN) {
+    C mine[ROT_UN][4];
+    int64_t qq[ROT_UN];
+    bool live[ROT_UN], on[ROT_UN];  // on: the whole warp has this trip
+#pragma unroll
+    for (int u = 0; u < ROT_UN; ++u) {
+      const int64_t q = q0 + u * stride;
+      on[u] = q < limit;
+      live[u] = q < quads;
+      qq[u] = live[u] ? q : quads - 1;
+      if (on[u]) {
+        if constexpr (kSameType) Quad<Tin>::load(x + qq[u] * 4, mine[u]);
+        else load_as_f32<Tin>(x + qq[u] * 4, mine[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < ROT_UN; ++u) {
+      if (!on[u]) continue;
+      const int g = (int)((qq[u] >> 2) % groups_per_row);
+      const bool flagged = flags[g] != 0;
+      if constexpr (!kSameType || sizeof(Tin) == 4) {
         if (col_scale != nullptr) {
           float4 s = *reinterpret_cast<const float4*>(col_scale + (int64_t)g * 16 + (lane & 3) * 4);
-          mine[0] *= s.x, mine[1] *= s.y, mine[2] *= s.z, mine[3] *= s.w;
+          mine[u][0] *= s.x, mine[u][1] *= s.y, mine[u][2] *= s.z, mine[u][3] *= s.w;
         }
       }
-      rotate_quad<C>(mine, lane, out);
-      if (live) Quad<Tout>::store(y + qq * 4, flagged ? out : mine);
-    } else {
-      float mine[4], out[4];
-      load_as_f32<Tin>(x + qq * 4, mine);
-      if (col_scale != nullptr) {
-        float4 s = *reinterpret_cast<const float4*>(col_scale + (int64_t)g * 16 + (lane & 3) * 4);
-        mine[0] *= s.x, mine[1] *= s.y, mine[2] *= s.z, mine[3] *= s.w;
-      }
-      rotate_quad<float>(mine, lane, out);
-      if (live) Quad<float>::store(y + qq * 4, flagged ? out : mine);
+      C out[4];
+      rotate_quad<C>(mine[u], lane, out);
+      if (live[u]) Quad<Tout>::store(y + qq[u] * 4, flagged ? out : mine[u]);
     }
   }
 }
