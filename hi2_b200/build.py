@@ -31,6 +31,7 @@ SOURCES = [
     "sigma.cu",
     "cholinv.cu",
     "hessian.cu",
+    "hessian2.cu",
     "allocate.cu",
 ]
 FLAGS = [

@@ -31,6 +31,12 @@
 #include "gemm.cuh"
 
 namespace hi2 {
+
+// hessian2.cu: the same product on pairs of thread blocks (256 x 256 tiles, cta_group::2)
+size_t pair_workspace_bytes(int64_t tokens, int64_t k);
+int accumulate_pair(const void* x, int dtype, int64_t tokens, int64_t k, float* s, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream);
+
 namespace {
 
 constexpr int BM = 128;       // output rows per tile (columns of X on the A side)
@@ -409,6 +415,14 @@ TcPlan plan_tc(int64_t tokens, int64_t k) {
 bool use_tc(int dtype, int64_t tokens, int64_t k) {
   return (dtype == HI2_BF16 || dtype == HI2_F16) && k >= 256 && tokens >= 256;
 }
+// Large problems go to the pair kernel: its 256 x 256 tiles want a few tiles per SM pair and
+// thousands of tokens per item.
+bool use_pair(int dtype, int64_t tokens, int64_t k) {
+#ifdef HI2_NO_PAIR
+  return false;
+#endif
+  return use_tc(dtype, tokens, k) && k >= 1024 && tokens >= 8192;
+}
 
 int accumulate_tc(const void* x, int dtype, int64_t tokens, int64_t k, float* s, void* workspace,
                   size_t workspace_bytes, cudaStream_t stream) {
@@ -472,6 +486,7 @@ int accumulate_fma(const void* x, int64_t tokens, int64_t k, float* s, cudaStrea
 extern "C" size_t hi2_hessian_workspace_bytes(int64_t tokens, int64_t k, int dtype) {
   using namespace hi2;
   if (tokens <= 0 || k <= 0 || !use_tc(dtype, tokens, k)) return 0;
+  if (use_pair(dtype, tokens, k)) return pair_workspace_bytes(tokens, k);
   return plan_tc(tokens, k).scratch_bytes + 256;
 }
 
@@ -493,6 +508,7 @@ extern "C" int hi2_hessian_accumulate(const void* x, int dtype, int64_t tokens, 
   HI2_REQUIRE(x && s, "hessian_accumulate: null pointer");
   HI2_REQUIRE(aligned16(x) && aligned16(s), "hessian_accumulate: x and s must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_pair(dtype, tokens, k)) return accumulate_pair(x, dtype, tokens, k, s, workspace, workspace_bytes, st);
   if (use_tc(dtype, tokens, k))
     return accumulate_tc(x, dtype, tokens, k, s, workspace, workspace_bytes, st);
   if (dtype == HI2_BF16) return accumulate_fma<__nv_bfloat16>(x, tokens, k, s, st);

@@ -45,8 +45,9 @@ def test_second_moment_small_path(golden, dtype):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("tokens,k", [(4096, 512), (5000, 448), (20000, 1024), (9000, 2304)])
 def test_second_moment_tensor_core_path(dtype, tokens, k):
-    """tcgen05 path: tokens not a multiple of 64, K not a multiple of the 128 x 256 tile, several
-    token splits; accumulated on top of an existing sum; exactly symmetric."""
+    """tcgen05 paths (the first two sizes take the one-block kernel, the last two the CTA-pair
+    kernel with 256 x 256 tiles): tokens not a multiple of 64, K not a multiple of the tile,
+    several token splits; accumulated on top of an existing sum; exactly symmetric."""
     from hi2_b200.hessian import HessianStats
 
     x = activations(tokens, k, tokens + k, spread=1.0, dtype=dtype)
