@@ -1,31 +1,41 @@
 // Bit packing of codes and the scatter of one candidate group into the flat per-tensor buffers
 // (hi2/format.py:73-85 pack_codes, :158-171 assemble).  Integer work, bound by HBM traffic:
 // a thread reads the 16 / 8 / 4 code bytes of one output word with one vector load and writes
-// one int32; neighbouring threads touch neighbouring addresses on both sides.
+// one int32; neighbouring threads touch neighbouring addresses on both sides, and four words are
+// in flight per thread.
 #include "common.cuh"
 
 namespace hi2 {
 namespace {
 
-// One packed word from `per = 32 / nbits` consecutive code bytes at p (p is per-byte aligned).
-// *bad is raised when a code does not fit nbits.
+// The `per = 32 / nbits` consecutive code bytes of one output word (p is per-byte aligned).
 template <int NBITS>
-__device__ __forceinline__ uint32_t pack_word(const uint8_t* __restrict__ p, int32_t* bad) {
+struct Raw {
+  uint32_t v[(32 / NBITS) / 4];
+};
+template <int NBITS>
+__device__ __forceinline__ Raw<NBITS> load_raw(const uint8_t* __restrict__ p) {
   constexpr int PER = 32 / NBITS;
-  uint32_t raw[PER / 4];
+  Raw<NBITS> r;
   if constexpr (PER == 16) {
     uint4 v = *reinterpret_cast<const uint4*>(p);
-    raw[0] = v.x, raw[1] = v.y, raw[2] = v.z, raw[3] = v.w;
+    r.v[0] = v.x, r.v[1] = v.y, r.v[2] = v.z, r.v[3] = v.w;
   } else if constexpr (PER == 8) {
     uint2 v = *reinterpret_cast<const uint2*>(p);
-    raw[0] = v.x, raw[1] = v.y;
+    r.v[0] = v.x, r.v[1] = v.y;
   } else {
-    raw[0] = *reinterpret_cast<const uint32_t*>(p);
+    r.v[0] = *reinterpret_cast<const uint32_t*>(p);
   }
+  return r;
+}
+// One packed word; *bad is raised when a code does not fit nbits.
+template <int NBITS>
+__device__ __forceinline__ uint32_t pack_raw(const Raw<NBITS>& r, int32_t* bad) {
+  constexpr int PER = 32 / NBITS;
   uint32_t word = 0, over = 0;
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
-    const uint32_t c = (raw[i >> 2] >> (8 * (i & 3))) & 0xffu;
+    const uint32_t c = (r.v[i >> 2] >> (8 * (i & 3))) & 0xffu;
     over |= c >> NBITS;
     word |= (c & ((1u << NBITS) - 1u)) << (NBITS * i);
   }
@@ -33,14 +43,25 @@ __device__ __forceinline__ uint32_t pack_word(const uint8_t* __restrict__ p, int
   return word;
 }
 
+// A thread takes PACK_UN words per trip and issues all their loads first: one 16-byte load in
+// flight per thread does not cover the latency of HBM.
+constexpr int PACK_UN = 4;
+
 template <int NBITS>
 __global__ void __launch_bounds__(256)
 pack_kernel(const uint8_t* __restrict__ codes, int32_t* __restrict__ words, int64_t n_words,
             int32_t* bad) {
   constexpr int PER = 32 / NBITS;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += stride)
-    words[i] = (int32_t)pack_word<NBITS>(codes + i * PER, bad);
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < n_words; i0 += stride * PACK_UN) {
+    Raw<NBITS> raw[PACK_UN];
+#pragma unroll
+    for (int u = 0; u < PACK_UN; ++u)
+      if (i0 + u * stride < n_words) raw[u] = load_raw<NBITS>(codes + (i0 + u * stride) * PER);
+#pragma unroll
+    for (int u = 0; u < PACK_UN; ++u)
+      if (i0 + u * stride < n_words) words[i0 + u * stride] = (int32_t)pack_raw<NBITS>(raw[u], bad);
+  }
 }
 
 // grid.x strides the words of a row, grid.y the rows of the piece.
@@ -59,8 +80,16 @@ assemble_kernel(const int64_t* __restrict__ rows, int64_t n_rows, const uint8_t*
     const uint8_t* src = codes + r * k;
     const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t w = t0; w < words_per_row; w += step)
-      out_codes[cbase + w] = (int32_t)pack_word<NBITS>(src + w * PER, bad);
+    for (int64_t w0 = t0; w0 < words_per_row; w0 += step * PACK_UN) {
+      Raw<NBITS> raw[PACK_UN];
+#pragma unroll
+      for (int u = 0; u < PACK_UN; ++u)
+        if (w0 + u * step < words_per_row) raw[u] = load_raw<NBITS>(src + (w0 + u * step) * PER);
+#pragma unroll
+      for (int u = 0; u < PACK_UN; ++u)
+        if (w0 + u * step < words_per_row)
+          out_codes[cbase + w0 + u * step] = (int32_t)pack_raw<NBITS>(raw[u], bad);
+    }
     for (int64_t b = t0; b < param_bytes_per_row; b += step)
       out_params[pbase + b] = params[r * param_bytes_per_row + b];
     if (t0 < 3) out_consts[row * 3 + t0] = consts[r * 3 + t0];

@@ -395,9 +395,19 @@ def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str |
     for x in units:
         per_job[x.job].append(_finish(x, jobs[x.job]))
     out = []
-    for encs in per_job:
+    for job, encs in zip(jobs, per_job):
         if len(encs) == 1:
             out.append(encs[0])
+            continue
+        if not encs:  # a job without rows: nothing was launched for it
+            dev, k = job.w.device, job.w.shape[1]
+            out.append(Encoded(
+                torch.empty(0, k, dtype=torch.uint8, device=dev),
+                torch.empty(0, k // job.block, 2, dtype=torch.uint8, device=dev),
+                torch.empty(0, 3, dtype=torch.float16, device=dev),
+                torch.empty(0, dtype=torch.float32, device=dev),
+                torch.empty(0, k, dtype=torch.float32, device=dev) if comp else None,
+            ))
             continue
         out.append(
             Encoded(

@@ -112,3 +112,57 @@ def test_config1_layer_gptq_beats_nearest_and_hits_the_budget():
     assert int(gptq.code_off[-1]) == gptq.codes.numel() and torch.equal(gptq.row_nbits, near.row_nbits)
     e_g, e_n = hessian_error(gptq), hessian_error(near)
     assert e_g < 0.97 * e_n, (e_g, e_n)
+
+
+def test_widest_input_of_the_70b_shape():
+    """K = 28672 (the FFN width of BASELINE config 4): second moment against exact columns, basis
+    change, and the inverse factor through its defining identity.  The largest single matrices
+    the path meets: S and U are 3.3 GB each."""
+    from hi2_b200.hessian import HessianStats, inverse_factor, transform_sigma
+
+    g = _gen(5)
+    k, tokens = 28672, 32768
+    x = (torch.randn(tokens, k, generator=g, device=DEV) * torch.exp(0.5 * torch.randn(1, k, generator=g, device=DEV))).bfloat16()
+    h = HessianStats(k, DEV)
+    h.update(x)
+    assert h.n == tokens and torch.equal(h.S, h.S.T)
+    cols = torch.randint(0, k, (16,), generator=g, device=DEV)
+    want = x.double().T[cols] @ x.double()
+    scale = (x.double() ** 2).sum(0).sqrt()
+    err = ((h.S[cols].double() - want) / (scale[cols, None] * scale[None, :])).abs().max().item()
+    assert err < 2e-5, err
+    del x, want
+    hs, d = transform_sigma(h.S, None, torch.ones(k // 16, dtype=torch.uint8), denom=float(h.n), return_diag=True)
+    del h
+    u = inverse_factor(hs, 0.01)
+    assert torch.equal(u, u.triu()) and bool((u.diagonal() > 0).all())
+    lam = 0.01 * hs.diagonal().mean()
+    v = torch.randn(k, 4, generator=g, device=DEV)
+    hv = (hs @ v + lam * v).double()
+    back = (u.T.double() @ (u.double() @ hv)).float()
+    rel = ((back - v).norm() / v.norm()).item()
+    assert rel < 2e-3, rel
+
+
+def test_empty_and_single_row_inputs():
+    """Nothing to do is not an error (hi2/gptq_kernel.py:116), and one row is a full problem."""
+    from hi2_b200.encode import encode_rows
+    from hi2_b200.format import fwht_groups, pack_codes
+    from hi2_b200.hessian import HessianStats, encode_rows_gptq, inverse_factor
+
+    k = 256
+    h = HessianStats(k, DEV)
+    h.update(torch.zeros(0, k, device=DEV, dtype=torch.bfloat16))
+    assert h.n == 0 and not h.S.any()
+    g = _gen(6)
+    x = torch.randn(600, k, generator=g, device=DEV).bfloat16()
+    h.update(x)
+    u = inverse_factor(h.S / h.n, 0.01)
+    d = (h.S / h.n).diagonal().contiguous()
+    none = encode_rows_gptq(torch.zeros(0, k, device=DEV), d, u, 2, 32)
+    assert none.codes.shape == (0, k) and none.sse.numel() == 0
+    one = encode_rows_gptq(torch.randn(1, k, generator=g, device=DEV) * 0.02, d, u, 4, 16)
+    assert one.codes.shape == (1, k) and int(one.codes.max()) <= 15
+    assert encode_rows(torch.zeros(0, k, device=DEV), d, 2, 16).codes.shape == (0, k)
+    assert pack_codes(torch.zeros(0, k, dtype=torch.uint8, device=DEV), 2).shape == (0, k // 16)
+    assert fwht_groups(torch.zeros(0, k, device=DEV), torch.ones(k // 16, dtype=torch.uint8)).shape == (0, k)
