@@ -382,7 +382,8 @@ def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str |
         side.wait_stream(main)
         with torch.cuda.stream(side):
             for batch in bl:
-                _round_units(batch, jobs, comp, splits, checks)
+                if batch:  # a width whose jobs have no rows leaves one empty batch
+                    _round_units(batch, jobs, comp, splits, checks)
         joins.append((main, side))
     for main, side in joins:
         main.wait_stream(side)
