@@ -405,29 +405,35 @@ def run_reference(args, cfg):
 # the rest of the tile re-reads), DRAM writes the per-item output tiles.  Reads grow in proportion
 # to the tokens, the tiles do not, so a full-size launch is scaled from those two figures.
 # DRAM reads of the second-moment kernel as a multiple of the bytes of X, from ncu captures at
-# 32768 tokens: 1.78 at K = 4096 (X of a wave fits in L2), 6.2 at K = 11008 (banded tile schedule,
-# ~13 waves, the L2 absorbs about half of them)
-HESSIAN_READ_FACTOR = {4096: 1.78, 11008: 6.2}
+# 32768 tokens: 1.05 at K = 4096 (pair kernel, X of a wave fits in L2), 6.2 at K = 11008 (one-block
+# kernel, banded tile schedule, ~13 waves of which the L2 absorbs half)
+HESSIAN_READ_FACTOR = {4096: 1.05, 11008: 6.2}
 
 
 def hessian_traffic(widths, tokens, elem_bytes=2):
     """Estimated DRAM bytes per launch, averaged over the launches of one step."""
     total = 0.0
     for k in widths.values():
-        # item tiles of the CTA-pair kernel: 256 x 256 fp32 per (tile, token split); the split count
-        # follows the kernel's plan (fewest waves per split, at most 512 MiB of tiles)
-        nb = -(-k // 256)
-        tiles = nb * (nb + 1) // 2
-        cap = max(1, -(-tokens // 64) // 64)
-        best, best_cost = 1, float("inf")
-        for sp in range(1, min(16, cap) + 1):
-            if sp > 1 and sp * tiles * 256 * 256 * 4 > (512 << 20):
-                break
-            cost = -(-tiles * sp // 74) / sp
-            if cost < best_cost * 0.995:
-                best, best_cost = sp, cost
-        factor = HESSIAN_READ_FACTOR.get(k, 1.78 if k <= 4096 else 6.2)
-        total += factor * tokens * k * elem_bytes + best * tiles * 256 * 256 * 4
+        kblocks = -(-tokens // 64)
+        cap = max(1, kblocks // 64)
+        if 1024 <= k <= 8192:
+            # CTA-pair kernel: 256 x 256 fp32 per (tile, token split); the split count follows the
+            # kernel's plan (fewest waves per split, at most 512 MiB of tiles)
+            nb = -(-k // 256)
+            tiles, area = nb * (nb + 1) // 2, 256 * 256
+            splits, best_cost = 1, float("inf")
+            for sp in range(1, min(16, cap) + 1):
+                if sp > 1 and sp * tiles * area * 4 > (512 << 20):
+                    break
+                cost = -(-tiles * sp // 74) / sp
+                if cost < best_cost * 0.995:
+                    splits, best_cost = sp, cost
+        else:  # one-block kernel: 128 x 256 tiles
+            nib, njb = -(-k // 128), -(-k // 256)
+            tiles, area = sum(njb - (ib >> 1) for ib in range(nib)), 128 * 256
+            splits = max(1, min(-(-148 * 6 // tiles), cap))
+        factor = HESSIAN_READ_FACTOR.get(k, 1.05 if k <= 4096 else 6.2)
+        total += factor * tokens * k * elem_bytes + splits * tiles * area * 4
     return total / max(1, len(widths))
 
 
@@ -515,13 +521,13 @@ def run_ours(args, cfg):
     hess_s = stage["hessian"] / 1e3  # resident steps run the four second moments back to back, alone
     achieved = issued / hess_s / 1e12
     roofline = {
-        "kernel": "hessian_pair_kernel (second moment X^T X, tcgen05 cta_group::2, fp32 accumulate)",
+        "kernel": "hessian_pair_kernel / hessian_tc_kernel (second moment X^T X, tcgen05 cta_group::2 up to K=8192, cta_group::1 beyond; fp32 accumulate)",
         "bound": "tensor", "achieved": achieved, "peak": pk["tensor"], "unit": "TFLOP/s",
         "frac": achieved / pk["tensor"], "peak_source": f"{pk['source']}, sustained (kernel timed inside a long step)",
         "effective": algo / hess_s / 1e12,
         "note": "achieved counts the flops issued (upper-triangle 256x256 tiles); effective counts 2*T*K^2",
         "traffic": hessian_traffic(job.widths, cfg["tokens"]),
-        "traffic_note": "bytes per launch, scaled from ncu captures at 32768 tokens (reads 1.78 x X at K=4096, 6.2 x X at K=11008, plus item tiles)",
+        "traffic_note": "bytes per launch, scaled from ncu captures at 32768 tokens (reads 1.05 x X at K=4096, 6.2 x X at K=11008, plus item tiles)",
         "algorithmic_bytes": sum(cfg["tokens"] * k * 2 + 4 * k * k for k in job.widths.values()) / max(1, len(job.widths)),
         "launch_ms": hess_s * 1e3 / max(1, len(job.widths) * world),
     }

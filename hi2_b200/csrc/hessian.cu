@@ -416,12 +416,14 @@ bool use_tc(int dtype, int64_t tokens, int64_t k) {
   return (dtype == HI2_BF16 || dtype == HI2_F16) && k >= 256 && tokens >= 256;
 }
 // Large problems go to the pair kernel: its 256 x 256 tiles want a few tiles per SM pair and
-// thousands of tokens per item.
+// thousands of tokens per item.  Beyond K = 8192 the 74 tiles in flight cover so many columns
+// that they fall out of step in L2 (DRAM reads of 10.9 x X at K = 11008 against 6.2 x for 148
+// one-block tiles, same time, less stable), so the widest inputs stay with the one-block kernel.
 bool use_pair(int dtype, int64_t tokens, int64_t k) {
 #ifdef HI2_NO_PAIR
   return false;
 #endif
-  return use_tc(dtype, tokens, k) && k >= 1024 && tokens >= 8192;
+  return use_tc(dtype, tokens, k) && k >= 1024 && k <= 8192 && tokens >= 8192;
 }
 
 int accumulate_tc(const void* x, int dtype, int64_t tokens, int64_t k, float* s, void* workspace,
