@@ -216,17 +216,31 @@ class Job:
             L.start_factors(mine, self.qcfg, self.device, only=name, into=factors)
             L.tabulate(self.weights, self.plan, mine, self.qcfg, only=name, into=tables)
 
+        # With one layer per rank the partial sums of an input are kept as one [world, K, K] stack and
+        # summed by ONE reduce-scatter (every link carries (world - 1) / world of the stack once);
+        # otherwise each layer's sum is reduced onto its owner.  The token total is known without
+        # asking: the shards of dist.token_shard add up to it.
+        scatter = self.world > 1 and len(self.inputs) == self.world
+        if scatter and not hasattr(self, "stacks"):
+            self.stacks = {n: torch.empty(self.world, k, k, dtype=torch.float32, device=self.device)
+                           for n, k in self.widths.items()}
         for name in order:
             for layer, xs in enumerate(self.inputs):
                 if ready is not None:
                     cur.wait_event(ready[(layer, name)])
-                L.accumulate({name: xs[name]}, self.device, into=shared_all[layer], defer_check=True)
+                where = {name: self.stacks[name][layer]} if scatter else None
+                L.accumulate({name: xs[name]}, self.device, into=shared_all[layer], defer_check=True, storage=where)
                 s = shared_all[layer][name]  # partial sum of this rank's tokens -> the layer's owner
-                n, work = hd.reduce_second_moment(s.hessian.S, s.hessian.n, hd.owner_of(layer, self.world),
-                                                  async_op=True)
-                s.hessian.n = n
-                if work is not None:
-                    pending.append(work)
+                if not scatter:
+                    n, work = hd.reduce_second_moment(s.hessian.S, s.hessian.n, hd.owner_of(layer, self.world),
+                                                      async_op=True, n_total=self.cfg["tokens"])
+                    s.hessian.n = n
+                    if work is not None:
+                        pending.append(work)
+            if scatter:
+                own, work = hd.reduce_scatter_second_moments(self.stacks[name], async_op=True)
+                mine[name].hessian.S, mine[name].hessian.n = own, self.cfg["tokens"]
+                pending.append(work)
             if from_host:  # end to end: work on an input as soon as it has arrived
                 for work in pending:
                     work.wait()

@@ -67,15 +67,37 @@ def token_shard(tokens: int, r: int | None = None, world: int | None = None) -> 
     return lo, lo + base + (1 if r < extra else 0)
 
 
-def reduce_second_moment(s: torch.Tensor, n: int, owner: int, async_op: bool = False):
+def reduce_second_moment(s: torch.Tensor, n: int, owner: int, async_op: bool = False,
+                         n_total: int | None = None):
     """Sum partial second moments ``s`` (in place, fp32) onto ``owner`` and the token counts onto
-    every rank.  Returns ``(n_total, work)``; ``work`` is None unless ``async_op``."""
+    every rank.  Returns ``(n_total, work)``; ``work`` is None unless ``async_op``.  A caller that
+    knows the total token count (the shards of :func:`token_shard` add up to it) passes ``n_total``
+    and saves the count's all-reduce and the host synchronisation that reading it costs."""
     if world_size() == 1:
         return n, None
-    count = torch.tensor([n], dtype=torch.int64, device=s.device)
-    dist.all_reduce(count)
+    if n_total is None:
+        count = torch.tensor([n], dtype=torch.int64, device=s.device)
+        dist.all_reduce(count)
+        n_total = int(count.item())
     work = dist.reduce(s, dst=owner, op=dist.ReduceOp.SUM, async_op=async_op)
-    return int(count.item()), work
+    return n_total, work
+
+
+def reduce_scatter_second_moments(stack: torch.Tensor, async_op: bool = False):
+    """``stack [world, K, K]`` (fp32): this rank's partial second moment of the same input of every
+    unit, unit ``r`` owned by rank ``r``.  One reduce-scatter instead of ``world`` reductions onto
+    single owners: every link carries ``(world - 1) / world`` of the stack once, and the switch can
+    do the sums.  Returns ``(own [K, K] summed over the ranks, work)``."""
+    if world_size() == 1:
+        return stack[0], None
+    if stack.shape[0] != world_size():
+        raise ValueError("one slice per rank is needed")
+    if dist.get_backend() == "gloo":  # gloo has no reduce-scatter: all-reduce and keep the own slice
+        work = dist.all_reduce(stack, async_op=async_op)
+        return stack[rank()], work
+    out = torch.empty_like(stack[0])
+    work = dist.reduce_scatter_tensor(out, stack, op=dist.ReduceOp.SUM, async_op=async_op)
+    return out, work
 
 
 def all_reduce_second_moment(s: torch.Tensor, n: int):

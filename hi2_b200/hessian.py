@@ -60,9 +60,16 @@ def _side_stream(dev: torch.device, i: int) -> torch.cuda.Stream:
 class HessianStats:
     """Full second moment ``sum x x^T`` of a Linear's input (fp32, ``[K, K]``)."""
 
-    def __init__(self, k: int, device="cuda"):
+    def __init__(self, k: int, device="cuda", out: torch.Tensor | None = None):
+        """``out`` (optional): a contiguous fp32 ``[k, k]`` tensor to accumulate into (it is zeroed),
+        e.g. one slice of a stack that a reduce-scatter will sum over the ranks."""
         self.k = k
-        self.S = torch.zeros(k, k, dtype=torch.float32, device=device)
+        if out is not None:
+            if out.shape != (k, k) or out.dtype != torch.float32 or not out.is_contiguous():
+                raise ValueError("out must be a contiguous fp32 [k, k] tensor")
+            self.S = out.zero_()
+        else:
+            self.S = torch.zeros(k, k, dtype=torch.float32, device=device)
         self.n = 0
         self._unchecked: list = []  # status words of launches whose outcome nobody has read yet
 

@@ -41,15 +41,18 @@ class LayerPlan:
     reads: dict = field(default_factory=dict)
 
 
-def accumulate(inputs: dict, device, into: dict | None = None, defer_check: bool = False) -> dict:
+def accumulate(inputs: dict, device, into: dict | None = None, defer_check: bool = False,
+               storage: dict | None = None) -> dict:
     """``{input name: activations [tokens, k]}`` -> ``{input name: SharedInput}`` with the second
     moment summed (``into`` continues earlier sums: more tokens, or another rank's shard).  With
-    ``defer_check`` the launches are not waited for; :func:`encode` settles their status."""
+    ``defer_check`` the launches are not waited for; :func:`encode` settles their status.
+    ``storage`` (optional) gives the ``[k, k]`` tensor a new input's sum is kept in."""
     out = into if into is not None else {}
     for name, x in inputs.items():
         k = x.shape[-1]
         if name not in out:
-            out[name] = SharedInput(name, k, HessianStats(k, device))
+            where = None if storage is None else storage.get(name)
+            out[name] = SharedInput(name, k, HessianStats(k, device, out=where))
         out[name].hessian.update(x, defer_check=defer_check)
     return out
 

@@ -102,6 +102,14 @@ for owner in range(world):
 s = part.T @ part
 assert hd.all_reduce_second_moment(s, part.shape[0]) == tokens
 assert torch.allclose(s, full, rtol=1e-5, atol=1e-4)
+n, _ = hd.reduce_second_moment(part.T @ part, part.shape[0], 0, n_total=tokens)  # no count exchange
+assert n == tokens
+# one input of `world` units, unit r owned by rank r: every rank's partial sums as one stack
+units = [torch.randn(tokens, k, generator=g) for _ in range(world)]
+stack = torch.stack([u[lo:hi].T @ u[lo:hi] for u in units])
+own, work = hd.reduce_scatter_second_moments(stack, async_op=True)
+work.wait()
+assert torch.allclose(own, units[rank].T @ units[rank], rtol=1e-5, atol=1e-4)
 tabs = hd.gather_tables([{"name": f"r{rank}", "sse": torch.full((2, 3), float(rank))}])
 assert [t["name"] for t in tabs] == [f"r{i}" for i in range(world)]
 from types import SimpleNamespace as NS
