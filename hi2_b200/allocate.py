@@ -48,36 +48,71 @@ class Allocation:
 
 
 class _Flat:
-    """Costs and bits of all tables side by side, ``[C, sum R]`` fp64 on the device."""
+    """Costs and bits of all tables side by side, ``[C, sum R]`` fp64 on the device.  Built with a
+    handful of launches and one read-back whatever the number of tables (a model has hundreds)."""
 
     def __init__(self, tables, sens, dev):
         self.dev = dev
+        self.tables = list(tables)
         cmax = max(len(t.candidates) for t in tables)
-        costs, bits, self.spans, self.per_table = [], [], [], []
-        off = 0
-        for t in tables:
-            r, k = t.shape
-            scale = sens.get(t.name, 1.0) / max(float(t.energy), 1e-30)
-            # fp32 product with the scalar rounded to fp32 first, then widened: what
-            # `scalar * float32_tensor` followed by `.double()` gives
-            cost = (t.sse.to(dev, torch.float32) * scale).double()
-            b = torch.tensor(
-                [candidate_row_bits(nb, bl, k) for nb, bl in t.candidates],
-                dtype=torch.float64, device=dev,
-            )
-            self.per_table.append((t, cost, b))
-            pad = cmax - cost.shape[0]
-            costs.append(torch.cat([cost, torch.full((pad, r), float("inf"), dtype=torch.float64,
-                                                      device=dev)]))
-            bits.append(torch.cat([b, torch.zeros(pad, dtype=torch.float64, device=dev)])
-                        .unsqueeze(1).expand(cmax, r))
+        # energies: device scalars of local tables and plain numbers of gathered ones, read once
+        lazy = [(i, t.energy) for i, t in enumerate(tables) if isinstance(t.energy, torch.Tensor)]
+        energy = [0.0 if isinstance(t.energy, torch.Tensor) else float(t.energy) for t in tables]
+        if lazy:
+            for (i, _), v in zip(lazy, torch.stack([e.to(dev, torch.float64).reshape(()) for _, e in lazy]).tolist()):
+                energy[i] = v
+        rows = [t.shape[0] for t in tables]
+        self.rows = sum(rows)
+        self.spans, off = [], 0
+        for t, r in zip(tables, rows):
             self.spans.append((t.name, off, off + r))
             off += r
-        self.cost = torch.cat(costs, 1).contiguous()
-        self.bits = torch.cat(bits, 1).contiguous()
-        self.rows = off
-        self.picks = torch.empty(off, dtype=torch.int64, device=dev)
+        # Per table (a few numbers each, built on the host and uploaded as one small matrix): the bits
+        # of every candidate, which candidates exist, their widths, and the table's scale; per row
+        # they are gathered on the device through the row's table index.
+        n_t = len(tables)
+        desc = torch.zeros(n_t, 3 * cmax + 2, dtype=torch.float64)
+        for i, (t, r, e) in enumerate(zip(tables, rows, energy)):
+            k = t.shape[1]
+            for ci, (nb, bl) in enumerate(t.candidates):
+                desc[i, ci] = candidate_row_bits(nb, bl, k)
+                desc[i, cmax + ci] = 1.0
+                desc[i, 2 * cmax + ci] = nb
+            # the fp32 number a Python scalar becomes in an fp32 product
+            desc[i, 3 * cmax] = float(torch.tensor(sens.get(t.name, 1.0) / max(e, 1e-30), dtype=torch.float64).to(torch.float32))
+            desc[i, 3 * cmax + 1] = r
+        desc = _lib.upload(desc, dev)
+        table_of_row = torch.repeat_interleave(torch.arange(n_t, device=dev), desc[:, 3 * cmax + 1].long(),
+                                               output_size=self.rows)
+        per_row = desc[table_of_row]  # [rows, 3 cmax + 2]
+        self.bits = per_row[:, :cmax].T.contiguous()
+        self.valid = per_row[:, cmax : 2 * cmax].T > 0.5
+        self.nbits_of = per_row[:, 2 * cmax : 3 * cmax].T.long()
+        scale_d = per_row[:, 3 * cmax].to(torch.float32)
+        parts = []
+        for t in tables:
+            sse = t.sse.to(dev, torch.float32)
+            if sse.shape[0] < cmax:
+                pad = torch.full((cmax - sse.shape[0], sse.shape[1]), float("inf"), dtype=torch.float32, device=dev)
+                sse = torch.cat([sse, pad])
+            parts.append(sse)
+        sse_all = parts[0] if len(parts) == 1 else torch.cat(parts, 1)
+        # fp32 product with the scalar rounded to fp32 first, then widened: what
+        # `scalar * float32_tensor` followed by `.double()` gives
+        self.cost = (sse_all * scale_d[None]).double().contiguous()
+        self.picks = torch.empty(self.rows, dtype=torch.int64, device=dev)
         self.total = torch.zeros(1, dtype=torch.float64, device=dev)
+
+    def upper_multiplier(self) -> float:
+        """``max(1, 2 * max over rows of (cost spread) / (bit spread of the row's table))``: one
+        read-back (the reference takes the maximum table by table)."""
+        neg, pos = float("-inf"), float("inf")
+        hi = torch.where(self.valid, self.cost, torch.full_like(self.cost, neg)).max(0).values
+        lo = torch.where(self.valid, self.cost, torch.full_like(self.cost, pos)).min(0).values
+        bhi = torch.where(self.valid, self.bits, torch.full_like(self.bits, neg)).max(0).values
+        blo = torch.where(self.valid, self.bits, torch.full_like(self.bits, pos)).min(0).values
+        slope = 2 * ((hi - lo) / (bhi - blo).clamp_min(1e-9)).max()
+        return max(1.0, float(slope.item()))
 
     def solve(self, lam: float):
         """``(picks [sum R] on the device, total picked bits)`` for one multiplier."""
@@ -108,12 +143,9 @@ class _Flat:
 def _summary(flat: _Flat, picks):
     """``(error / floor, fraction of rows by width)`` with two read-backs for all tables."""
     err = flat.cost.gather(0, picks[None])[0].sum()
-    floor = flat.cost.min(0).values.sum()
-    widths = sorted({nb for t, _, _ in flat.per_table for nb, _ in t.candidates})
-    nbits = torch.cat([
-        torch.tensor([nb for nb, _ in t.candidates], device=flat.dev)[picks[a:b]]
-        for (t, _, _), (_, a, b) in zip(flat.per_table, flat.spans)
-    ])
+    floor = torch.where(flat.valid, flat.cost, torch.full_like(flat.cost, float("inf"))).min(0).values.sum()
+    widths = sorted({nb for t in flat.tables for nb, _ in t.candidates})
+    nbits = flat.nbits_of.gather(0, picks[None])[0]
     counts = torch.stack([(nbits == nb).sum() for nb in widths])
     head = torch.stack([err, floor]).tolist()
     counts = counts.tolist()
@@ -130,11 +162,7 @@ def allocate_global(tables, target_bpw: float, sensitivity: dict | None = None,
     budget = target_bpw * total_w - overhead
     flat = _Flat(tables, sens, dev)
 
-    slopes = []
-    for _t, cost, bits in flat.per_table:
-        span_b = (bits.max() - bits.min()).clamp_min(1e-9)
-        slopes.append(2 * ((cost.max(0).values - cost.min(0).values) / span_b).max())
-    lam_hi = max(1.0, max(torch.stack(slopes).tolist()))  # one read-back for all tables
+    lam_hi = flat.upper_multiplier()
     lo, hi = lam_hi * 1e-12, lam_hi
 
     def done(p, b, lam, ok):
