@@ -212,7 +212,7 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
                 out.append(None)
             else:
                 enc = encode_rows(wt[rows], d, nb, b, cfg.effort)
-                out.append((rows, enc.codes, enc.params, enc.consts))
+                out.append((rows, enc.codes, enc.params, enc.consts, nb, b))
     want = any(reqs[ri].comp_out is not None for ri, _ in where)
     encs = encode_jobs_gptq(jobs, cfg.effort, comp=want) if jobs else []
     if any(not job.succeeded() for job in waits.values()):
@@ -238,13 +238,20 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
                 encs[x] = type(encs[x])(codes, encs[x].params, encs[x].consts, encs[x].sse, encs[x].comp)
     slot = {ri: iter([j for j, p in enumerate(pieces[ri]) if p is None]) for ri in pieces}
     comps: dict[int, list] = {}
-    for (ri, rows), enc in zip(where, encs):
-        pieces[ri][next(slot[ri])] = (rows, enc.codes, enc.params, enc.consts)
+    for (ri, rows), enc, job in zip(where, encs, jobs):
+        pieces[ri][next(slot[ri])] = (rows, enc.codes, enc.params, enc.consts, job.nbits, job.block)
         if reqs[ri].comp_out is not None:
             comps.setdefault(ri, []).append((rows, enc.comp))
     out = []
+    flags: dict = {}  # one out-of-ladder flag per device for all tensors, read once
     for ri, r in enumerate(reqs):
         t = r.table
+        bad = None
+        if pieces.get(ri):
+            dev = _lib.need_cuda(r.w)
+            if dev not in flags:
+                flags[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+            bad = flags[dev]
         if r.comp_out is not None:
             full = stored[ri].clone()  # nearest rounding: the stored-basis weights themselves
             for rows, c in comps.get(ri, []):
@@ -254,8 +261,10 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
         picks = r.picks.cpu()
         out.append(
             assemble(pieces[ri], cand[picks, 0], cand[picks, 1], t.had, t.shape[1], t.col_scale,
-                     to_host=to_host)
+                     to_host=to_host, bad=bad)
         )
+    if any(int(f.item()) for f in flags.values()):
+        raise ValueError("code outside the ladder")
     return out
 
 

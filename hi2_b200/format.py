@@ -124,9 +124,12 @@ FIELDS = ("codes", "code_off", "blk_params", "param_off", "row_consts", "row_nbi
 
 
 def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=None,
-             to_host: bool = True) -> HI2Tensor:
+             to_host: bool = True, bad: torch.Tensor | None = None) -> HI2Tensor:
     """Flat buffers from per-candidate pieces ``(rows, codes[r, K] u8, params[r, nb, 2] u8,
-    consts[r, 3] fp16)``.
+    consts[r, 3] fp16)``.  A piece may carry its ``(nbits, block)`` as fifth and sixth entry, which
+    saves reading ``rows[0]`` back from the device; ``bad`` (optional, a device int32) collects the
+    out-of-ladder flag for a caller that checks it once for several tensors instead of waiting
+    for every one of them here.
 
     The packing and the scatters run on the device of the first piece.  As in the reference the
     result is returned on the host (``to_host=False`` keeps the three big buffers on the device,
@@ -147,16 +150,22 @@ def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=N
         consts = torch.zeros(r, 3, dtype=torch.float16)
     else:
         dev = _lib.need_cuda(*[p[1] for p in pieces])
-        code_off_d, param_off_d = code_off.to(dev), param_off.to(dev)
+        code_off_d, param_off_d = _lib.upload(code_off, dev), _lib.upload(param_off, dev)
         codes = torch.zeros(int(code_off[-1]), dtype=torch.int32, device=dev)
         params = torch.zeros(int(param_off[-1]) * 2, dtype=torch.uint8, device=dev)
         consts = torch.zeros(r, 3, dtype=torch.float16, device=dev)
-        bad = torch.zeros(1, dtype=torch.int32, device=dev)
-        for rows, c, p, rc in pieces:
+        check_here = bad is None
+        if check_here:
+            bad = torch.zeros(1, dtype=torch.int32, device=dev)
+        for piece in pieces:
+            rows, c, p, rc = piece[:4]
             if rows.numel() == 0:
                 continue
-            first = int(rows[0])
-            nbits, block = int(nb[first]), int(bl[first])
+            if len(piece) >= 6:
+                nbits, block = int(piece[4]), int(piece[5])
+            else:
+                first = int(rows[0])
+                nbits, block = int(nb[first]), int(bl[first])
             rows_d = rows.to(dev, torch.int64).contiguous()
             c = c.to(dev, torch.uint8).contiguous()
             p = p.to(dev, torch.uint8).contiguous()
@@ -166,7 +175,7 @@ def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=N
                 _lib.ptr(rc), k, nbits, block, _lib.ptr(code_off_d), _lib.ptr(param_off_d),
                 _lib.ptr(codes), _lib.ptr(params), _lib.ptr(consts), _lib.ptr(bad), _lib.stream(dev),
             )
-        if int(bad.item()):
+        if check_here and int(bad.item()):
             raise ValueError("code outside the ladder")
     if to_host:
         codes, params, consts = codes.cpu(), params.cpu(), consts.cpu()
