@@ -167,3 +167,18 @@ def test_expert_names_and_allocation_weights():
     assert w["l.experts.2.down_proj"] == 0.05 / 4
     own, need = moe.blend(torch.ones(2, 2), 10, torch.full((2, 2), 8.0), 40, 30)
     assert need == 30 and torch.equal(own, torch.full((2, 2), 5.0))
+
+
+def test_host_side_helpers_need_no_device():
+    """Argument checks that run before any kernel is launched."""
+    from hi2_b200.hessian import HessianStats
+
+    store = torch.ones(3, 8, 8)
+    h = HessianStats(8, "cpu", out=store[1])
+    assert h.S.data_ptr() == store[1].data_ptr() and not h.S.any() and bool(store[0].all())
+    with pytest.raises(ValueError):
+        HessianStats(8, "cpu", out=torch.zeros(8, 4))
+    with pytest.raises(ValueError):
+        HessianStats(8, "cpu", out=torch.zeros(8, 8, dtype=torch.float64))
+    with pytest.raises(RuntimeError):
+        h.update(torch.zeros(4, 8))  # no CPU path
