@@ -1,13 +1,16 @@
-"""Benchmark of the per-layer PTQ encode path (Hessian + tables + allocation + GPTQ + pack).
+"""Benchmark of the PTQ encode path (Hessian + tables + allocation + GPTQ + pack).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config cfg2|cfg1|tiny]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config cfg3|cfg2|cfg1|...]
 
-One step = the whole path over one Llama-style decoder layer per GPU (BASELINE config 2: seven
-bf16 matrices, hidden 4096 / FFN 11008, 128 x 2048 synthetic calibration tokens per distinct
-input, 2.5 bpw, INT2/INT4 candidates).  With N GPUs there are N layers, layer l owned by rank l;
-the calibration tokens of every layer are sharded over the ranks, partial second moments are
-reduced to the owner over NCCL, the error tables are all-gathered for the global allocation, and
-everything else runs on the owner ("weak" scaling: work per GPU is fixed).
+Default workload (``cfg3``, the configuration BASELINE.json's metric is quoted on): a whole
+Llama-2-7B-shaped model, 32 decoder layers of seven bf16 matrices (hidden 4096, FFN 11008),
+256 x 2048 synthetic calibration tokens per distinct input, 3.0 bpw, INT2/INT4 candidates.  One
+step = the whole model through tabulate -> allocate -> encode.  Layer l is owned by rank
+``l mod N`` (strong scaling: the model is fixed), the calibration tokens are sharded over the
+ranks, partial second moments are summed onto the owner by one NCCL reduce-scatter per input and
+group of N layers, the error tables are gathered once for the global allocation, and everything
+else runs on the owner.  ``--config cfg2`` is one decoder layer per GPU at 128 x 2048 tokens and
+2.5 bpw (weak scaling), ``cfg1`` the single 4096 x 4096 Linear the reference runs on CPU.
 
 Prints ONE JSON line (rank 0).  ``value`` is rows of weight matrix encoded per second with all
 inputs resident in HBM; ``e2e`` is the same through the public API from pinned host buffers with
@@ -34,6 +37,10 @@ if str(ROOT) not in sys.path:
 
 CONFIGS = {
     # name: hidden, ffn, sequences, seq_len, activation spread, target bpw, weight dtype
+    # BASELINE config 3, the one the metric is quoted on: a whole 7B-shaped model, 32 layers of the
+    # config-2 shapes, 256 x 2048 calibration tokens per input, 3.0 bpw, layer l owned by rank l mod N
+    "cfg3": dict(hidden=4096, ffn=11008, tokens=256 * 2048, spread=1.5, bpw=3.0, dtype="bf16", layers=32,
+                 workload="llama2_7b_shape_32_layers_x_7_matrices_256x2048_tokens_3.0bpw"),
     "cfg2": dict(hidden=4096, ffn=11008, tokens=128 * 2048, spread=1.5, bpw=2.5, dtype="bf16",
                  workload="llama_decoder_layer_7_matrices_4096x11008_128x2048_tokens_2.5bpw"),
     "cfg1": dict(hidden=4096, ffn=0, tokens=2048, spread=1.0, bpw=3.0, dtype="f16",
@@ -41,8 +48,11 @@ CONFIGS = {
     # config 2 with 32768 tokens per input: small enough for an ncu capture, inputs still > L2
     "cfg2_32k": dict(hidden=4096, ffn=11008, tokens=32768, spread=1.5, bpw=2.5, dtype="bf16",
                      workload="llama_decoder_layer_7_matrices_4096x11008_32768_tokens_2.5bpw"),
+    # small cases for the tests of this file (one layer; a four-layer model)
     "tiny": dict(hidden=512, ffn=1024, tokens=4096, spread=1.5, bpw=2.5, dtype="bf16",
                  workload="tiny_decoder_layer_512x1024_4096_tokens_2.5bpw"),
+    "tiny_model": dict(hidden=512, ffn=1024, tokens=4096, spread=1.5, bpw=3.0, dtype="bf16", layers=4,
+                       layers_per_encode=2, workload="tiny_model_4_layers_512x1024_4096_tokens_3.0bpw"),
 }
 
 
@@ -285,6 +295,187 @@ class Job:
                    for t in self.last["packed"].values() for f in FIELDS)
 
 
+class ModelJob:
+    """Resident workload of one rank for a whole model (BASELINE config 3): ``layers`` decoder
+    layers, layer l owned by rank ``l mod world`` ("strong" scaling: the model is fixed).
+
+    Inputs resident when the timed region starts: the bf16 weights of the owned layers and this
+    rank's token shard of ONE set of synthetic calibration activations (four tensors, 24 GB at
+    524 288 tokens), which stands in for the inputs of every layer: 32 distinct sets do not fit in
+    HBM, and in the real pipeline a layer's inputs are produced on the device by the layer before
+    it.  Every layer's second moments are computed from it anew; nothing is reused between layers.
+
+    A step is the reference's three phases (hi2/pipeline.py:1087-1252):
+      tabulate  per group of ``world`` consecutive layers: every rank accumulates the partial
+                second moments of its tokens for all layers of the group, one reduce-scatter per
+                input hands layer ``g * world + r`` to rank r; the owner then derives statistics,
+                starts the four factorisations on side streams and builds the seven error tables;
+      allocate  all tables of the model (1.36 M rows) gathered once, one global allocation;
+      encode    per owned layer: basis change / factor (already in flight), GPTQ, packing.
+    """
+
+    def __init__(self, cfg, rank, world, device):
+        from hi2_b200 import dist as hd
+        from hi2_b200.calibrate import ALL_CANDIDATES, Config
+
+        self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
+        self.n_layers = cfg["layers"]
+        if self.n_layers % world:
+            raise SystemExit(f"{self.n_layers} layers do not divide over {world} ranks")
+        self.groups = self.n_layers // world
+        self.owned = [g * world + rank for g in range(self.groups)]
+        self.shapes, self.widths, self.plan = shapes_of(cfg)
+        self.qcfg = Config(candidates=list(ALL_CANDIDATES))
+        self.weights = {l: make_weights(cfg, self.shapes, l, device) for l in self.owned}
+        lo, hi = hd.token_shard(cfg["tokens"], rank, world)
+        self.inputs = make_inputs(cfg, self.widths, 0, hi - lo, lo, device)
+        self.rows_layer = sum(r for r, _ in self.shapes.values())
+        self.rows = self.rows_layer * self.n_layers  # whole model, all ranks
+        self.specs = [(l % world, f"L{l}.{name}", shape, list(ALL_CANDIDATES), cfg["tokens"], True)
+                      for l in range(self.n_layers) for name, shape in self.shapes.items()]
+        self.stacks = None
+        self.host = None
+        self.copy_stream = None
+        self.stage_ms: dict = {}
+        self.hessian_ms = 0.0
+        self.hessian_launches = 0
+        self.gptq = {}  # K -> [rows, ms] over the timed steps
+
+    def input_order(self):
+        rows = {n: 0 for n in self.widths}
+        for w, (r, _) in self.shapes.items():
+            rows[self.plan.reads[w]] += r
+        return sorted(self.widths, key=lambda n: (-self.widths[n], -rows[n]))
+
+    def h2d_bytes(self):
+        n = sum(w.numel() * w.element_size() for ws in self.weights.values() for w in ws.values())
+        return n + sum(x.numel() * x.element_size() for x in self.inputs.values())
+
+    def pin_host_copies(self):
+        self.host = {"w": {l: {k: v.cpu().pin_memory() for k, v in ws.items()} for l, ws in self.weights.items()},
+                     "x": {k: v.cpu().pin_memory() for k, v in self.inputs.items()}}
+        self.copy_stream = torch.cuda.Stream(self.device)
+
+    def _mark(self, marks, name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append((name, ev))
+
+    def step(self, from_host=False, to_host=False):
+        from hi2_b200 import dist as hd
+        from hi2_b200 import layer as L
+        from hi2_b200.allocate import allocate_global
+        from hi2_b200.calibrate import EncodeRequest, TensorTable, encode_many
+
+        marks: list = []
+        cur = torch.cuda.current_stream(self.device)
+        order = self.input_order()
+        ready = None
+        if from_host:  # this step's inputs over PCIe, in the order of use, beside the kernels below
+            ready = {}
+            with torch.cuda.stream(self.copy_stream):
+                for name in order:
+                    self.inputs[name].copy_(self.host["x"][name], non_blocking=True)
+                    ready[name] = self.copy_stream.record_event()
+                for l in self.owned:
+                    for name, w in self.weights[l].items():
+                        w.copy_(self.host["w"][l][name], non_blocking=True)
+                    ready[l] = self.copy_stream.record_event()
+        if self.world > 1 and self.stacks is None:
+            self.stacks = {n: torch.empty(self.world, k, k, dtype=torch.float32, device=self.device)
+                           for n, k in self.widths.items()}
+        self._mark(marks, "tabulate")
+        state = {}
+        hess_events = []
+        for g, mine_l in enumerate(self.owned):
+            shared_all = [dict() for _ in range(self.world)]
+            mine = shared_all[self.rank]
+            pending = []
+            h0 = torch.cuda.Event(enable_timing=True)
+            h0.record()
+            for name in order:
+                if ready is not None and g == 0:
+                    cur.wait_event(ready[name])
+                for r in range(self.world):  # this rank's tokens, for the layer rank r owns in this group
+                    where = {name: self.stacks[name][r]} if self.world > 1 else None
+                    L.accumulate({name: self.inputs[name]}, self.device, into=shared_all[r], defer_check=True,
+                                 storage=where)
+                if self.world > 1:
+                    own, work = hd.reduce_scatter_second_moments(self.stacks[name], async_op=True)
+                    mine[name].hessian.S, mine[name].hessian.n = own, self.cfg["tokens"]
+                    pending.append(work)
+            h1 = torch.cuda.Event(enable_timing=True)
+            h1.record()
+            hess_events.append((h0, h1))
+            for work in pending:
+                work.wait()
+            if ready is not None:
+                cur.wait_event(ready[mine_l])
+            factors, tables = {}, {}
+            for name in order:
+                L.finish_statistics(mine, self.qcfg, only=name)
+                L.start_factors(mine, self.qcfg, self.device, only=name, into=factors, release_scratch=True)
+            for name in order:
+                L.tabulate(self.weights[mine_l], self.plan, mine, self.qcfg, only=name, into=tables)
+            for name, t in tables.items():
+                t.name = f"L{mine_l}.{name}"
+            state[mine_l] = dict(shared=mine, others=[sh for i, sh in enumerate(shared_all) if i != self.rank],
+                                 factors=factors, tables={name: tables[name] for name in self.shapes})
+        self._mark(marks, "allocate")
+        local = [state[l]["tables"][name] for l in self.owned for name in self.shapes]
+        everything = hd.gather_tables_known_layout(local, self.specs, TensorTable)
+        alloc = allocate_global(everything, self.cfg["bpw"])
+        for st in state.values():  # the allocation has read results back: the status words are there
+            for sh in [st["shared"], *st["others"]]:
+                for s_in in sh.values():
+                    s_in.hessian.check()
+            st["others"] = None
+        self._mark(marks, "encode")
+        # Several layers per call: rows of equal width from all of them share the column loops, and the
+        # host reads status words back once per call, not once per layer.
+        packed, timing = {}, []
+        per_call = self.cfg.get("layers_per_encode", 4)
+        for c0 in range(0, len(self.owned), per_call):
+            chunk = self.owned[c0 : c0 + per_call]
+            reqs, keys, fac = [], [], {}
+            for l in chunk:
+                st = state[l]
+                for name, w in self.weights[l].items():
+                    s_in = st["shared"][self.plan.reads[name]]
+                    reqs.append(EncodeRequest(w, s_in.moments, st["tables"][name], alloc.picks[f"L{l}.{name}"],
+                                              sigma=s_in.hessian.S, sigma_id=f"L{l}.{s_in.name}",
+                                              sigma_n=s_in.hessian.n))
+                    keys.append((l, name))
+                for iname, f in st["factors"].items():
+                    fac[f"L{l}.{iname}"] = f
+            out = encode_many(reqs, self.qcfg, to_host=to_host, factors=fac, timing=timing)
+            for (l, name), t in zip(keys, out):
+                packed.setdefault(l, {})[name] = t
+            for l in chunk:
+                state[l] = None  # second moments and factors of the layer are free again
+        self._mark(marks, "end")
+        self.last = dict(marks=marks, alloc=alloc, packed=packed, hess_events=hess_events, timing=timing)
+        return packed
+
+    def collect_stage_times(self):
+        marks = self.last["marks"]
+        for (name, a), (_, b) in zip(marks, marks[1:]):
+            self.stage_ms[name] = self.stage_ms.get(name, 0.0) + a.elapsed_time(b)
+        for a, b in self.last["hess_events"]:
+            self.hessian_ms += a.elapsed_time(b)
+            self.hessian_launches += len(self.widths) * self.world
+        for k, rows, a, b in self.last["timing"]:
+            acc = self.gptq.setdefault(k, [0, 0.0])
+            acc[0] += rows
+            acc[1] += a.elapsed_time(b)
+
+    def d2h_bytes(self):
+        from hi2_b200.format import FIELDS
+
+        return sum(getattr(t, f).numel() * getattr(t, f).element_size()
+                   for layer in self.last["packed"].values() for t in layer.values() for f in FIELDS)
+
+
 def hessian_flops(widths, tokens):
     """(algorithmic 2 T K^2, issued by the upper-triangle 128 x 256 tiles) summed over the inputs."""
     algo = issued = 0.0
@@ -471,7 +662,9 @@ def run_ours(args, cfg):
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
     _lib.load()
-    job = Job(cfg, rank, world, device)
+    whole_model = "layers" in cfg
+    job = ModelJob(cfg, rank, world, device) if whole_model else Job(cfg, rank, world, device)
+    total_rows = job.rows if whole_model else job.rows * world
 
     def sync_all():
         torch.cuda.synchronize(device)
@@ -520,7 +713,7 @@ def run_ours(args, cfg):
         ems = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=device)
         if world > 1:
             dist.all_reduce(ems, op=dist.ReduceOp.MAX)
-        e2e = {"value": job.rows * world / (float(ems.item()) / 1e3), "unit": "rows/s",
+        e2e = {"value": total_rows / (float(ems.item()) / 1e3), "unit": "rows/s",
                "ms_per_step": float(ems.item()), "h2d_bytes_per_step": need * world,
                "d2h_bytes_per_step": job.d2h_bytes() * world}
     else:
@@ -531,8 +724,19 @@ def run_ours(args, cfg):
         return
     pk = peaks()
     stage = {k: v / args.steps for k, v in job.stage_ms.items()}
-    algo, issued = hessian_flops(job.widths, cfg["tokens"])
-    hess_s = stage["hessian"] / 1e3  # resident steps run the four second moments back to back, alone
+    if whole_model:
+        # second moments: CUDA events around every layer group's launches (the reduce-scatters and the
+        # previous layer's factorisations run beside them)
+        stage["hessian"] = job.hessian_ms / args.steps
+        n_launch = job.hessian_launches / args.steps
+        tokens_per_launch = cfg["tokens"] // world
+        algo, issued = hessian_flops(job.widths, tokens_per_launch)
+        algo, issued = algo * n_launch / len(job.widths), issued * n_launch / len(job.widths)
+    else:
+        n_launch = len(job.widths) * world
+        tokens_per_launch = cfg["tokens"] // world
+        algo, issued = hessian_flops(job.widths, cfg["tokens"])
+    hess_s = stage["hessian"] / 1e3
     achieved = issued / hess_s / 1e12
     roofline = {
         "kernel": "hessian_pair_kernel / hessian_tc_kernel (second moment X^T X, tcgen05 cta_group::2 up to K=8192, cta_group::1 beyond; fp32 accumulate)",
@@ -540,10 +744,11 @@ def run_ours(args, cfg):
         "frac": achieved / pk["tensor"], "peak_source": f"{pk['source']}, sustained (kernel timed inside a long step)",
         "effective": algo / hess_s / 1e12,
         "note": "achieved counts the flops issued (upper-triangle 256x256 tiles); effective counts 2*T*K^2",
-        "traffic": hessian_traffic(job.widths, cfg["tokens"]),
+        "traffic": hessian_traffic(job.widths, tokens_per_launch),
         "traffic_note": "bytes per launch, scaled from ncu captures at 32768 tokens (reads 1.05 x X at K=4096, 6.2 x X at K=11008, plus item tiles)",
-        "algorithmic_bytes": sum(cfg["tokens"] * k * 2 + 4 * k * k for k in job.widths.values()) / max(1, len(job.widths)),
-        "launch_ms": hess_s * 1e3 / max(1, len(job.widths) * world),
+        "algorithmic_bytes": sum(tokens_per_launch * k * 2 + 4 * k * k for k in job.widths.values()) / max(1, len(job.widths)),
+        "launches_per_step": n_launch,
+        "launch_ms": hess_s * 1e3 / max(1, n_launch),
     }
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -552,21 +757,29 @@ def run_ours(args, cfg):
         res = cpu_sample(cfg, rows_s, tokens_s, threads)
         cpu = {"value": res["rows"] / res["seconds"], "unit": "rows/s", "cores": threads, "kind": "port",
                "sample": res["sample"], "seconds_full_workload": res["seconds"], "stages_s": res["stages"]}
-    gptq_rows_per_s = None
+    config = {"workload": cfg["workload"], "layers": cfg.get("layers", world), "rows_per_layer": job.rows_layer if whole_model else job.rows,
+              "tokens_per_input": cfg["tokens"], "target_bpw": cfg["bpw"], "achieved_bpw": alloc.bpw,
+              "candidates": "int2,int4 x b16,b32,b64",
+              "parallelism": (f"layer l on rank l mod {world}, token-sharded hessian, one reduce-scatter per input and layer group"
+                              if whole_model else f"layer-per-gpu x{world}, token-sharded hessian"),
+              "l2": "inputs larger than L2 (12-24 GB of activations per layer)"}
+    if whole_model:
+        config["activations"] = ("one synthetic set (four tensors) stands in for the inputs of every layer; each layer's "
+                                 "statistics are computed from it anew")
     line = {
-        "metric": "ptq_encode_rows_per_s", "value": job.rows * world / (ms_per_step / 1e3), "unit": "rows/s",
+        "metric": "ptq_encode_rows_per_s", "value": total_rows / (ms_per_step / 1e3), "unit": "rows/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg["workload"], "layers": world, "rows_per_layer": job.rows,
-                   "tokens_per_input": cfg["tokens"], "target_bpw": cfg["bpw"], "achieved_bpw": alloc.bpw,
-                   "candidates": "int2,int4 x b16,b32,b64", "parallelism": f"layer-per-gpu x{world}, token-sharded hessian",
-                   "l2": "inputs larger than L2 (12 GB of activations per step)"},
+        "higher_is_better": True, "scaling": "strong" if whole_model else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": config,
         "encode_wall_s": ms_per_step / 1e3,
         "stage_ms": {k: round(v, 3) for k, v in stage.items()},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clock_info,
     }
-    del gptq_rows_per_s
+    if whole_model and job.gptq:
+        # rows through the GPTQ column loop (block kernel + trailing updates) per second of that loop,
+        # per width; the widths run beside each other on two streams
+        line["gptq_rows_per_s"] = {str(k): rows / (ms / 1e3) for k, (rows, ms) in sorted(job.gptq.items())}
     emit(line)
 
 
@@ -732,7 +945,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="cfg2", choices=sorted(CONFIGS))
+    ap.add_argument("--config", default="cfg3", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--kernels", action="store_true", help="time every hot kernel alone against its bound")

@@ -115,9 +115,33 @@ def check(rc: int, what: str) -> None:
     raise RuntimeError(msg)
 
 
+class StreamArg:
+    """A stream handle that remembers its device: ``call`` makes that device current for the
+    launch.  (ctypes passes ``_as_parameter_``.)"""
+
+    __slots__ = ("_as_parameter_", "index")
+
+    def __init__(self, handle: int, index: int):
+        self._as_parameter_ = C.c_void_p(handle)
+        self.index = index
+
+
 def call(name: str, *args) -> None:
-    """Invoke an ``int``-returning entry point and raise on a non-zero status."""
-    check(getattr(load(), name)(*args), name)
+    """Invoke an ``int``-returning entry point and raise on a non-zero status.
+
+    The entry points launch on the CUDA runtime's current device.  The reference's API names
+    devices explicitly and drives several of them from one process (one thread each, sometimes
+    without ``set_device``), so the device of the stream argument is made current around the call;
+    a call whose tensors live on ``cuda:1`` never launches on ``cuda:0``."""
+    fn = getattr(load(), name)
+    for a in args:
+        if isinstance(a, StreamArg):
+            if a.index != torch.cuda.current_device():
+                with torch.cuda.device(a.index):
+                    check(fn(*args), name)
+                return
+            break
+    check(fn(*args), name)
 
 
 def ptr(t: torch.Tensor | None):
@@ -127,9 +151,11 @@ def ptr(t: torch.Tensor | None):
     return C.c_void_p(t.data_ptr())
 
 
-def stream(device=None):
-    """The current CUDA stream of ``device`` as an opaque pointer."""
-    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+def stream(device=None) -> StreamArg:
+    """The current CUDA stream of ``device`` (default: the current device), tagged with the
+    device's index."""
+    st = torch.cuda.current_stream(device)
+    return StreamArg(st.cuda_stream, st.device.index)
 
 
 def upload(t: torch.Tensor, dev: torch.device, dtype: torch.dtype | None = None) -> torch.Tensor:

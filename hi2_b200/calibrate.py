@@ -131,11 +131,15 @@ class EncodeRequest:
     sigma_n: int = 1  # divide sigma by this (lets the raw sum be passed without a copy)
 
 
+def _transform_key(col_scale, had):
+    cs = None if col_scale is None else col_scale.detach().cpu().to(torch.float16).numpy().tobytes()
+    return cs, had.detach().cpu().to(torch.uint8).numpy().tobytes()
+
+
 def _factor_key(req: EncodeRequest, i: int):
     t = req.table
-    cs = None if t.col_scale is None else t.col_scale.cpu().numpy().tobytes()
     sid = req.sigma_id if req.sigma_id is not None else f"#{i}"
-    return sid, cs, t.had.cpu().numpy().tobytes()
+    return (sid, *_transform_key(t.col_scale, t.had))
 
 
 def factor_for(sigma, sigma_n, col_scale, had, cfg: Config):
@@ -150,11 +154,12 @@ def factor_for(sigma, sigma_n, col_scale, had, cfg: Config):
     d_ready.record()
     job = FactorJob(hs, cfg.damp)
     job.d_ready = d_ready
+    job.transform_key = _transform_key(col_scale, had)  # a factor belongs to ONE (input, s, flags)
     return d, job, hs
 
 
 def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool = True,
-                factors: dict | None = None) -> list[HI2Tensor]:
+                factors: dict | None = None, timing: list | None = None) -> list[HI2Tensor]:
     """Encode several tensors with their allocator picks (hi2/calibrate.py:297-424): all GPTQ
     candidate groups of all tensors go through one batched column loop; the Hessian transform
     and factorisation happen once per distinct input."""
@@ -178,11 +183,15 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
         use_gptq = cfg.rounding == "gptq" and r.sigma is not None
         if use_gptq:
             fk = _factor_key(r, ri)
-            if fk not in factors and r.sigma_id in ready:
-                # started earlier on a side stream: order after it on the device, never on the host,
-                # so the narrow matrices are rounded while the widest factor is still being computed
+            if fk not in factors and r.sigma_id in ready and ready[r.sigma_id][1].transform_key == fk[1:]:
+                # started earlier on a side stream for this very (input, smoothing vector, flags):
+                # order after it on the device, never on the host, so the narrow matrices are rounded
+                # while the widest factor is still being computed.  d is complete at d_ready; U only
+                # at job.done, which every GptqJob below carries as its ``wait`` event.
                 d, job, hs = ready[r.sigma_id]
                 torch.cuda.current_stream(dev).wait_event(job.d_ready)
+                if cfg.refine_passes and hs is None:  # the prefactoring released it
+                    hs = transform_sigma(r.sigma.to(dev), t.col_scale, had, denom=float(max(r.sigma_n, 1)))
                 factors[fk] = (d, job.first_attempt(), None, hs if cfg.refine_passes else None)
                 waits[fk] = job
             if fk not in factors:
@@ -206,7 +215,7 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
             if rows.numel() == 0:
                 continue
             if use_gptq:
-                jobs.append(GptqJob(wt[rows], d, u, nb, b, perm))
+                jobs.append(GptqJob(wt[rows], d, u, nb, b, perm, waits[fk].done if fk in waits else None))
                 where.append((ri, rows))
                 refine_with.append(hs_keep if r.comp_out is None else None)
                 out.append(None)
@@ -214,11 +223,11 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
                 enc = encode_rows(wt[rows], d, nb, b, cfg.effort)
                 out.append((rows, enc.codes, enc.params, enc.consts, nb, b))
     want = any(reqs[ri].comp_out is not None for ri, _ in where)
-    encs = encode_jobs_gptq(jobs, cfg.effort, comp=want) if jobs else []
+    encs = encode_jobs_gptq(jobs, cfg.effort, comp=want, timing=timing) if jobs else []
     if any(not job.succeeded() for job in waits.values()):
         # a first attempt met a non-positive pivot: redo everything on the synchronous path, which
         # retries with more damping (hi2/hessian.py:78-86)
-        return encode_many(reqs, cfg, to_host=to_host, factors=None)
+        return encode_many(reqs, cfg, to_host=to_host, factors=None, timing=timing)
     if cfg.refine_passes:
         for job in waits.values():
             torch.cuda.current_stream().wait_event(job.done)

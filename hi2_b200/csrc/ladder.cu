@@ -34,6 +34,23 @@ struct BlockRegs {
   float a[WIDE ? B : 1];  // x - lo of the current lo
 };
 
+// Block sums are formed in the order of torch's CPU reduction over a contiguous inner dimension
+// (aten/src/ATen/native/cpu/SumKernel.cpp): the block is read as B/8 vectors of 8 lanes, four
+// interleaved vector accumulators take vectors 0-3 and then 4-7, the accumulators are added left
+// to right, and the 8 lanes of the result are added left to right.  The reference's (lo, step)
+// depend on these sums to the last bit (the least-squares formulas cancel), so with this order
+// the search returns the reference's ladders bit for bit; a plain left-to-right sum does not.
+template <int B>
+__device__ __forceinline__ float fold_lane(const float (&v)[B / 8]) {
+  if constexpr (B == 16) {
+    return v[0] + v[1];
+  } else if constexpr (B == 32) {
+    return ((v[0] + v[1]) + v[2]) + v[3];
+  } else {
+    return (((v[0] + v[4]) + (v[1] + v[5])) + (v[2] + v[6])) + (v[3] + v[7]);
+  }
+}
+
 template <int B, bool WIDE>
 __device__ __forceinline__ float block_error(const BlockRegs<B, WIDE>& r, const float* __restrict__ dd,
                                              bool a_valid, float lo, float step, float nmax) {
@@ -42,21 +59,35 @@ __device__ __forceinline__ float block_error(const BlockRegs<B, WIDE>& r, const 
   float err = 0.0f;
   if (rc.fast) {
 #pragma unroll
-    for (int t = 0; t < B; ++t) {
-      const float num = (WIDE && a_valid) ? r.a[t] : r.x[t] - lo;
-      const float q0 = num * rc.r;
-      float q = rintf(fmaf(fmaf(-q0, safe, num), rc.r, q0));
-      q = fminf(fmaxf(q, 0.0f), nmax);
-      const float diff = (lo + q * step) - r.x[t];
-      err += (WIDE ? r.d[t] : __ldg(dd + t)) * (diff * diff);
+    for (int l = 0; l < 8; ++l) {
+      float v[B / 8];
+#pragma unroll
+      for (int j = 0; j < B / 8; ++j) {
+        const int t = 8 * j + l;
+        const float num = (WIDE && a_valid) ? r.a[t] : r.x[t] - lo;
+        const float q0 = num * rc.r;
+        float q = rintf(fmaf(fmaf(-q0, safe, num), rc.r, q0));
+        q = fminf(fmaxf(q, 0.0f), nmax);
+        const float diff = (lo + q * step) - r.x[t];
+        v[j] = (WIDE ? r.d[t] : __ldg(dd + t)) * (diff * diff);
+      }
+      const float s = fold_lane<B>(v);
+      err = (l == 0) ? s : err + s;
     }
   } else {
 #pragma unroll
-    for (int t = 0; t < B; ++t) {
-      float q = rintf(__fdiv_rn(r.x[t] - lo, safe));
-      q = fminf(fmaxf(q, 0.0f), nmax);
-      const float diff = (lo + q * step) - r.x[t];
-      err += (WIDE ? r.d[t] : __ldg(dd + t)) * (diff * diff);
+    for (int l = 0; l < 8; ++l) {
+      float v[B / 8];
+#pragma unroll
+      for (int j = 0; j < B / 8; ++j) {
+        const int t = 8 * j + l;
+        float q = rintf(__fdiv_rn(r.x[t] - lo, safe));
+        q = fminf(fmaxf(q, 0.0f), nmax);
+        const float diff = (lo + q * step) - r.x[t];
+        v[j] = (WIDE ? r.d[t] : __ldg(dd + t)) * (diff * diff);
+      }
+      const float s = fold_lane<B>(v);
+      err = (l == 0) ? s : err + s;
     }
   }
   return err;
@@ -78,17 +109,25 @@ __device__ __forceinline__ void block_error2(const BlockRegs<B, WIDE>& r, const 
   }
   float ea = 0.0f, eb = 0.0f;
 #pragma unroll
-  for (int t = 0; t < B; ++t) {
-    const float num = WIDE ? r.a[t] : r.x[t] - lo;
-    const float dt = WIDE ? r.d[t] : __ldg(dd + t);
-    const float qa0 = num * ra.r, qb0 = num * rb.r;
-    float qa = rintf(fmaf(fmaf(-qa0, safe_a, num), ra.r, qa0));
-    float qb = rintf(fmaf(fmaf(-qb0, safe_b, num), rb.r, qb0));
-    qa = fminf(fmaxf(qa, 0.0f), nmax);
-    qb = fminf(fmaxf(qb, 0.0f), nmax);
-    const float da = (lo + qa * step_a) - r.x[t], db = (lo + qb * step_b) - r.x[t];
-    ea += dt * (da * da);
-    eb += dt * (db * db);
+  for (int l = 0; l < 8; ++l) {
+    float va[B / 8], vb[B / 8];
+#pragma unroll
+    for (int j = 0; j < B / 8; ++j) {
+      const int t = 8 * j + l;
+      const float num = WIDE ? r.a[t] : r.x[t] - lo;
+      const float dt = WIDE ? r.d[t] : __ldg(dd + t);
+      const float qa0 = num * ra.r, qb0 = num * rb.r;
+      float qa = rintf(fmaf(fmaf(-qa0, safe_a, num), ra.r, qa0));
+      float qb = rintf(fmaf(fmaf(-qb0, safe_b, num), rb.r, qb0));
+      qa = fminf(fmaxf(qa, 0.0f), nmax);
+      qb = fminf(fmaxf(qb, 0.0f), nmax);
+      const float da = (lo + qa * step_a) - r.x[t], db = (lo + qb * step_b) - r.x[t];
+      va[j] = dt * (da * da);
+      vb[j] = dt * (db * db);
+    }
+    const float sa = fold_lane<B>(va), sb = fold_lane<B>(vb);
+    ea = (l == 0) ? sa : ea + sa;
+    eb = (l == 0) ? sb : eb + sb;
   }
   err_a = ea, err_b = eb;
 }
@@ -152,23 +191,30 @@ fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d
     const Recip rc = make_recip(safe);
     float sd = 0.f, sc = 0.f, scc = 0.f, sw = 0.f, scw = 0.f, sum = 0.f;
 #pragma unroll
-    for (int t = 0; t < B; ++t) {
-      const float num = r.x[t] - best_lo;
-      float c;
-      if (rc.fast) {
-        const float q0 = num * rc.r;
-        c = rintf(fmaf(fmaf(-q0, safe, num), rc.r, q0));
-      } else {
-        c = rintf(__fdiv_rn(num, safe));
+    for (int l = 0; l < 8; ++l) {
+      float vd[B / 8], vc[B / 8], vcc[B / 8], vw[B / 8], vcw[B / 8], vx[B / 8];
+#pragma unroll
+      for (int j = 0; j < B / 8; ++j) {
+        const int t = 8 * j + l;
+        const float num = r.x[t] - best_lo;
+        float c;
+        if (rc.fast) {
+          const float q0 = num * rc.r;
+          c = rintf(fmaf(fmaf(-q0, safe, num), rc.r, q0));
+        } else {
+          c = rintf(__fdiv_rn(num, safe));
+        }
+        c = fminf(fmaxf(c, 0.0f), nmax);
+        const float dt = WIDE ? r.d[t] : __ldg(dd + t), dc = dt * c;
+        vd[j] = dt, vc[j] = dc, vcc[j] = dc * c, vw[j] = dt * r.x[t], vcw[j] = dc * r.x[t], vx[j] = r.x[t];
       }
-      c = fminf(fmaxf(c, 0.0f), nmax);
-      const float dt = WIDE ? r.d[t] : __ldg(dd + t), dc = dt * c;
-      sd += dt;
-      sc += dc;
-      scc += dc * c;
-      sw += dt * r.x[t];
-      scw += dc * r.x[t];
-      sum += r.x[t];
+      const float fd = fold_lane<B>(vd), fc = fold_lane<B>(vc), fcc = fold_lane<B>(vcc), fw = fold_lane<B>(vw),
+                  fcw = fold_lane<B>(vcw), fx = fold_lane<B>(vx);
+      if (l == 0) {
+        sd = fd, sc = fc, scc = fcc, sw = fw, scw = fcw, sum = fx;
+      } else {
+        sd += fd, sc += fc, scc += fcc, sw += fw, scw += fcw, sum += fx;
+      }
     }
     const float det = sd * scc - sc * sc;
     const bool ok = fabsf(det) > 1e-20f;

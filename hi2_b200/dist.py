@@ -159,6 +159,54 @@ def gather_error_tables(tables: list, make):
     return out
 
 
+def gather_tables_known_layout(local: list, specs: list, make) -> list:
+    """All error tables of a job whose table list every rank can write down beforehand.
+
+    ``specs`` lists every table of the job in one global order as ``(owner rank, name, shape,
+    candidates, n_tokens, has smoothing vector)``; ``local`` holds this rank's tables in that
+    order.  Nothing but numbers crosses the wire and the host never waits: each rank sends ONE flat
+    fp32 tensor (per table its energy, then ``sse [C, R]`` row-major; padded to the longest rank)
+    through one ``all_gather``.  Returns table objects in the order of ``specs``; local ones are
+    returned as they are, the others are built by ``make(**fields)`` around views of the gathered
+    buffer."""
+    if world_size() == 1:
+        return list(local)
+    me = rank()
+    sizes = [0] * world_size()
+    for owner, _, shape, cands, _, _ in specs:
+        sizes[owner] += 1 + len(cands) * shape[0]
+    if local:
+        dev = local[0].sse.device
+    else:
+        dev = torch.device("cpu") if dist.get_backend() == "gloo" else torch.device("cuda", torch.cuda.current_device())
+    mine = torch.zeros(max(sizes), dtype=torch.float32, device=dev)
+    off = 0
+    for t in local:
+        e = t.energy if isinstance(t.energy, torch.Tensor) else torch.tensor(float(t.energy))
+        n = t.sse.numel()
+        mine[off] = e.to(dev, torch.float32).reshape(())
+        mine[off + 1 : off + 1 + n] = t.sse.reshape(-1)
+        off += 1 + n
+    if off != sizes[me]:
+        raise ValueError("local tables do not match the layout")
+    parts = [torch.empty_like(mine) for _ in range(world_size())]
+    dist.all_gather(parts, mine)
+    offs = [0] * world_size()
+    it = iter(local)
+    out = []
+    for owner, name, shape, cands, n_tokens, scaled in specs:
+        if owner == me:
+            out.append(next(it))
+            continue
+        buf, o = parts[owner], offs[owner]
+        c, rows = len(cands), shape[0]
+        out.append(make(name=name, shape=tuple(shape), had=None, sse=buf[o + 1 : o + 1 + c * rows].view(c, rows),
+                        candidates=list(cands), energy=buf[o], n_tokens=n_tokens,
+                        col_scale=torch.empty(0) if scaled else None))
+        offs[owner] = o + 1 + c * rows
+    return out
+
+
 def barrier() -> None:
     if world_size() > 1:
         dist.barrier()

@@ -96,11 +96,11 @@ def pack_codes(codes: torch.Tensor, nbits: int) -> torch.Tensor:
 
 
 def unpack_codes(words: torch.Tensor, nbits: int) -> torch.Tensor:
-    per_word = 32 // nbits
-    w = words.to(torch.int64) & 0xFFFFFFFF
-    mask = (1 << nbits) - 1
-    c = torch.stack([(w >> (nbits * i)) & mask for i in range(per_word)], dim=-1)
-    return c.reshape(*words.shape[:-1], -1)
+    """Inverse of :func:`pack_codes` (hi2/format.py:88-93): field ``i`` of a word occupies bits
+    ``[i * nbits, (i + 1) * nbits)``.  Returns int64 codes ``[..., n_words * 32 / nbits]``."""
+    shifts = torch.arange(0, 32, nbits, device=words.device)
+    fields = (words.to(torch.int64).unsqueeze(-1) >> shifts) & (2**nbits - 1)
+    return fields.flatten(-2)
 
 
 # ---- tensor container ---------------------------------------------------------------------------

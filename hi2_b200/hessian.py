@@ -183,6 +183,15 @@ class FactorJob:
         self.done.synchronize()
         return int(self.info.item()) == 0 and bool(torch.isfinite(self.u.diagonal()).all())
 
+    def release_scratch(self) -> None:
+        """Drop the damped input and the scratch of the attempt in flight (about five times the
+        bytes of ``U``).  Both were allocated on the stream the attempt runs on, so the caching
+        allocator hands them out again only to later work of that stream.  A job released this
+        way cannot retry: a caller that finds :meth:`succeeded` false factorises again from the
+        second moment."""
+        self.h = None
+        self.ws = None
+
     def _launch(self) -> None:
         self.lam = (self.damp * self.mean * 10**self.attempt).to(torch.float32).reshape(1)
         self.info.zero_()
@@ -192,6 +201,8 @@ class FactorJob:
         )
 
     def result(self) -> torch.Tensor:
+        if self.h is None:
+            raise RuntimeError("FactorJob.result() after release_scratch(): use first_attempt()/succeeded()")
         with torch.cuda.stream(self.stream):
             while True:
                 last = int(self.info.item())
@@ -350,12 +361,14 @@ def _use_kernel(dev: torch.device, backend: str) -> bool:
 
 @torch.no_grad()
 def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str | None = None,
-                     comp: bool = False) -> list[Encoded]:
+                     comp: bool = False, timing: list | None = None) -> list[Encoded]:
     """:func:`encode_rows_gptq` for several jobs (tensors, experts, candidate groups) at once.
 
     Jobs are cut into row units; units with the same K on the same device are batched (up to
     ``BATCH_ELEMS`` weights) through one column loop.  With ``comp`` every result carries
-    ``Encoded.comp``, the value each code was rounded from."""
+    ``Encoded.comp``, the value each code was rounded from.  ``timing`` (optional list) receives one
+    ``(K, rows, start event, end event)`` per width: the column loops of that width (block kernel +
+    trailing updates) on their stream, for a caller that reports rows per second of the loop."""
     backend = backend or os.environ.get("HI2_GPTQ_BACKEND", "auto")
     # Widths are independent column loops of many short launches.  The jobs of one width are
     # prepared (ladders, parameter bytes) on the current stream and their column loop is then
@@ -388,9 +401,16 @@ def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str |
         side = _side_stream(dev, gi + 1)
         side.wait_stream(main)
         with torch.cuda.stream(side):
+            if timing is not None:
+                t0 = torch.cuda.Event(enable_timing=True)
+                t0.record()
             for batch in bl:
                 if batch:  # a width whose jobs have no rows leaves one empty batch
                     _round_units(batch, jobs, comp, splits, checks)
+            if timing is not None:
+                t1 = torch.cuda.Event(enable_timing=True)
+                t1.record()
+                timing.append((k, sum(x.rows for x in mine), t0, t1))
         joins.append((main, side))
     for main, side in joins:
         main.wait_stream(side)

@@ -83,10 +83,13 @@ def _side_stream(device, i: int) -> torch.cuda.Stream:
     return _side_streams[key]
 
 
-def start_factors(shared: dict, cfg: Config, device, only: str | None = None, into: dict | None = None) -> dict:
+def start_factors(shared: dict, cfg: Config, device, only: str | None = None, into: dict | None = None,
+                  release_scratch: bool = False) -> dict:
     """Basis change and inverse factor of every input (or of input ``only``), each on a stream of
     its own, started now so they run beside the tables (which do not need them).  Pass the result
-    to :func:`encode`."""
+    to :func:`encode`.  ``release_scratch`` frees each factorisation's input and scratch as soon
+    as it is enqueued (a model's worth of factors in flight would otherwise hold five times the
+    bytes of the factors themselves); ``Hs`` is then not kept either, so not with refinement."""
     from .calibrate import factor_for
 
     main = torch.cuda.current_stream(device)
@@ -97,7 +100,11 @@ def start_factors(shared: dict, cfg: Config, device, only: str | None = None, in
         side = _side_stream(device, i)
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            out[s.name] = factor_for(s.hessian.S, s.hessian.n, s.transform[0], s.transform[1], cfg)
+            d, job, hs = factor_for(s.hessian.S, s.hessian.n, s.transform[0], s.transform[1], cfg)
+            if release_scratch:
+                job.release_scratch()
+                hs = None
+            out[s.name] = (d, job, hs)
     return out
 
 
@@ -114,7 +121,7 @@ def tabulate(weights: dict, plan: LayerPlan, shared: dict, cfg: Config, only: st
 
 
 def encode(weights: dict, plan: LayerPlan, shared: dict, tables: dict, picks: dict, cfg: Config,
-           to_host: bool = True, factors: dict | None = None) -> dict:
+           to_host: bool = True, factors: dict | None = None, timing: list | None = None) -> dict:
     """Packed ``HI2Tensor`` of every weight for the allocator's ``picks``."""
     reqs, names = [], []
     for s in shared.values():
@@ -124,7 +131,7 @@ def encode(weights: dict, plan: LayerPlan, shared: dict, tables: dict, picks: di
         reqs.append(EncodeRequest(w, s.moments, tables[name], picks[name], sigma=s.hessian.S,
                                   sigma_id=s.name, sigma_n=s.hessian.n))
         names.append(name)
-    out = encode_many(reqs, cfg, to_host=to_host, factors=factors)
+    out = encode_many(reqs, cfg, to_host=to_host, factors=factors, timing=timing)
     return dict(zip(names, out))
 
 

@@ -97,19 +97,21 @@ def top_up(stats: dict, hess: dict | None, k_of: dict, min_tokens: float):
 
 
 def expert_weights(tables: dict, share_floor: float = 0.05) -> dict:
-    """Allocation multiplier per expert tensor: ``max(n_e / mean(n), share_floor) / E``."""
-    groups: dict[str, list[str]] = {}
-    for name in tables:
+    """Allocation multiplier of every expert tensor (hi2/moe.py:188-207): an expert's share of its
+    group's calibration tokens relative to an even split, floored at ``share_floor``, divided by
+    the number of experts in the group, so a group weighs as much as one dense tensor."""
+    members: dict[str, list[tuple[str, int]]] = {}
+    for name, table in tables.items():
         if expert_parts(name) is not None:
-            groups.setdefault(group_key(name), []).append(name)
-    out: dict[str, float] = {}
-    for names in groups.values():
-        ns = [tables[n].n_tokens for n in names]
-        mean = sum(ns) / len(ns)
-        for n, c in zip(names, ns):
-            share = c / mean if mean > 0 else 1.0
-            out[n] = max(share, share_floor) / len(names)
-    return out
+            members.setdefault(group_key(name), []).append((name, table.n_tokens))
+    weights: dict[str, float] = {}
+    for group in members.values():
+        experts = len(group)
+        even = sum(tokens for _, tokens in group) / experts
+        for name, tokens in group:
+            relative = tokens / even if even > 0 else 1.0
+            weights[name] = max(relative, share_floor) / experts
+    return weights
 
 
 __all__ = ["expert_parts", "group_key", "sibling_leader", "blend", "accumulate_routed", "top_up",

@@ -55,18 +55,24 @@ class ColumnStats:
         self.n += other.n
 
     def diag(self, flags: torch.Tensor | None = None, inv_scale: torch.Tensor | None = None):
-        """``E[x_j^2]`` per column of ``x * inv_scale``, in the rotated basis where flagged."""
-        s = self.S / max(self.n, 1)
+        """Mean square of every column of ``x * inv_scale`` after the flagged groups have been
+        rotated: the diagonal of ``T_g M_g T_g^T`` per group, ``M_g`` the group's mean moment and
+        ``T_g`` the rotation (or the identity).  fp64 throughout, returned as fp32 ``[K]``
+        (hi2/stats.py:39-54)."""
+        moment = self.S / max(self.n, 1)
+        dev = moment.device
         if inv_scale is not None:
-            inv = inv_scale.to(s.device, s.dtype).reshape(-1, GROUP)
-            s = s * inv[:, :, None] * inv[:, None, :]
-        plain = torch.diagonal(s, dim1=1, dim2=2)
+            # scale first (rows, then columns), then rotate: the order the reference rounds in
+            v = inv_scale.to(dev, moment.dtype).reshape(-1, GROUP)
+            moment = moment * v.unsqueeze(2) * v.unsqueeze(1)
+        unrotated = moment.diagonal(dim1=-2, dim2=-1)
         if flags is None:
-            return plain.reshape(-1).float()
-        h = hadamard16(torch.float64, s.device)
-        rot = ((h @ s) * h).sum(-1)  # diag(h s h) per group, h symmetric
-        f = flags.to(s.device).bool().reshape(-1, 1)
-        return torch.where(f, rot, plain).reshape(-1).float()
+            return unrotated.flatten().float()
+        basis = hadamard16(torch.float64, dev)
+        # (T M T^T)_ii = sum_jk T_ij M_jk T_ik
+        rotated = torch.einsum("ij,gjk,ik->gi", basis, moment, basis)
+        chosen = torch.where(flags.to(dev).reshape(-1, 1) != 0, rotated, unrotated)
+        return chosen.flatten().float()
 
     def state(self) -> dict:
         return {"S": self.S.cpu(), "n": self.n, "k": self.k}

@@ -125,6 +125,24 @@ for r in range(world):
     assert tuple(a.sse.shape) == (2, 3 + r) and bool((a.sse == float(r)).all()) and a.energy == 1.0 + r
     assert tuple(b.sse.shape) == (1, 2) and bool((b.sse == 10.0 + r).all())
     assert (a.col_scale is not None) == (r == 0) and b.col_scale is None
+# the same tables through the fixed-layout gather: no metadata exchange, one all_gather
+specs = [(r, f"r{r}.{x}", (3 + r, 64) if x == "a" else (2, 32), [(2, 16), (4, 16)] if x == "a" else [(2, 16)], 5,
+          x == "a" and r == 0) for r in range(world) for x in "ab"]
+every = hd.gather_tables_known_layout(local, specs, lambda **kw: NS(**kw))
+assert [t.name for t in every] == ["r0.a", "r0.b", "r1.a", "r1.b"]
+assert every[2 * rank] is local[0] and every[2 * rank + 1] is local[1]
+for r in range(world):
+    a, b = every[2 * r], every[2 * r + 1]
+    assert tuple(a.sse.shape) == (2, 3 + r) and bool((a.sse == float(r)).all()) and float(a.energy) == 1.0 + r
+    assert tuple(b.sse.shape) == (1, 2) and bool((b.sse == 10.0 + r).all()) and float(b.energy) == 2.0
+    assert (a.col_scale is not None) == (r == 0) and b.col_scale is None
+# layers interleaved over the ranks (layer l on rank l mod world), as a whole-model job lays them out
+specs = [(l % world, f"L{l}", (2, 16), [(2, 16)], 7, False) for l in range(4)]
+mine = [NS(name=f"L{l}", shape=(2, 16), candidates=[(2, 16)], energy=float(l), n_tokens=7, col_scale=None,
+           sse=torch.full((1, 2), float(l))) for l in range(4) if l % world == rank]
+every = hd.gather_tables_known_layout(mine, specs, lambda **kw: NS(**kw))
+assert [t.name for t in every] == ["L0", "L1", "L2", "L3"]
+assert all(float(t.energy) == float(l) and bool((t.sse == float(l)).all()) for l, t in enumerate(every))
 hd.barrier()
 print("ok", rank)
 """
