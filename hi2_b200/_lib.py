@@ -27,7 +27,7 @@ SIGNATURES = {
     "hi2_abi_version": (_I, []),
     "hi2_last_error": (C.c_char_p, []),
     "hi2_launch_count": (C.c_longlong, []),
-    "hi2_hessian_kernel_info": (_I, [_P]),
+    "hi2_graph_launch_count": (C.c_longlong, []),
     "hi2_rotate_groups": (_I, [_P, _I, _P, _I, _P, _P, _L, _L, _P]),
     "hi2_pack_codes": (_I, [_P, _P, _L, _L, _I, _P, _P]),
     "hi2_assemble_piece": (_I, [_P, _L, _P, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
@@ -100,6 +100,10 @@ def failure() -> str | None:
 
 def launch_count() -> int:
     return int(load().hi2_launch_count())
+
+
+def graph_launch_count() -> int:
+    return int(load().hi2_graph_launch_count())
 
 
 def last_error() -> str:

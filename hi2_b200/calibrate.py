@@ -50,7 +50,7 @@ class TensorTable:
     candidates: list
     energy: float | torch.Tensor  # sum d * w^2; a 0-dim device tensor until someone reads it
     n_tokens: int
-    col_scale: torch.Tensor | None = None  # fp16 [K]
+    col_scale: torch.Tensor | None = None  # fp16 [K]; on the device when the table was built there
 
 
 def candidate_row_bits(nbits: int, block: int, k: int) -> float:
@@ -109,10 +109,11 @@ def build_table(name: str, w: torch.Tensor, stats: ColumnStats | None, cfg: Conf
         sse.append(enc.sse)
         if i == 0:
             energy = enc.energy
+    # nothing is read back here: the smoothing vector stays where it was computed (the device) and
+    # the energy is a device scalar, so the host can queue the next table while this one runs
     return TensorTable(
-        name, (r, k), had.cpu(), torch.stack(sse), list(cfg.candidates), energy.sum(),  # no sync here
-        n_tokens if n_tokens is not None else (stats.n if stats else 0),
-        None if s16 is None else s16.cpu(),
+        name, (r, k), had.cpu(), torch.stack(sse), list(cfg.candidates), energy.sum(),
+        n_tokens if n_tokens is not None else (stats.n if stats else 0), s16,
     )
 
 
@@ -136,6 +137,12 @@ def _transform_key(col_scale, had):
     return cs, had.detach().cpu().to(torch.uint8).numpy().tobytes()
 
 
+def _job_key(job):
+    if job.transform_key is None:
+        job.transform_key = _transform_key(*job.transform)
+    return job.transform_key
+
+
 def _factor_key(req: EncodeRequest, i: int):
     t = req.table
     sid = req.sigma_id if req.sigma_id is not None else f"#{i}"
@@ -154,7 +161,11 @@ def factor_for(sigma, sigma_n, col_scale, had, cfg: Config):
     d_ready.record()
     job = FactorJob(hs, cfg.damp)
     job.d_ready = d_ready
-    job.transform_key = _transform_key(col_scale, had)  # a factor belongs to ONE (input, s, flags)
+    # A factor belongs to ONE (input, smoothing vector, flags).  The key is only made when someone
+    # compares it (encode_many): reading the smoothing vector back here would make the host wait
+    # for the factorisation that was just enqueued.
+    job.transform = (col_scale, had)
+    job.transform_key = None
     return d, job, hs
 
 
@@ -183,7 +194,7 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
         use_gptq = cfg.rounding == "gptq" and r.sigma is not None
         if use_gptq:
             fk = _factor_key(r, ri)
-            if fk not in factors and r.sigma_id in ready and ready[r.sigma_id][1].transform_key == fk[1:]:
+            if fk not in factors and r.sigma_id in ready and _job_key(ready[r.sigma_id][1]) == fk[1:]:
                 # started earlier on a side stream for this very (input, smoothing vector, flags):
                 # order after it on the device, never on the host, so the narrow matrices are rounded
                 # while the widest factor is still being computed.  d is complete at d_ready; U only

@@ -33,6 +33,29 @@ inline int check_launch(const char* what) {
   return HI2_OK;
 }
 
+// A long chain of short kernels queued as ONE graph launch.  Between construction and finish()
+// everything the calling thread launches on `stream` is captured instead of run; finish()
+// instantiates the captured graph and launches it on the stream.  Why: a stream's launch queue
+// holds about a thousand entries, so a chain of 1700 small kernels (the inverse factor of one
+// input) throttles the host to the GPU's pace until it has drained, and the host cannot feed the
+// other streams meanwhile - the chains of four inputs then run one after the other instead of
+// side by side; as a graph the chain costs the host one launch and its kernels start back to back.
+// A stream that is already being captured by the caller is left alone (the launches then join the
+// caller's graph).  Finished graphs are destroyed on later calls, once their completion event has
+// passed.
+class ChainGraph {
+ public:
+  explicit ChainGraph(cudaStream_t stream);
+  // rc: the status of the launches issued since construction.  Returns rc if it is an error (the
+  // captured work is dropped), else the status of instantiating and launching the graph.
+  int finish(int rc, const char* what);
+  ~ChainGraph();
+
+ private:
+  cudaStream_t stream_;
+  bool capturing_ = false;
+};
+
 #define HI2_REQUIRE(cond, msg)                         \
   do {                                                 \
     if (!(cond)) return ::hi2::fail(HI2_ERR_ARG, msg); \

@@ -32,6 +32,10 @@ struct GemmArgs {
   T* c;
   int64_t ldc;
   int flags;
+  // reduction window: only k in [k_begin, k_end) is summed (k_begin a multiple of 16).  A caller
+  // that wants a long reduction added up in pieces calls once per window with beta = 1 after the
+  // first, which bounds the length of any one fp32 accumulation chain.
+  int64_t k_begin = 0, k_end = INT64_MAX;
 };
 
 template <typename T>
@@ -71,6 +75,7 @@ gemm_kernel(const GemmArgs<T, TA, TB> p) {
   if (p.flags & GEMM_KA_LE_I) k_hi = min(k_hi, m0 + BM);
   if (p.flags & GEMM_KB_LE_J) k_hi = min(k_hi, n0 + BN);
   if (p.flags & GEMM_KB_GE_J) k_lo = (n0 / BK) * BK;
+  k_lo = max(k_lo, p.k_begin), k_hi = min(k_hi, p.k_end);
 
   T acc[TM][TN];
 #pragma unroll
@@ -185,6 +190,7 @@ gemm_async_kernel(const GemmArgs<T, T, T> p) {
   if (p.flags & GEMM_KA_LE_I) k_hi = min(k_hi, m0 + BM);
   if (p.flags & GEMM_KB_LE_J) k_hi = min(k_hi, n0 + BN);
   if (p.flags & GEMM_KB_GE_J) k_lo = (n0 / BK) * BK;
+  k_lo = max(k_lo, p.k_begin), k_hi = min(k_hi, p.k_end);
 
   auto issue = [&](int64_t k0, int slot) {
     T* as = As + slot * A_STAGE;

@@ -340,25 +340,29 @@ extern "C" int hi2_gptq_round(float* wc, int64_t n_rows, int64_t k, float* err1,
   HI2_REQUIRE(unit_rows_host[0] == 0 && unit_rows_host[n_units] == n_rows,
               "gptq_round: units must cover the rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  for (int64_t i1 = 0; i1 < k; i1 += LMAX) {
-    const int64_t i2 = (i1 + LMAX < k) ? i1 + LMAX : k;
-    const int len = (int)(i2 - i1);
-    int rc = check_block_args(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs,
-                              blk, nmax, comp);
-    if (rc != HI2_OK) return rc;
-    rc = launch_block(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs, blk, nmax,
-                      comp, s);
-    if (rc != HI2_OK) return rc;
-    if (i2 == k) break;
-    for (int un = 0; un < n_units; ++un) {
-      const int64_t r0 = unit_rows_host[un], r1 = unit_rows_host[un + 1];
-      if (r1 <= r0) continue;
-      rc = launch_lazy(wc + r0 * k, r1 - r0, k, i1, i2, err1 + r0 * len,
-                       reinterpret_cast<const float*>(u_host[un]), s);
+  ChainGraph chain(s);  // the K/128 segments and their trailing updates as one graph launch
+  auto enqueue = [&]() -> int {
+    for (int64_t i1 = 0; i1 < k; i1 += LMAX) {
+      const int64_t i2 = (i1 + LMAX < k) ? i1 + LMAX : k;
+      const int len = (int)(i2 - i1);
+      int rc = check_block_args(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs,
+                                blk, nmax, comp);
       if (rc != HI2_OK) return rc;
+      rc = launch_block(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs, blk, nmax,
+                        comp, s);
+      if (rc != HI2_OK) return rc;
+      if (i2 == k) break;
+      for (int un = 0; un < n_units; ++un) {
+        const int64_t r0 = unit_rows_host[un], r1 = unit_rows_host[un + 1];
+        if (r1 <= r0) continue;
+        rc = launch_lazy(wc + r0 * k, r1 - r0, k, i1, i2, err1 + r0 * len,
+                         reinterpret_cast<const float*>(u_host[un]), s);
+        if (rc != HI2_OK) return rc;
+      }
     }
-  }
-  return HI2_OK;
+    return HI2_OK;
+  };
+  return chain.finish(enqueue(), "gptq_round");
 }
 
 extern "C" int hi2_gptq_lazy_update_tc(float* wc, int64_t n_rows, int64_t k, int64_t i1,
@@ -388,32 +392,36 @@ extern "C" int hi2_gptq_round_tc(float* wc, int64_t n_rows, int64_t k, float* er
   HI2_REQUIRE(err_split && status && aligned16(err_split), "gptq_round_tc: scratch missing or unaligned");
   HI2_REQUIRE(k % 4 == 0, "gptq_round_tc: k must be a multiple of 4");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (cudaMemsetAsync(status, 0, sizeof(int32_t), s) != cudaSuccess)
-    return fail(HI2_ERR_LAUNCH, "gptq_round_tc: memset failed");
   float* err_hi = err_split;
   float* err_lo = err_split + n_rows * LMAX;
-  for (int64_t i1 = 0; i1 < k; i1 += LMAX) {
-    const int64_t i2 = (i1 + LMAX < k) ? i1 + LMAX : k;
-    const int len = (int)(i2 - i1);
-    int rc = check_block_args(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs,
-                              blk, nmax, comp);
-    if (rc != HI2_OK) return rc;
-    rc = launch_block(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs, blk, nmax,
-                      comp, s);
-    if (rc != HI2_OK) return rc;
-    if (i2 == k) break;  // a block shorter than 128 columns is always the last one
-    rc = launch_split_tf32(err1, err_hi, err_lo, n_rows * LMAX, s);
-    if (rc != HI2_OK) return rc;
-    for (int un = 0; un < n_units; ++un) {
-      const int64_t r0 = unit_rows_host[un], r1 = unit_rows_host[un + 1];
-      if (r1 <= r0) continue;
-      const float* u_hi = reinterpret_cast<const float*>(u_split_host[un]);
-      rc = launch_lazy_tc(wc + r0 * k, r1 - r0, k, i1, err_hi + r0 * LMAX, err_lo + r0 * LMAX, u_hi,
-                          u_hi + k * k, reinterpret_cast<int*>(status), s);
+  ChainGraph chain(s);  // the K/128 segments and their trailing updates as one graph launch
+  auto enqueue = [&]() -> int {
+    if (cudaMemsetAsync(status, 0, sizeof(int32_t), s) != cudaSuccess)
+      return fail(HI2_ERR_LAUNCH, "gptq_round_tc: memset failed");
+    for (int64_t i1 = 0; i1 < k; i1 += LMAX) {
+      const int64_t i2 = (i1 + LMAX < k) ? i1 + LMAX : k;
+      const int len = (int)(i2 - i1);
+      int rc = check_block_args(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs,
+                                blk, nmax, comp);
       if (rc != HI2_OK) return rc;
+      rc = launch_block(wc, n_rows, k, i1, len, err1, codes, lo, st, ldp, row_grp, u_ptrs, blk, nmax,
+                        comp, s);
+      if (rc != HI2_OK) return rc;
+      if (i2 == k) break;  // a block shorter than 128 columns is always the last one
+      rc = launch_split_tf32(err1, err_hi, err_lo, n_rows * LMAX, s);
+      if (rc != HI2_OK) return rc;
+      for (int un = 0; un < n_units; ++un) {
+        const int64_t r0 = unit_rows_host[un], r1 = unit_rows_host[un + 1];
+        if (r1 <= r0) continue;
+        const float* u_hi = reinterpret_cast<const float*>(u_split_host[un]);
+        rc = launch_lazy_tc(wc + r0 * k, r1 - r0, k, i1, err_hi + r0 * LMAX, err_lo + r0 * LMAX, u_hi,
+                            u_hi + k * k, reinterpret_cast<int*>(status), s);
+        if (rc != HI2_OK) return rc;
+      }
     }
-  }
-  return HI2_OK;
+    return HI2_OK;
+  };
+  return chain.finish(enqueue(), "gptq_round_tc");
 }
 
 extern "C" int hi2_gemm_f32(int trans_a, int trans_b, int64_t m, int64_t n, int64_t kk, float alpha,

@@ -420,9 +420,6 @@ bool use_tc(int dtype, int64_t tokens, int64_t k) {
 // that they fall out of step in L2 (DRAM reads of 10.9 x X at K = 11008 against 6.2 x for 148
 // one-block tiles, same time, less stable), so the widest inputs stay with the one-block kernel.
 bool use_pair(int dtype, int64_t tokens, int64_t k) {
-#ifdef HI2_NO_PAIR
-  return false;
-#endif
   return use_tc(dtype, tokens, k) && k >= 1024 && k <= 8192 && tokens >= 8192;
 }
 
@@ -517,24 +514,6 @@ extern "C" int hi2_hessian_accumulate(const void* x, int dtype, int64_t tokens, 
   if (dtype == HI2_F16) return accumulate_fma<__half>(x, tokens, k, s, st);
   if (dtype == HI2_F32) return accumulate_fma<float>(x, tokens, k, s, st);
   return fail(HI2_ERR_ARG, "hessian_accumulate: dtype must be F16, BF16 or F32");
-}
-
-// Launch-resource figures of the tensor-core kernel on the current device (diagnostics):
-// out = {registers, static smem, max dynamic smem, max threads per block, active blocks per SM
-// at the launch configuration, requested dynamic smem, threads}.
-extern "C" int hi2_hessian_kernel_info(int64_t* out) {
-  using namespace hi2;
-  HI2_REQUIRE(out != nullptr, "hessian_kernel_info: null pointer");
-  cudaFuncSetAttribute(hessian_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
-  cudaFuncAttributes a;
-  if (cudaFuncGetAttributes(&a, hessian_tc_kernel) != cudaSuccess)
-    return fail(HI2_ERR_LAUNCH, "hessian_kernel_info: cudaFuncGetAttributes failed");
-  int blocks = -1;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, hessian_tc_kernel, TC_THREADS, TC_SMEM);
-  out[0] = a.numRegs, out[1] = (int64_t)a.sharedSizeBytes, out[2] = a.maxDynamicSharedSizeBytes;
-  out[3] = a.maxThreadsPerBlock, out[4] = blocks, out[5] = (int64_t)TC_SMEM, out[6] = TC_THREADS;
-  cudaGetLastError();
-  return HI2_OK;
 }
 
 // --------------------------------------------------------------------------------------------

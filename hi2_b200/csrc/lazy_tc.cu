@@ -260,8 +260,15 @@ lazy_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
 // A and Bt are given as their TF32 parts (K-major, leading dimension ldk), C is fp32 with its own
 // leading dimension.  Triangular operands are expressed as reduction ranges per tile (the same
 // flags as gemm.cuh): the skipped range holds exact zeros, so taking whole 32-wide stages of it
-// changes nothing.  The result is stored (beta = 0) or added (beta = 1) by TMA, which clips the
-// boxes at the edge of C, so m and n need no alignment.
+// changes nothing.  The reduction of a tile is cut into windows of G_WINDOW stages (64 values of
+// k): each window is accumulated in its own TMEM buffer and ADDED to C by TMA (round-to-nearest
+// adds in L2), the windows of a tile in order.  The tensor core's own accumulator truncates, so a
+// chain of thousands of accumulation steps loses a decimal digit that the heavy cancellation of
+// the factor recursion then exposes.  Measured on a rank-deficient 4096-wide Hessian (2048 tokens,
+// condition 1e5), error of U against an fp64 solution over max|U|: one chain per tile 4.4e-4,
+// windows of 256 4.1e-5, of 128 2.0e-5, of 64 1.2e-5 (the reference's fp32 LAPACK path: 8e-6), at
+// the same speed.  C therefore always receives adds: for a plain store the launcher zeroes C
+// first.  TMA clips the boxes at the edge of C, so m and n need no alignment.
 constexpr int GT_KB_LE_J = 1, GT_KB_GE_J = 2, GT_KA_LE_I = 4, GT_LOWER_OUT = 8, GT_NEGATE = 16, GT_ADD = 32;
 
 struct GParams {
@@ -278,12 +285,6 @@ __device__ __forceinline__ void mma_tf32_d(uint32_t d_tmem, uint64_t da, uint64_
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void tma_store(const CUtensorMap* map, const void* src, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
-      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(s32(src)), "r"(x), "r"(y) : "memory");
-}
-
 // Reduction stages [s0, s1) of tile (tr, tc), or s0 >= s1 for a tile that is not computed.
 __device__ __forceinline__ void tile_range(const GParams& p, int tr, int tc, int& s0, int& s1) {
   int k0 = 0, k1 = p.kk;
@@ -292,9 +293,10 @@ __device__ __forceinline__ void tile_range(const GParams& p, int tr, int tc, int
   if (p.flags & GT_KB_GE_J) k0 = tc * LN;
   s0 = k0 / KSTAGE;
   s1 = (k1 + KSTAGE - 1) / KSTAGE;
-  if (s1 <= s0) s1 = s0 + 1;  // an empty range still yields a (zero) tile
+  if (s1 < s0) s1 = s0;  // an empty range adds nothing: the tile of C keeps its (zeroed) content
   if ((p.flags & GT_LOWER_OUT) && tc * LN > tr * LM + LM - 1) s1 = s0;
 }
+constexpr int G_WINDOW = 2;  // stages per accumulation window
 
 __global__ void __launch_bounds__(L_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
@@ -358,68 +360,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
       const int tr = tile % p.row_tiles, tc = tile / p.row_tiles;
       int s0, s1;
       tile_range(p, tr, tc, s0, s1);
-      if (s1 <= s0) continue;
-      const int buf = n & 1;
-      if (!(ok = bar_wait(&ctl->acc_empty[buf], ((n >> 1) & 1) ^ 1, ctl, p.status))) break;
-      fence_after();
-      const uint32_t d_tmem = tmem_base + buf * LN;
-      for (int ks = s0; ks < s1 && ok; ++ks) {
-        if (!(ok = bar_wait(&ctl->full[stage], phase, ctl, p.status))) break;
+      for (int w0 = s0; w0 < s1 && ok; w0 += G_WINDOW) {  // one TMEM buffer per window
+        const int w1 = min(w0 + G_WINDOW, s1);
+        const int buf = n & 1;
+        if (!(ok = bar_wait(&ctl->acc_empty[buf], ((n >> 1) & 1) ^ 1, ctl, p.status))) break;
         fence_after();
-        const uint32_t sa = s32(smem + (size_t)stage * LSTAGE_BYTES);
+        const uint32_t d_tmem = tmem_base + buf * LN;
+        for (int ks = w0; ks < w1 && ok; ++ks) {
+          if (!(ok = bar_wait(&ctl->full[stage], phase, ctl, p.status))) break;
+          fence_after();
+          const uint32_t sa = s32(smem + (size_t)stage * LSTAGE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < KSTAGE / 8; ++kk) {
-          const uint64_t ahi = desc_kmajor(sa + kk * 32), alo = desc_kmajor(sa + A_BOX + kk * 32);
-          const uint64_t bhi = desc_kmajor(sa + 2 * A_BOX + kk * 32);
-          const uint64_t blo = desc_kmajor(sa + 2 * A_BOX + B_PART + kk * 32);
-          mma_tf32_d(d_tmem, ahi, bhi, idesc, (ks > s0 || kk > 0) ? 1u : 0u);
-          mma_tf32_d(d_tmem, alo, bhi, idesc, 1u);
-          mma_tf32_d(d_tmem, ahi, blo, idesc, 1u);
+          for (int kk = 0; kk < KSTAGE / 8; ++kk) {
+            const uint64_t ahi = desc_kmajor(sa + kk * 32), alo = desc_kmajor(sa + A_BOX + kk * 32);
+            const uint64_t bhi = desc_kmajor(sa + 2 * A_BOX + kk * 32);
+            const uint64_t blo = desc_kmajor(sa + 2 * A_BOX + B_PART + kk * 32);
+            mma_tf32_d(d_tmem, ahi, bhi, idesc, (ks > w0 || kk > 0) ? 1u : 0u);
+            mma_tf32_d(d_tmem, alo, bhi, idesc, 1u);
+            mma_tf32_d(d_tmem, ahi, blo, idesc, 1u);
+          }
+          commit_to(&ctl->empty[stage]);
+          if (++stage == LSTAGES) stage = 0, phase ^= 1;
         }
-        commit_to(&ctl->empty[stage]);
-        if (++stage == LSTAGES) stage = 0, phase ^= 1;
+        if (ok) commit_to(&ctl->acc_full[buf]);
+        ++n;
       }
-      if (ok) commit_to(&ctl->acc_full[buf]);
-      ++n;
     }
   } else if (warp < 4) {
     // ------------------------------------------------------------ epilogue
     uint32_t n = 0, chunk_no = 0;
     bool ok = true;
-    const bool add = (p.flags & GT_ADD) != 0;
     uint8_t* my_boxes = stage_c + warp * (2 * C_BOX / 4);  // two 4 KiB boxes per warp
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
       const int tr = tile % p.row_tiles, tc = tile / p.row_tiles;
       int s0, s1;
       tile_range(p, tr, tc, s0, s1);
-      if (s1 <= s0) continue;
-      const int buf = n & 1;
-      if (!(ok = bar_wait(&ctl->acc_full[buf], (n >> 1) & 1, ctl, p.status))) break;
-      fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * LN;
-      for (int c = 0; c < LN / 32; ++c, ++chunk_no) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c * 32, v);
-        uint8_t* box = my_boxes + (chunk_no & 1) * (C_BOX / 4);
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      for (int w0 = s0; w0 < s1 && ok; w0 += G_WINDOW) {
+        const int buf = n & 1;
+        if (!(ok = bar_wait(&ctl->acc_full[buf], (n >> 1) & 1, ctl, p.status))) break;
+        fence_after();
+        // the adds of the previous window of this tile have landed before this window's are sent:
+        // the windows reach every element of C in one fixed order (same bits on every run)
+        if (w0 > s0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         __syncwarp();
-        uint8_t* rowp = box + lane * 128;
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * LN;
+        for (int c = 0; c < LN / 32; ++c, ++chunk_no) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          uint8_t* box = my_boxes + (chunk_no & 1) * (C_BOX / 4);
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+          uint8_t* rowp = box + lane * 128;
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) =
-              make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          if (add) tma_reduce_add(&map_c, box, tc * LN + c * 32, tr * LM + warp * 32);
-          else tma_store(&map_c, box, tc * LN + c * 32, tr * LM + warp * 32);
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) =
+                make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add(&map_c, box, tc * LN + c * 32, tr * LM + warp * 32);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
+        fence_before();
+        __syncwarp();
+        if (lane == 0) bar_arrive(&ctl->acc_empty[buf]);
+        ++n;
       }
-      fence_before();
-      __syncwarp();
-      if (lane == 0) bar_arrive(&ctl->acc_empty[buf]);
-      ++n;
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
@@ -595,11 +602,14 @@ int launch_gemm_tc(int64_t m, int64_t n, int64_t kk, const float* a_hi, const fl
     return fail(HI2_ERR_DRIVER, "gemm_tc: cuTensorMapEncodeTiled failed");
   if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L_SMEM) != cudaSuccess)
     return fail(HI2_ERR_LAUNCH, "gemm_tc: cannot reserve shared memory");
+  if (!(flags & GT_ADD) &&  // the kernel only adds: a plain store starts from zeros
+      cudaMemset2DAsync(c, (size_t)ldc * sizeof(float), 0, (size_t)n * sizeof(float), (size_t)m, stream) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "gemm_tc: memset failed");
   GParams p;
   p.status = status;
   p.row_tiles = (int)ceil_div(m, LM);
   p.col_tiles = (int)ceil_div(n, LN);
-  p.kk = (int)kk, p.flags = flags;
+  p.kk = (int)kk, p.flags = flags | GT_ADD;
   const int tiles = p.row_tiles * p.col_tiles;
   int device = 0, sms = 148;
   cudaGetDevice(&device);

@@ -189,5 +189,5 @@ def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=N
         row_block=row_block.to("cpu", torch.uint8),
         had=had.to("cpu", torch.uint8).reshape(-1),
         shape=(r, k),
-        col_scale=col_scale,
+        col_scale=col_scale.cpu() if (to_host and col_scale is not None and col_scale.is_cuda) else col_scale,
     )

@@ -41,10 +41,10 @@ const char* hi2_last_error(void);
 /* Kernel launches this library has enqueued in the process so far (all threads).  No counterpart
  * in the reference; benchmarks difference it around a timed region. */
 long long hi2_launch_count(void);
-/* Launch-resource figures of the tensor-core second-moment kernel on the current device:
- * out[7] = registers, static smem, max dynamic smem, max threads per block, resident blocks per
- * SM at the launch configuration, requested dynamic smem, threads.  Diagnostics only. */
-int hi2_hessian_kernel_info(int64_t* out);
+/* Chains of short kernels (the inverse factor, the GPTQ column loop) that this library has sent
+ * to a stream as one CUDA graph launch each, in the process so far.  No counterpart in the
+ * reference. */
+long long hi2_graph_launch_count(void);
 
 /* ---- rotation ------------------------------------------------------------------------------
  * hi2/format.py:30-41 fwht_groups, fused with the cast and smoothing multiply of

@@ -83,3 +83,46 @@ def ladder_report(got, want):
         codes_same_rows=(gk[same] == want.codes[same]).float().mean().item() if bool(same.any()) else 1.0,
         same=same,
     )
+
+
+def config1_inputs(rows=4096, k=4096, tokens=2048, seed=2024):
+    """BASELINE config 1: a 4096 x 4096 fp16 Linear, N(0, 0.02), 0.1 % of the input columns x 20;
+    2048 tokens of fp16 activations, N(0, 1) times a per-channel lognormal(0, 1) scale."""
+    g = gen(seed)
+    w = torch.randn(rows, k, generator=g) * 0.02
+    cols = torch.randperm(k, generator=g)[: max(1, k // 1000)]
+    w[:, cols] *= 20
+    x = torch.randn(tokens, k, generator=g) * torch.exp(torch.randn(1, k, generator=g))
+    return w.half(), x.half()
+
+
+def oracle_layer(w, x, candidates, target, keep_codes=True):
+    """The reference's chain for one Linear on the CPU oracle: statistics, smoothing vector, table,
+    allocation, basis change, factor, GPTQ per candidate group, flat-buffer assembly."""
+    k = w.shape[1]
+    sm = po.SecondMoment(k)
+    sm.update(x)
+    gm = po.GroupMoments(k)
+    gm.update(x)
+    s16 = po.smoothing_vector(gm, 0.5)
+    had = torch.ones(k // 16, dtype=torch.uint8)
+    wt = po.rotate_groups(w.float() * s16.float(), had)
+    d_tab = gm.diag(had, 1.0 / s16.float())
+    sse = torch.stack([po.nearest_rows(wt, d_tab, nb, b).sse for nb, b in candidates])
+    table = po.Table("w", tuple(w.shape), had, sse, list(candidates), float((d_tab * wt**2).sum()),
+                     x.shape[0], s16)
+    alloc = po.allocate_rows([table], target)
+    hs = po.stored_basis_hessian(sm.mean(), s16, had)
+    u = po.inverse_cholesky(hs, 0.01)
+    d = hs.diagonal().clone()
+    pieces = []
+    picks = alloc.picks["w"]
+    for ci, (nb, b) in enumerate(candidates):
+        rows = (picks == ci).nonzero().flatten()
+        if rows.numel():
+            pieces.append((rows, po.gptq_rows(wt[rows], d, u, nb, b), nb, b))
+    cand = torch.tensor(candidates)
+    flat = po.assemble_flat([(r, e.codes, e.params, e.consts) for r, e, _, _ in pieces], cand[picks, 0],
+                            cand[picks, 1], had, k, s16)
+    return dict(sm=sm, gm=gm, s16=s16, had=had, wt=wt, d_tab=d_tab, table=table, alloc=alloc, hs=hs, u=u, d=d,
+                pieces=pieces, flat=flat)

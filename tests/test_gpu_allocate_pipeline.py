@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import ptq_oracle as po
-from tests.helpers import DEV, activations, agreement, gen, rel_close, weighted_error
+from tests.helpers import DEV, activations, agreement, gen, oracle_layer, rel_close, weighted_error
 
 pytestmark = pytest.mark.gpu
 
@@ -51,34 +51,6 @@ def test_allocation_large_random_tables():
         assert abs(got.bpw - target) < 1e-3
 
 
-def _oracle_layer(w, x, cfg_candidates, target):
-    """The reference's chain on the CPU oracle: statistics, table, allocation, GPTQ, assembly."""
-    k = w.shape[1]
-    sm = po.SecondMoment(k)
-    sm.update(x)
-    gm = po.GroupMoments(k)
-    gm.update(x)
-    s16 = po.smoothing_vector(gm, 0.5)
-    had = torch.ones(k // 16, dtype=torch.uint8)
-    wt = po.rotate_groups(w.float() * s16.float(), had)
-    d_tab = gm.diag(had, 1.0 / s16.float())
-    sse = torch.stack([po.nearest_rows(wt, d_tab, nb, b).sse for nb, b in cfg_candidates])
-    table = po.Table("w", tuple(w.shape), had, sse, list(cfg_candidates), float((d_tab * wt**2).sum()),
-                     x.shape[0], s16)
-    alloc = po.allocate_rows([table], target)
-    hs = po.stored_basis_hessian(sm.mean(), s16, had)
-    u = po.inverse_cholesky(hs, 0.01)
-    d = hs.diagonal().clone()
-    pieces = []
-    picks = alloc.picks["w"]
-    for ci, (nb, b) in enumerate(cfg_candidates):
-        rows = (picks == ci).nonzero().flatten()
-        if rows.numel():
-            e = po.gptq_rows(wt[rows], d, u, nb, b)
-            pieces.append((rows, e))
-    return dict(s16=s16, wt=wt, table=table, alloc=alloc, hs=hs, u=u, d=d, pieces=pieces)
-
-
 def test_layer_end_to_end_against_oracle():
     """A 256 x 512 bf16 layer with 4096 calibration tokens.  Stage by stage on the oracle's
     inputs the kernels meet the code / scale bars (other tests); end to end the comparison is the
@@ -94,7 +66,7 @@ def test_layer_end_to_end_against_oracle():
     w = (torch.randn(r, k, generator=g) * 0.02).bfloat16()
     w[:, 7] *= 20
     x = activations(4096, k, 5, spread=1.0, dtype=torch.bfloat16)
-    ref = _oracle_layer(w, x, ALL_CANDIDATES, 3.0)
+    ref = oracle_layer(w, x, ALL_CANDIDATES, 3.0)
 
     cfg = Config()
     h = HessianStats(k, DEV)
@@ -128,8 +100,7 @@ def test_layer_end_to_end_against_oracle():
         e = rec - wt[row]
         err += float(e @ hs @ e)
     err_ref = 0.0
-    for rows, e in ref["pieces"]:
-        b = k // e.params.shape[1]
+    for rows, e, _, b in ref["pieces"]:
         err_ref += weighted_error(ref["wt"][rows], ref["hs"], e.codes, e.params, e.consts, b)
     assert abs(err - err_ref) <= 0.01 * err_ref, (err, err_ref)
 

@@ -1,19 +1,16 @@
 """Ladder search, parameter bytes and nearest rows on the GPU against the oracle.
 
-The search sums d*(..)^2, d*c, d*c*w ... over a block in fp32; a CPU reduction and the kernel
-add in different orders, so (lo, step) differ in their last bits, and where such a value sits on
-a rounding boundary of the 8-bit parameter quantiser one byte of the row moves by one (measured:
-0.01-0.1 % of bytes, more for INT8 whose grid errors are near-ties by construction).  The same
-happens between two CPUs with different vector widths.  Bars: rows whose ladders came out
-identical must have identical codes; >= 99.5 % of parameter bytes equal; row constants (scales)
-within 1e-3 for >= 95 % of rows; codes >= 99.9 % for INT2/INT4 and >= 99 % for INT8; weighted
-error within 1e-3 in total."""
+The search's block sums are formed in the order of torch's CPU reduction (8-lane vectors, four
+interleaved accumulators, lanes left to right), every quotient is the IEEE one, and no product is
+fused, so on identical fp32 inputs the kernel returns the reference's ``(lo, step)`` BIT FOR BIT;
+parameter bytes, row constants and nearest codes follow.  Bars: ladders, bytes, constants and
+codes equal; the row error (a K-term fp32 sum added in another order) within 1e-5."""
 
 import pytest
 import torch
 
 from oracle import ptq_oracle as po
-from tests.helpers import CASES, DEV, agreement, gen, ladder_report, rel_close, weights
+from tests.helpers import CASES, DEV, gen, rel_close, weights
 
 pytestmark = pytest.mark.gpu
 
@@ -30,10 +27,9 @@ def test_grid_matches_reference_grid():
     grid = EFFORT["normal"]["grid"]
     lo, st, err = ladder_kernel.ladder_grid(wb.to(DEV), db.to(DEV), grid, 4)
     lo_t, st_t, err_t = po.grid_search(wb, db.reshape(1, 640, 16), 4, grid)
-    same = (lo.cpu() == lo_t)
-    assert same.float().mean().item() >= 0.9999
-    assert ((st.cpu() - st_t).abs()[same] < 1e-6).all()
-    assert rel_close(err.cpu()[same], err_t[same], 1e-5, 1e-7)
+    # the reference's own kernel test asks lo equal and step within 1e-6
+    # (tests/test_ladder_kernel.py:47-60); here all three outputs are equal
+    assert torch.equal(lo.cpu(), lo_t) and torch.equal(st.cpu(), st_t) and torch.equal(err.cpu(), err_t)
 
 
 @pytest.mark.parametrize("block", [16, 32, 64])
@@ -48,22 +44,16 @@ def test_fit_ladder(block, n, effort):
     db = torch.rand(1, 12, block, generator=g) + 0.1
     lo, st = fit_ladder(wb.to(DEV), db.to(DEV), n, effort)
     lo_t, st_t = po.search_ladder(wb, db, n, effort)
-    ok = ((lo.cpu() - lo_t).abs() <= 1e-5 * (1 + lo_t.abs())) & ((st.cpu() - st_t).abs() <= 1e-5 * (1 + st_t.abs()))
-    assert ok.float().mean().item() >= 0.995, ok.float().mean().item()
+    assert torch.equal(lo.cpu(), lo_t) and torch.equal(st.cpu(), st_t)
     assert st.cpu()[0, 0] == 0 and lo.cpu()[0, 0] == 0.25
 
 
 def test_fit_ladder_fixture(golden):
     from hi2_b200.encode import fit_ladder
 
-    hits = total = 0
-    for case in golden["ladder"]:
+    for case in golden["ladder"]:  # outputs of the reference itself
         lo, st = fit_ladder(case["wb"].to(DEV), case["db"].to(DEV), case["n"], case["effort"])
-        ok = ((lo.cpu() - case["lo"]).abs() <= 1e-5 * (1 + case["lo"].abs())) & (
-            (st.cpu() - case["step"]).abs() <= 1e-5 * (1 + case["step"].abs()))
-        hits += int(ok.sum())
-        total += ok.numel()
-    assert hits / total >= 0.995
+        assert torch.equal(lo.cpu(), case["lo"]) and torch.equal(st.cpu(), case["step"]), (case["n"], case["effort"])
 
 
 def test_quantize_params_is_exact(golden):
@@ -82,12 +72,9 @@ def test_quantize_params_is_exact(golden):
 
 
 def _check_rows(got, want, nbits):
-    rep = ladder_report(got, want)
-    assert rep["codes_same_rows"] >= 0.9999, rep
-    assert rep["params"] >= 0.995 and rep["consts_ok"] >= 0.95, rep
-    assert rep["codes"] >= (0.999 if nbits <= 4 else 0.99), rep
-    assert abs(float(got.sse.sum()) - float(want.sse.sum())) <= 1e-3 * float(want.sse.sum())
-    assert rel_close(got.sse.cpu()[rep["same"]], want.sse[rep["same"]], 1e-4, 1e-7)
+    assert torch.equal(got.params.cpu(), want.params) and torch.equal(got.consts.cpu(), want.consts)
+    assert torch.equal(got.codes.cpu(), want.codes)
+    assert rel_close(got.sse.cpu(), want.sse, 1e-5, 1e-9)
 
 
 @pytest.mark.parametrize("nbits,block", CASES)
@@ -105,12 +92,9 @@ def test_encode_rows_fixture(golden):
     from hi2_b200.encode import encode_rows
 
     near = golden["nearest"]
-    codes_ok = n = 0
-    for (nb, b, effort), want in near["cases"].items():
+    for (nb, b, effort), want in near["cases"].items():  # outputs of the reference itself
         got = encode_rows(near["w"].to(DEV), near["d"].to(DEV), nb, b, effort)
-        codes_ok += int((got.codes.cpu() == want["codes"]).sum())
-        n += want["codes"].numel()
-    assert codes_ok / n >= 0.995
+        assert torch.equal(got.codes.cpu(), want["codes"]), (nb, b, effort)
 
 
 def test_encode_rows_wide_and_strided():
