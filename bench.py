@@ -476,6 +476,91 @@ class ModelJob:
                    for layer in self.last["packed"].values() for t in layer.values() for f in FIELDS)
 
 
+class PropagatedJob:
+    """The whole-model workload with the calibration activations PRODUCED ON THE DEVICE: a
+    Llama-shaped model (random init) and calibration token ids start in pinned host memory; a step
+    copies the weights of the owned layers to the device (the owners then broadcast them over
+    NVLink, every rank runs every layer), embeds the ids, runs the decoder layers one at a time over
+    this rank's sequences with the statistics taken by forward pre-hooks
+    (hi2_b200.layerwise.calibrate_layerwise), allocates over all tables, encodes every Linear from
+    the statistics left in HBM, and copies the packed buffers back.  No activation crosses PCIe.
+    The layer forward itself (library GEMMs and attention) is the caller's model, not this
+    package's kernels; its time is inside the step."""
+
+    def __init__(self, cfg, rank, world, device, heads=32, vocab=32000):
+        from transformers import LlamaConfig, LlamaForCausalLM
+
+        self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
+        seq_len = 2048 if cfg["tokens"] % 2048 == 0 else cfg["tokens"]
+        self.sequences = cfg["tokens"] // seq_len
+        mc = LlamaConfig(hidden_size=cfg["hidden"], intermediate_size=cfg["ffn"], num_hidden_layers=cfg["layers"],
+                         num_attention_heads=heads, num_key_value_heads=heads, vocab_size=vocab,
+                         max_position_embeddings=seq_len)
+        dt = torch_dtype(cfg["dtype"])
+        old = torch.get_default_dtype()
+        torch.set_default_dtype(dt)
+        try:
+            torch.manual_seed(1234)  # the same model on every rank
+            with torch.device(device):
+                self.model = LlamaForCausalLM(mc).eval()
+        finally:
+            torch.set_default_dtype(old)
+        self.layers = self.model.model.layers
+        g = torch.Generator().manual_seed(99)
+        self.ids_host = torch.randint(0, vocab, (self.sequences, seq_len), generator=g).pin_memory()
+        self.owned = [l for l in range(cfg["layers"]) if l % world == rank]
+        self.host = {l: [p.detach().cpu().pin_memory() for p in self.layers[l].parameters()] for l in self.owned}
+        self.h2d = sum(t.numel() * t.element_size() for ts in self.host.values() for t in ts) + \
+            self.ids_host.numel() * self.ids_host.element_size()
+        self.rows = sum(p.shape[0] for l in range(cfg["layers"]) for n, p in self.layers[l].named_parameters()
+                        if p.dim() == 2)
+        from hi2_b200.calibrate import ALL_CANDIDATES, Config
+
+        self.qcfg = Config(candidates=list(ALL_CANDIDATES))
+        self.specs = None
+
+    def step(self):
+        import torch.distributed as dist
+
+        from hi2_b200 import dist as hd
+        from hi2_b200.allocate import allocate_global
+        from hi2_b200.calibrate import ALL_CANDIDATES, TensorTable
+        from hi2_b200.layerwise import DeviceSink, calibrate_layerwise, encode_layerwise
+
+        for l in self.owned:
+            for p, h in zip(self.layers[l].parameters(), self.host[l]):
+                p.data.copy_(h, non_blocking=True)
+        if self.world > 1:
+            for l in range(self.cfg["layers"]):
+                for p in self.layers[l].parameters():
+                    dist.broadcast(p.data, src=l % self.world)
+        ids = self.ids_host.to(self.device, non_blocking=True)
+        sink = DeviceSink()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        tables = calibrate_layerwise(self.model, ids, self.qcfg, exclude=["lm_head|embed"], sink=sink,
+                                     log=lambda *_: None, device=self.device)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t1.record()
+        if self.specs is None:
+            self.specs = [(l % self.world, f"model.layers.{l}.{n}.weight", tuple(m.weight.shape), list(ALL_CANDIDATES),
+                           self.cfg["tokens"], True)
+                          for l in range(self.cfg["layers"]) for n, m in self.layers[l].named_modules()
+                          if isinstance(m, torch.nn.Linear)]
+        local = [tables[name] for owner, name, *_ in self.specs if owner == self.rank]
+        everything = hd.gather_tables_known_layout(local, self.specs, TensorTable)
+        alloc = allocate_global(everything, self.cfg["bpw"])
+        packed = encode_layerwise(self.model, tables, alloc.picks, sink, self.qcfg, to_host=True)
+        self.last = dict(alloc=alloc, packed=packed, tabulate=(t0, t1))
+        return packed
+
+    def d2h_bytes(self):
+        from hi2_b200.format import FIELDS
+
+        return sum(getattr(t, f).numel() * getattr(t, f).element_size() for t in self.last["packed"].values()
+                   for f in FIELDS)
+
+
 def hessian_flops(widths, tokens):
     """(algorithmic 2 T K^2, issued by the upper-triangle 128 x 256 tiles) summed over the inputs."""
     algo = issued = 0.0
@@ -720,6 +805,39 @@ def run_ours(args, cfg):
         e2e = {"value": None, "unit": "rows/s", "h2d_bytes_per_step": need * world, "d2h_bytes_per_step": 0,
                "note": "host memory too small to pin the inputs"}
 
+    # ---- the same model with the activations produced on the device (calibration propagation) ----
+    propagated = None
+    if whole_model and not args.no_propagate:
+        keep = dict(stage_ms=job.stage_ms, hessian_ms=job.hessian_ms, hessian_launches=job.hessian_launches,
+                    gptq=job.gptq, widths=job.widths, rows_layer=job.rows_layer)
+        job.weights = job.inputs = job.host = job.stacks = job.last = None  # free HBM and pinned memory
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        pj = PropagatedJob(cfg, rank, world, device)
+        pj.step()
+        sync_all()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        tab_ms = 0.0
+        for _ in range(args.steps):
+            pj.step()
+            torch.cuda.synchronize(device)
+            tab_ms += pj.last["tabulate"][0].elapsed_time(pj.last["tabulate"][1])
+        p1.record()
+        sync_all()
+        pms = torch.tensor([p0.elapsed_time(p1) / args.steps], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(pms, op=dist.ReduceOp.MAX)
+        propagated = {"value": pj.rows / (float(pms.item()) / 1e3), "unit": "rows/s", "ms_per_step": float(pms.item()),
+                      "forward_and_tabulate_ms": tab_ms / args.steps, "achieved_bpw": pj.last["alloc"].bpw,
+                      "h2d_bytes_per_step": pj.h2d * world, "d2h_bytes_per_step": pj.d2h_bytes() * world,
+                      "note": "weights and token ids from pinned host memory, activations produced on the device by "
+                              "the layer forwards (library GEMMs and attention, inside the step), packed buffers back"}
+        job.stage_ms, job.hessian_ms, job.hessian_launches, job.gptq = (keep["stage_ms"], keep["hessian_ms"],
+                                                                        keep["hessian_launches"], keep["gptq"])
+
     if rank != 0:
         return
     pk = peaks()
@@ -776,6 +894,8 @@ def run_ours(args, cfg):
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
         "gpu_launches": launches, "clocks": clock_info,
     }
+    if propagated is not None:
+        line["propagated"] = propagated
     if whole_model and job.gptq:
         # rows through the GPTQ column loop (block kernel + trailing updates) per second of that loop,
         # per width; the widths run beside each other on two streams
@@ -948,6 +1068,8 @@ def main():
     ap.add_argument("--config", default="cfg3", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-propagate", action="store_true",
+                    help="skip the run with the activations produced on the device by layer forwards")
     ap.add_argument("--kernels", action="store_true", help="time every hot kernel alone against its bound")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]

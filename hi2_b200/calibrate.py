@@ -26,10 +26,14 @@ INT8_CANDIDATES = [(8, 32), (8, 64)]
 SELECTABLE = ALL_CANDIDATES + INT8_CANDIDATES
 
 
+ROTATION_ROWS = 1024  # rows sampled to decide the rotation per 64-column chunk
+CHUNK = 64
+
+
 @dataclass
 class Config:
     candidates: list = field(default_factory=lambda: list(ALL_CANDIDATES))
-    rotation: str = "on"  # on | off ("auto" is a search above this path and is not built here)
+    rotation: str = "on"  # on | off | auto (per 64-column chunk, decided on a row sample)
     smooth: float = 0.5
     smooth_search: tuple = ()
     rounding: str = "gptq"  # gptq | nearest
@@ -72,12 +76,101 @@ def smoothing_scale(stats: ColumnStats | None, alpha: float) -> torch.Tensor | N
     return s.to(torch.float16)
 
 
-def _flags(k: int, cfg: Config) -> torch.Tensor:
-    if cfg.rotation == "on":
-        return torch.ones(k // GROUP, dtype=torch.uint8)
+def _sample_rows(w: torch.Tensor) -> torch.Tensor:
+    """Every (R // 1024)-th row, at most 1024 of them (hi2/calibrate.py:125)."""
+    r = w.shape[0]
+    return w[torch.arange(0, r, max(1, r // ROTATION_ROWS), device=w.device)[:ROTATION_ROWS]]
+
+
+def _chunk_errors(wt, d, enc, block: int) -> torch.Tensor:
+    """Weighted error of an encode per 64-column chunk, summed over the rows
+    (hi2/calibrate.py:140-157): codes and parameter bytes come from the kernels, the fp16 decode
+    and the sums are elementwise tensor math on the device."""
+    from .format import decode_params, ladder_dequantize
+
+    r, k = wt.shape
+    lo, step = decode_params(enc.params[..., 0], enc.params[..., 1], enc.consts[:, 0:1], enc.consts[:, 1:2],
+                             enc.consts[:, 2:3])
+    rec = ladder_dequantize(enc.codes.reshape(r, k // block, block), lo.float(), step.float(), torch.float32).float()
+    return (d.reshape(1, k // block, block) * (rec - wt.reshape(r, k // block, block)) ** 2).sum((0, 2))
+
+
+def choose_rotation(w: torch.Tensor, stats: ColumnStats | None, cfg: Config, device=None,
+                    inv_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotation flags ``[K/16]`` uint8, uniform over rows (hi2/calibrate.py:114-137).  ``auto``
+    encodes a sample of the rows at INT2 / block 64 (effort fast) with and without the rotation
+    and keeps, per 64-column chunk, whichever leaves the smaller activation-weighted error."""
+    k = w.shape[1]
+    ng = k // GROUP
     if cfg.rotation == "off":
-        return torch.zeros(k // GROUP, dtype=torch.uint8)
-    raise NotImplementedError("rotation='auto' is chosen above this path; pass a transform")
+        return torch.zeros(ng, dtype=torch.uint8)
+    if cfg.rotation == "on":
+        return torch.ones(ng, dtype=torch.uint8)
+    if cfg.rotation != "auto":
+        raise ValueError(f"rotation must be on, off or auto (got {cfg.rotation!r})")
+    dev = _lib.need_cuda(w) if device is None else torch.device(device)
+    ws = _sample_rows(w).to(dev, torch.float32)
+    err = []
+    for rot in (0, 1):
+        fl = torch.full((ng,), rot, dtype=torch.uint8)
+        wt = fwht_groups(ws, fl) if rot else ws
+        d = _weights(stats, k, fl, dev, inv_scale)
+        err.append(_chunk_errors(wt, d, encode_rows(wt, d, 2, CHUNK, "fast"), CHUNK))
+    return (err[1] < err[0]).to(torch.uint8).repeat_interleave(CHUNK // GROUP).cpu()
+
+
+def _fixed_transform(ws: list, stats: ColumnStats | None, cfg: Config, alpha: float):
+    """``(smoothing vector for exponent alpha, flags)`` (hi2/calibrate.py:160-170); with ``auto``
+    the flags are chosen on the smoothed rows of all the Linears together."""
+    s16 = smoothing_scale(stats, alpha)
+    if cfg.rotation != "auto":
+        return s16, choose_rotation(ws[0], stats, cfg)
+    dev = _lib.need_cuda(*ws)
+    scale = None if s16 is None else s16.to(dev, torch.float32)
+    # the reference samples the rows of the Linears stacked on top of each other; the same rows are
+    # picked here without stacking the full matrices
+    total = sum(w.shape[0] for w in ws)
+    idx = torch.arange(0, total, max(1, total // ROTATION_ROWS))[:ROTATION_ROWS]
+    parts, off = [], 0
+    for w in ws:
+        mine = idx[(idx >= off) & (idx < off + w.shape[0])] - off
+        if mine.numel():
+            rows = w[mine.to(w.device)].float()
+            parts.append(rows if scale is None else rows * scale)
+        off += w.shape[0]
+    return s16, choose_rotation(torch.cat(parts), stats, cfg, dev, None if scale is None else 1.0 / scale)
+
+
+def transform_error(ws: list, stats: ColumnStats, s16, had: torch.Tensor) -> float:
+    """Weighted INT2 / block-32 error (effort fast) of a row sample of ``ws`` under one transform,
+    relative to their weighted energy (hi2/calibrate.py:173-191)."""
+    dev = _lib.need_cuda(*ws)
+    inv = None if s16 is None else 1.0 / s16.to(dev, torch.float32)
+    sse = energy = None
+    for w in ws:
+        wt = stored_rows(_sample_rows(w), s16, had)
+        d = _weights(stats, w.shape[1], had, dev, inv)
+        enc = encode_rows(wt, d, 2, 32, "fast", want_codes=False, want_energy=True)
+        sse = enc.sse.sum() if sse is None else sse + enc.sse.sum()
+        energy = enc.energy.sum() if energy is None else energy + enc.energy.sum()
+    return float(sse) / max(float(energy), 1e-30)
+
+
+def shared_transform(ws: list, stats: ColumnStats | None, cfg: Config, ex=None):
+    """``(smoothing vector, rotation flags)`` for Linears that read the same input (q/k/v,
+    gate/up): one vector from the shared statistics, one set of flags chosen on their rows
+    together; with ``cfg.smooth_search`` the exponent with the lowest :func:`transform_error`
+    wins, the first one on a tie (hi2/calibrate.py:194-209)."""
+    del ex
+    if not cfg.smooth_search or stats is None or stats.n == 0:
+        return _fixed_transform(ws, stats, cfg, cfg.smooth)
+    best = None
+    for alpha in dict.fromkeys((cfg.smooth, *cfg.smooth_search)):
+        s16, had = _fixed_transform(ws, stats, cfg, alpha)
+        err = transform_error(ws, stats, s16, had)
+        if best is None or err < best[0]:
+            best = (err, s16, had)
+    return best[1], best[2]
 
 
 def stored_rows(w: torch.Tensor, s16: torch.Tensor | None, had: torch.Tensor) -> torch.Tensor:
@@ -94,8 +187,17 @@ def build_table(name: str, w: torch.Tensor, stats: ColumnStats | None, cfg: Conf
     del ex
     dev = _lib.need_cuda(w)
     r, k = w.shape
+    if transform is None and cfg.smooth_search:
+        transform = shared_transform([w], stats, cfg)
     if transform is None:
-        s16, had = smoothing_scale(stats, cfg.smooth), _flags(k, cfg)
+        s16 = smoothing_scale(stats, cfg.smooth)
+        if cfg.rotation in ("on", "off"):
+            had = choose_rotation(w, stats, cfg)
+        else:  # the flags are chosen on the smoothed rows
+            scale = None if s16 is None else s16.to(dev, torch.float32)
+            rows = _sample_rows(w).float()
+            had = choose_rotation(rows if scale is None else rows * scale, stats, cfg, dev,
+                                  None if scale is None else 1.0 / scale)
     else:
         s16, had = transform
         s16 = None if s16 is None else s16.clone()

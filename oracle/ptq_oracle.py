@@ -28,6 +28,7 @@ Reference locations (paths inside the hi2 project):
   hi2/refine.py:44-106   +-1 refinement      -> refine_sweeps
   hi2/format.py:73-184   packing / layout    -> pack_words, unpack_words, assemble_flat
   hi2/allocate.py:79-261 allocation          -> allocate_rows
+  hi2/calibrate.py:114-209 transform choice  -> pick_rotation, transform_cost, pick_transform
 """
 
 from __future__ import annotations
@@ -444,6 +445,81 @@ def refine_groups(groups, hs, passes: int):
     joined = [torch.cat([p[i] for p in cat]) for i in range(5)]
     out = refine_sweeps(*joined, hs, passes)
     return [o.to(torch.uint8) for o in out.split([p[0].shape[0] for p in cat])]
+
+
+# --------------------------------------------------------------------------- transform choice
+SAMPLE_ROWS = 1024  # hi2/calibrate.py:32
+CHUNK_COLS = 64  # hi2/calibrate.py:33
+
+
+def _every_nth(w):
+    r = w.shape[0]
+    return w[torch.arange(0, r, max(1, r // SAMPLE_ROWS))[:SAMPLE_ROWS]]
+
+
+def _column_weights(moments, k, flags, inv_scale=None):
+    return torch.ones(k) if moments is None else moments.diag(flags, inv_scale)
+
+
+def pick_rotation(w, moments, mode: str, inv_scale=None) -> torch.Tensor:
+    """Flags ``[K/16]``: all, none, or (``auto``) per 64-column chunk whichever of rotated /
+    unrotated leaves the smaller weighted INT2/B64 error on a row sample."""
+    k = w.shape[1]
+    groups = k // GROUP
+    if mode == "off":
+        return torch.zeros(groups, dtype=torch.uint8)
+    if mode == "on":
+        return torch.ones(groups, dtype=torch.uint8)
+    sample = _every_nth(w).float()
+    cost = []
+    for rotated in (0, 1):
+        flags = torch.full((groups,), rotated, dtype=torch.uint8)
+        wt = rotate_groups(sample, flags) if rotated else sample
+        d = _column_weights(moments, k, flags, inv_scale)
+        enc = nearest_rows(wt, d, 2, CHUNK_COLS, "fast")
+        lo, step = _decoded(enc.params[..., 0], enc.params[..., 1], enc.consts)
+        rec = reconstruct(enc.codes.reshape(-1, k // CHUNK_COLS, CHUNK_COLS), lo, step, F32).float()
+        wb = wt.reshape(-1, k // CHUNK_COLS, CHUNK_COLS)
+        cost.append((d.reshape(1, -1, CHUNK_COLS) * (rec - wb) ** 2).sum((0, 2)))
+    return (cost[1] < cost[0]).to(torch.uint8).repeat_interleave(CHUNK_COLS // GROUP)
+
+
+def _transform_for(ws, moments, mode: str, alpha: float):
+    s16 = smoothing_vector(moments, alpha)
+    if mode != "auto":
+        return s16, pick_rotation(ws[0], moments, mode)
+    stacked = torch.cat([w.float() if s16 is None else w.float() * s16.float() for w in ws])
+    return s16, pick_rotation(stacked, moments, mode, None if s16 is None else 1.0 / s16.float())
+
+
+def transform_cost(ws, moments, s16, flags) -> float:
+    """Weighted INT2/B32 error of a row sample under one transform over its weighted energy."""
+    inv = None if s16 is None else 1.0 / s16.float()
+    sse = energy = 0.0
+    for w in ws:
+        wt = _every_nth(w).float()
+        if s16 is not None:
+            wt = wt * s16.float()
+        if bool(flags.any()):
+            wt = rotate_groups(wt, flags)
+        d = _column_weights(moments, w.shape[1], flags, inv)
+        sse += float(nearest_rows(wt, d, 2, 32, "fast").sse.sum())
+        energy += float((d * wt**2).sum())
+    return sse / max(energy, 1e-30)
+
+
+def pick_transform(ws, moments, mode: str, alpha: float, search=()):
+    """``(smoothing vector, flags)`` shared by the Linears ``ws`` of one input; with ``search`` the
+    exponent of lowest :func:`transform_cost`, the first on a tie."""
+    if not search or moments is None or moments.n == 0:
+        return _transform_for(ws, moments, mode, alpha)
+    best = None
+    for a in dict.fromkeys((alpha, *search)):
+        s16, flags = _transform_for(ws, moments, mode, a)
+        cost = transform_cost(ws, moments, s16, flags)
+        if best is None or cost < best[0]:
+            best = (cost, s16, flags)
+    return best[1], best[2]
 
 
 # --------------------------------------------------------------------------- packing

@@ -126,3 +126,28 @@ def oracle_layer(w, x, candidates, target, keep_codes=True):
                             cand[picks, 1], had, k, s16)
     return dict(sm=sm, gm=gm, s16=s16, had=had, wt=wt, d_tab=d_tab, table=table, alloc=alloc, hs=hs, u=u, d=d,
                 pieces=pieces, flat=flat)
+
+
+def transform_case(seed, k, rows):
+    """Linears that read one input (list of [R_i, K] fp32) and its activations: columns with very
+    different scales, a few heavy-tailed groups, so that rotation helps some chunks and not others."""
+    g = gen(1000 + seed)
+    ws = []
+    for r in rows:
+        w = torch.randn(r, k, generator=g) * 0.05
+        w[:, : k // 4] *= torch.exp(1.5 * torch.randn(1, k // 4, generator=g))  # spiky first quarter
+        ws.append(w)
+    x = torch.randn(2048, k, generator=g) * torch.exp(torch.randn(1, k, generator=g))
+    return ws, x.half()
+
+
+def toy_llama(layers=2, hidden=64, ffn=128, heads=2, vocab=256, sequences=6, tokens=48, seed=0):
+    """A Llama-shaped fp32 toy model with seeded weights and seeded calibration ids."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    cfg = LlamaConfig(hidden_size=hidden, intermediate_size=ffn, num_hidden_layers=layers, num_attention_heads=heads,
+                      num_key_value_heads=heads, vocab_size=vocab, max_position_embeddings=4 * tokens)
+    torch.manual_seed(seed)
+    model = LlamaForCausalLM(cfg).eval()
+    ids = torch.randint(0, vocab, (sequences, tokens), generator=gen(seed + 1))
+    return model, ids

@@ -105,3 +105,20 @@ def test_whole_model_job_equals_layer_by_layer():
         want = L.encode(job.weights[l], job.plan, shared, tables, picks, job.qcfg, to_host=False)
         for name in job.shapes:
             assert _same(packed[l][name], want[name]), (l, name)
+
+
+def test_propagated_job_runs_the_whole_model():
+    """bench.PropagatedJob on the toy model: weights and ids from pinned host memory, activations
+    produced by the layer forwards on the device, every Linear tabulated, allocated and encoded."""
+    import bench
+
+    cfg = dict(bench.CONFIGS["tiny_model"])
+    dev = torch.device(DEV, torch.cuda.current_device())
+    job = bench.PropagatedJob(cfg, 0, 1, dev, heads=8, vocab=512)
+    packed = job.step()
+    torch.cuda.synchronize()
+    assert len(packed) == cfg["layers"] * 7 and job.rows == cfg["layers"] * (4 * 512 + 2 * 1024 + 512)
+    assert job.last["alloc"].feasible and abs(job.last["alloc"].bpw - cfg["bpw"]) < 0.02
+    t = packed["model.layers.3.mlp.down_proj.weight"]
+    assert t.shape == (512, 1024) and t.codes.device.type == "cpu" and int(t.code_off[-1]) == t.codes.numel()
+    assert job.d2h_bytes() > 0 and job.h2d > 0

@@ -8,6 +8,7 @@ import torch
 
 from oracle import ptq_oracle as po
 
+ROOT = __import__("pathlib").Path(__file__).resolve().parents[1]
 TIGHT = dict(rtol=2e-6, atol=1e-7)
 
 
@@ -204,3 +205,22 @@ def test_allocation_is_bit_exact(golden):
         assert got.lam == want["lam"] and got.bpw == want["bpw"]
         for name, p in want["picks"].items():
             assert torch.equal(got.picks[name], p)
+
+
+def test_transform_choice_matches_reference():
+    """Shared transform (rotation flags per 64-column chunk, smoothing exponent search) against what
+    hi2 itself chose (tests/golden/transform_golden.pt, hi2/calibrate.py:114-209)."""
+    from tests.helpers import transform_case
+
+    cases = torch.load(ROOT / "tests" / "golden" / "transform_golden.pt", weights_only=False)
+    assert {c["mode"] for c in cases} == {"auto", "on", "off"}
+    for c in cases:
+        ws, x = transform_case(c["seed"], c["k"], c["rows"])
+        gm = po.GroupMoments(c["k"])
+        gm.update(x)
+        s16, had = po.pick_transform(ws, gm, c["mode"], c["alpha"], c["search"])
+        assert (s16 is None and c["s16"] is None) or torch.equal(s16, c["s16"])
+        assert torch.equal(had, c["had"])
+        for alpha, want in c["costs"].items():
+            s_a, had_a = po._transform_for(ws, gm, c["mode"], alpha)
+            assert abs(po.transform_cost(ws, gm, s_a, had_a) - want) <= 1e-6 * want
