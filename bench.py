@@ -584,11 +584,28 @@ def peaks():
 # --------------------------------------------------------------------------------------------
 # the CPU arm: the oracle (a restatement of the reference's CPU path) on the host cores
 # --------------------------------------------------------------------------------------------
-def cpu_sample(cfg, rows_s: int, tokens_s: int, threads: int) -> dict:
-    """Time every stage of the path on a bounded sample of the workload and scale each stage to
-    the full workload by the units it processes (tokens for the second moments, rows for tables,
-    GPTQ and packing; the basis change and the factorisation run at full size).  Returns the
-    extrapolated seconds per stage and their sum."""
+_FACTOR_SECONDS: dict = {}  # width -> measured seconds of one full-size CPU factorisation (timed once per process)
+
+
+def cpu_sample(cfg, threads: int, budget_s: float = 30.0) -> dict:
+    """The oracle (a restatement of the reference's CPU path) on a BOUNDED sample of one layer of the
+    workload, every stage scaled to the whole workload by the units it processes:
+
+    * second moments and group moments: 4096 tokens per input (the reference's own chunk size, the
+      product is in its efficient regime), scaled by tokens;
+    * basis change and factorisation: FULL size per distinct input (the widest is timed once per
+      process and its time reused, the others every call);
+    * tables: a row sample of every matrix, all six candidates, scaled by rows (the search is
+      elementwise over rows);
+    * allocation: on the sampled tables (its cost is negligible either way);
+    * GPTQ: ladders on a row sample (scaled by rows); the column loop on row groups of FULL size
+      (the allocation's shares of the matrix: a column step costs the same for 32 rows as for
+      2000, so a row sample would not do) over the first and the last 128-column block, whose mean
+      is the mean cost of a block (the trailing update shrinks linearly), scaled by blocks;
+    * packing: the sampled rows, scaled by rows.
+
+    The row sample is sized so that the call takes about ``budget_s`` seconds.  Returns the
+    extrapolated seconds per stage for ONE layer and their sum times the number of layers."""
     from oracle import ptq_oracle as po
 
     torch.set_num_threads(threads)
@@ -596,8 +613,11 @@ def cpu_sample(cfg, rows_s: int, tokens_s: int, threads: int) -> dict:
     cands = [(nb, b) for nb in (2, 4) for b in (16, 32, 64)]
     dt = torch_dtype(cfg["dtype"])
     g = torch.Generator().manual_seed(0)
-    t = {k: 0.0 for k in ("hessian", "statistics", "tables", "allocate", "factor", "gptq", "pack")}
-    tok_scale = cfg["tokens"] / tokens_s
+    t = {k: 0.0 for k in ("hessian", "statistics", "tables", "allocate", "factor", "gptq_ladders", "gptq_columns", "pack")}
+    tokens_s = min(4096, cfg["tokens"])
+    # tables cost ~1.7 us per weight and candidate on 8 cores: keep them within about half of the budget
+    weights_per_row = sum(k for _, k in shapes.values())
+    rows_s = int(max(32, min(1024, 0.5 * budget_s / (1.0e-6 * 6 * weights_per_row) * threads / 8)))
     shared = {}
     for name, k in widths.items():
         x = (torch.randn(tokens_s, k, generator=g) * torch.exp(cfg["spread"] * torch.randn(1, k, generator=g))).to(dt)
@@ -605,54 +625,136 @@ def cpu_sample(cfg, rows_s: int, tokens_s: int, threads: int) -> dict:
         sm, gm = po.SecondMoment(k), po.GroupMoments(k)
         sm.update(x)
         gm.update(x)
-        t["hessian"] += (time.perf_counter() - t0) * tok_scale
+        t["hessian"] += (time.perf_counter() - t0) * (cfg["tokens"] / tokens_s)
         t0 = time.perf_counter()
         s16 = po.smoothing_vector(gm, 0.5)
         had = torch.ones(k // 16, dtype=torch.uint8)
         d_tab = gm.diag(had, 1.0 / s16.float())
         t["statistics"] += time.perf_counter() - t0
-        t0 = time.perf_counter()
         hs = po.stored_basis_hessian(sm.mean(), s16, had)
-        u = po.inverse_cholesky(hs, 0.01)
-        t["factor"] += time.perf_counter() - t0
-        shared[name] = dict(s16=s16, had=had, d_tab=d_tab, hs=hs, u=u, d=hs.diagonal().clone())
+        widest = k == max(widths.values()) and k > 4096
+        if widest and k in _FACTOR_SECONDS:
+            u = _FACTOR_SECONDS[k][1]
+            t["factor"] += _FACTOR_SECONDS[k][0]
+        else:
+            t0 = time.perf_counter()
+            hs = po.stored_basis_hessian(sm.mean(), s16, had)
+            u = po.inverse_cholesky(hs, 0.01)
+            dtf = time.perf_counter() - t0
+            t["factor"] += dtf
+            if widest:
+                _FACTOR_SECONDS[k] = (dtf, u)
+        shared[name] = dict(s16=s16, had=had, d_tab=d_tab, u=u, d=hs.diagonal().clone())
     tables, stored = [], {}
     for name, (r, k) in shapes.items():
-        s = shared[plan.reads[name]]
+        s_in = shared[plan.reads[name]]
         rs = min(rows_s, r)
         w = (torch.randn(rs, k, generator=g) * 0.02).to(dt)
         t0 = time.perf_counter()
-        wt = po.rotate_groups(w.float() * s["s16"].float(), s["had"])
-        sse = torch.stack([po.nearest_rows(wt, s["d_tab"], nb, b).sse for nb, b in cands])
-        energy = float((s["d_tab"] * wt**2).sum())
+        wt = po.rotate_groups(w.float() * s_in["s16"].float(), s_in["had"])
+        sse = torch.stack([po.nearest_rows(wt, s_in["d_tab"], nb, b).sse for nb, b in cands])
+        energy = float((s_in["d_tab"] * wt**2).sum())
         t["tables"] += (time.perf_counter() - t0) * (r / rs)
-        tables.append(po.Table(name, (rs, k), s["had"], sse, list(cands), energy, cfg["tokens"], s["s16"]))
+        tables.append(po.Table(name, (rs, k), s_in["had"], sse, list(cands), energy, cfg["tokens"], s_in["s16"]))
         stored[name] = (wt, r / rs)
     t0 = time.perf_counter()
     alloc = po.allocate_rows(tables, cfg["bpw"])
     t["allocate"] += time.perf_counter() - t0
+    groups = []
     for table in tables:
-        s = shared[plan.reads[table.name]]
+        s_in = shared[plan.reads[table.name]]
         wt, scale = stored[table.name]
+        r, k = shapes[table.name]
         picks = alloc.picks[table.name]
+        blocks = -(-k // 128)
+        ends = {0, blocks - 1}
         pieces = []
-        t0 = time.perf_counter()
         for ci, (nb, b) in enumerate(cands):
             rows = (picks == ci).nonzero().flatten()
-            if rows.numel():
-                e = po.gptq_rows(wt[rows], s["d"], s["u"], nb, b)
-                pieces.append((rows, e.codes, e.params, e.consts))
-        t["gptq"] += (time.perf_counter() - t0) * scale
+            if rows.numel() == 0:
+                continue
+            # ladders of the sampled rows of this group (row-linear)
+            t0 = time.perf_counter()
+            lo, st = po.search_ladder(wt[rows].reshape(rows.numel(), k // b, b), s_in["d"].reshape(1, k // b, b), 2**nb)
+            lad = po.quantise_ladders(lo, st)
+            t["gptq_ladders"] += (time.perf_counter() - t0) * scale
+            # the column loop at the group's FULL size, first and last block
+            n_full = max(1, round(rows.numel() * scale))
+            reps = -(-n_full // rows.numel())
+            big = wt[rows].repeat(reps, 1)[:n_full]
+            lad_big = tuple(x.repeat(reps, *([1] * (x.dim() - 1)))[:n_full] for x in lad)
+            t0 = time.perf_counter()
+            e = po.gptq_rows(big, s_in["d"], s_in["u"], nb, b, ladders=lad_big, only_blocks=ends)
+            t["gptq_columns"] += (time.perf_counter() - t0) * (blocks / len(ends))
+            groups.append((table.name, nb, b, n_full))
+            pieces.append((rows, e.codes[: rows.numel()], e.params[: rows.numel()], e.consts[: rows.numel()]))
         t0 = time.perf_counter()
         nbits = torch.tensor([cands[i][0] for i in picks.tolist()])
         block = torch.tensor([cands[i][1] for i in picks.tolist()])
-        po.assemble_flat(pieces, nbits, block, s["had"], wt.shape[1], s["s16"])
+        po.assemble_flat(pieces, nbits, block, s_in["had"], k, s_in["s16"])
         t["pack"] += (time.perf_counter() - t0) * scale
-    total = sum(t.values())
-    return dict(seconds=total, stages={k: round(v, 3) for k, v in t.items()},
-                rows=sum(r for r, _ in shapes.values()),
-                sample=f"{rows_s} rows of each matrix and {tokens_s} of {cfg['tokens']} tokens per input, "
-                       f"each stage scaled by its units; basis change and factorisation at full size")
+    layers = cfg.get("layers", 1)
+    per_layer = sum(t.values())
+    return dict(seconds=per_layer * layers, seconds_per_layer=per_layer, layers=layers,
+                stages={k: round(v, 3) for k, v in t.items()}, rows=sum(r for r, _ in shapes.values()) * layers,
+                sample=f"one layer of {layers}: {tokens_s} of {cfg['tokens']} tokens per input; {rows_s} rows of each matrix "
+                       f"for tables, ladders and packing; the GPTQ column loop on {len(groups)} row groups of full size "
+                       f"(first and last 128-column block of each); basis change and factorisation at full size; every "
+                       f"stage scaled by its units, the layer by {layers} (extrapolated)")
+
+
+def cpu_config1_full(threads: int) -> dict:
+    """BASELINE config 1 IN FULL on the host (the case the reference itself runs on a CPU): the
+    oracle's whole chain for the 4096 x 4096 Linear with 2048 calibration tokens at 3.0 bpw, timed
+    stage by stage, nothing sampled, nothing scaled."""
+    from oracle import ptq_oracle as po
+
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(2024)
+    k = r = 4096
+    w = torch.randn(r, k, generator=g) * 0.02
+    w[:, torch.randperm(k, generator=g)[:4]] *= 20
+    w = w.half()
+    x = (torch.randn(2048, k, generator=g) * torch.exp(torch.randn(1, k, generator=g))).half()
+    cands = [(nb, b) for nb in (2, 4) for b in (16, 32, 64)]
+    st = {}
+    t0 = time.perf_counter()
+    sm, gm = po.SecondMoment(k), po.GroupMoments(k)
+    sm.update(x)
+    gm.update(x)
+    st["hessian"] = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    s16 = po.smoothing_vector(gm, 0.5)
+    had = torch.ones(k // 16, dtype=torch.uint8)
+    wt = po.rotate_groups(w.float() * s16.float(), had)
+    d_tab = gm.diag(had, 1.0 / s16.float())
+    sse = torch.stack([po.nearest_rows(wt, d_tab, nb, b).sse for nb, b in cands])
+    table = po.Table("w", (r, k), had, sse, list(cands), float((d_tab * wt**2).sum()), 2048, s16)
+    st["tables"] = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    alloc = po.allocate_rows([table], 3.0)
+    st["allocate"] = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    hs = po.stored_basis_hessian(sm.mean(), s16, had)
+    u = po.inverse_cholesky(hs, 0.01)
+    st["factor"] = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    d = hs.diagonal().clone()
+    picks = alloc.picks["w"]
+    pieces = []
+    for ci, (nb, b) in enumerate(cands):
+        rows = (picks == ci).nonzero().flatten()
+        if rows.numel():
+            e = po.gptq_rows(wt[rows], d, u, nb, b)
+            pieces.append((rows, e.codes, e.params, e.consts))
+    st["gptq"] = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    cand = torch.tensor(cands)
+    po.assemble_flat(pieces, cand[picks, 0], cand[picks, 1], had, k, s16)
+    st["pack"] = time.perf_counter() - t0
+    total = sum(st.values())
+    return {"workload": CONFIGS["cfg1"]["workload"], "seconds": total, "rows_per_s": r / total,
+            "stages_s": {k: round(v, 3) for k, v in st.items()}, "bpw": alloc.bpw, "sampled": False}
 
 
 def host_threads() -> int:
@@ -663,27 +765,37 @@ def host_threads() -> int:
 
 
 def run_reference(args, cfg):
+    """The CPU arm: the oracle on all host threads, one bounded sample of the workload per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = host_threads()
-    rows_s, tokens_s = (32, 1024) if cfg["ffn"] else (256, cfg["tokens"])
+    n = args.warmup + args.steps
+    budget = max(8.0, min(30.0, 150.0 / max(1, n)))  # the whole run stays within a few minutes
     times = []
-    for i in range(args.warmup + args.steps):
-        res = cpu_sample(cfg, rows_s, tokens_s, threads)
+    walls = []
+    for i in range(n):
+        t0 = time.perf_counter()
+        res = cpu_sample(cfg, threads, budget)
         if i >= args.warmup:
             times.append(res)
+            walls.append(time.perf_counter() - t0)
     secs = sum(r["seconds"] for r in times) / len(times)
     value = res["rows"] / secs
+    whole_model = "layers" in cfg
     line = {
         "impl": "reference", "metric": "ptq_encode_rows_per_s", "value": value, "unit": "rows/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg["workload"], "note": "CPU restatement of the reference on the host cores; "
-                   "ms_per_step is the full-workload time extrapolated from the sample"},
+        "higher_is_better": True, "scaling": "strong" if whole_model else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": cfg["workload"], "layers": cfg.get("layers", 1), "tokens_per_input": cfg["tokens"],
+                   "target_bpw": cfg["bpw"], "candidates": "int2,int4 x b16,b32,b64",
+                   "note": "CPU restatement of the reference (oracle/) on the host cores; value and ms_per_step are the "
+                           "full-workload figures EXTRAPOLATED from a bounded sample per step (see cpu_baseline.sample)"},
         "encode_wall_s": secs,
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
-                         "sample": res["sample"], "stages_s": res["stages"]},
+                         "sample": res["sample"], "stages_s_per_layer": res["stages"],
+                         "sample_wall_s_per_step": round(sum(walls) / len(walls), 1)},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -870,11 +982,14 @@ def run_ours(args, cfg):
     }
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        rows_s, tokens_s = (32, 1024) if cfg["ffn"] else (256, cfg["tokens"])
         threads = host_threads()
-        res = cpu_sample(cfg, rows_s, tokens_s, threads)
+        t0 = time.perf_counter()
+        res = cpu_sample(cfg, threads, 25.0)
+        wall = time.perf_counter() - t0
         cpu = {"value": res["rows"] / res["seconds"], "unit": "rows/s", "cores": threads, "kind": "port",
-               "sample": res["sample"], "seconds_full_workload": res["seconds"], "stages_s": res["stages"]}
+               "sample": res["sample"], "sample_wall_s": round(wall, 1), "seconds_full_workload": res["seconds"],
+               "stages_s_per_layer": res["stages"],
+               "config1_in_full": None if args.no_config1 else cpu_config1_full(threads)}
     config = {"workload": cfg["workload"], "layers": cfg.get("layers", world), "rows_per_layer": job.rows_layer if whole_model else job.rows,
               "tokens_per_input": cfg["tokens"], "target_bpw": cfg["bpw"], "achieved_bpw": alloc.bpw,
               "candidates": "int2,int4 x b16,b32,b64",
@@ -1068,6 +1183,7 @@ def main():
     ap.add_argument("--config", default="cfg3", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-config1", action="store_true", help="skip the full CPU run of config 1 in the cpu_baseline leg")
     ap.add_argument("--no-propagate", action="store_true",
                     help="skip the run with the activations produced on the device by layer forwards")
     ap.add_argument("--kernels", action="store_true", help="time every hot kernel alone against its bound")

@@ -336,11 +336,16 @@ def nearest_rows(w, d, nbits: int, block: int, effort: str = "normal") -> Rows:
 
 
 # --------------------------------------------------------------------------- GPTQ
-def gptq_rows(w, d, u, nbits: int, block: int, effort: str = "normal", perm=None) -> Rows:
+def gptq_rows(w, d, u, nbits: int, block: int, effort: str = "normal", perm=None, ladders=None,
+              only_blocks=None) -> Rows:
     """Error-compensated rounding with ladders frozen beforehand.
 
     Columns are visited in ``perm`` order when given (``u`` then belongs to the permuted Hessian);
-    codes and ``comp`` are reported at the original column positions."""
+    codes and ``comp`` are reported at the original column positions.
+
+    Two aids for the benchmark's bounded CPU sample (results are then NOT an encode): ``ladders``
+    ``(lo_u8, step_u8, consts)`` skips the search, ``only_blocks`` (a set of 128-column block
+    indices) visits only those blocks of the column loop."""
     n_rows, k = w.shape
     n = 2**nbits
     db = d.to(F32).reshape(1, k // block, block)
@@ -350,14 +355,19 @@ def gptq_rows(w, d, u, nbits: int, block: int, effort: str = "normal", perm=None
     for r0 in range(0, n_rows, per):
         src = w[r0 : r0 + per].float()
         work = src.clone()
-        lo, step = search_ladder(work.reshape(-1, k // block, block), db, n, effort)
-        lo_u8, step_u8, consts = quantise_ladders(lo, step)
+        if ladders is None:
+            lo, step = search_ladder(work.reshape(-1, k // block, block), db, n, effort)
+            lo_u8, step_u8, consts = quantise_ladders(lo, step)
+        else:
+            lo_u8, step_u8, consts = (t[r0 : r0 + per] for t in ladders)
         lo_d, step_d = _decoded(lo_u8, step_u8, consts)
         if perm is not None:
             work = work[:, perm]
         codes = torch.zeros_like(work)
         comp = torch.zeros_like(work)
         for c0 in range(0, k, LAZY):
+            if only_blocks is not None and c0 // LAZY not in only_blocks:
+                continue
             c1 = min(c0 + LAZY, k)
             seg = work[:, c0:c1].clone()
             errs = torch.zeros_like(seg)
