@@ -41,6 +41,22 @@ CONFIGS = {
     # config-2 shapes, 256 x 2048 calibration tokens per input, 3.0 bpw, layer l owned by rank l mod N
     "cfg3": dict(hidden=4096, ffn=11008, tokens=256 * 2048, spread=1.5, bpw=3.0, dtype="bf16", layers=32,
                  workload="llama2_7b_shape_32_layers_x_7_matrices_256x2048_tokens_3.0bpw"),
+    # BASELINE config 4: Llama-3-70B shapes (GQA: k/v 1024 x 8192), 80 layers, 128 x 4096 tokens, INT8
+    # candidates open to the 1 % most sensitive rows; 2.25 bpw is below the format's floor for these
+    # shapes (INT2/B64 costs 2.25 bits before the per-row overhead), so the step records that
+    # allocation as infeasible and encodes at 2.35 bpw.  80 layers hold 660 GB of second moments
+    # and factors: they fit on 8 GPUs, one GPU takes --layers 8.
+    "cfg4": dict(hidden=8192, ffn=28672, kv_rows=1024, tokens=128 * 4096, spread=1.5, bpw=2.35, bpw_infeasible=2.25,
+                 int8_fraction=0.01, dtype="bf16", layers=80, layers_per_encode=2,
+                 workload="llama3_70b_shape_80_layers_gqa_128x4096_tokens_2.35bpw_int8_top1pct"),
+    # BASELINE config 5: OLMoE shapes, 16 layers of 64 experts (gate/up 1024 x 2048, down 2048 x 1024),
+    # top-8 routing from a seeded random router with a per-expert bias (uneven token counts), per-expert
+    # second moments over the routed tokens only, gate and up of an expert share theirs; expert e of
+    # every layer is owned by rank e mod N
+    "cfg5": dict(hidden=2048, expert_ffn=1024, experts=64, top_k=8, tokens=256 * 2048, spread=1.5, bpw=2.5, dtype="bf16",
+                 moe_layers=16, router_bias=1.5, workload="olmoe_shape_16_layers_x_64_experts_top8_256x2048_tokens_2.5bpw"),
+    "tiny_moe": dict(hidden=256, expert_ffn=128, experts=8, top_k=2, tokens=4096, spread=1.0, bpw=3.0, dtype="bf16",
+                     moe_layers=2, router_bias=2.5, workload="tiny_moe_2_layers_x_8_experts_top2"),
     "cfg2": dict(hidden=4096, ffn=11008, tokens=128 * 2048, spread=1.5, bpw=2.5, dtype="bf16",
                  workload="llama_decoder_layer_7_matrices_4096x11008_128x2048_tokens_2.5bpw"),
     "cfg1": dict(hidden=4096, ffn=0, tokens=2048, spread=1.0, bpw=3.0, dtype="f16",
@@ -53,6 +69,9 @@ CONFIGS = {
                  workload="tiny_decoder_layer_512x1024_4096_tokens_2.5bpw"),
     "tiny_model": dict(hidden=512, ffn=1024, tokens=4096, spread=1.5, bpw=3.0, dtype="bf16", layers=4,
                        layers_per_encode=2, workload="tiny_model_4_layers_512x1024_4096_tokens_3.0bpw"),
+    "tiny_gqa_int8": dict(hidden=512, ffn=1024, kv_rows=128, tokens=4096, spread=1.5, bpw=2.6, bpw_infeasible=2.25,
+                          int8_fraction=0.01, dtype="bf16", layers=2, layers_per_encode=1,
+                          workload="tiny_gqa_model_2_layers_int8_top1pct"),
 }
 
 
@@ -61,8 +80,14 @@ def shapes_of(cfg):
 
     if cfg["ffn"] == 0:  # a single Linear (BASELINE config 1)
         return {"w": (cfg["hidden"], cfg["hidden"])}, {"x": cfg["hidden"]}, LayerPlan({"w": "x"})
-    w, x = llama_shapes(cfg["hidden"], cfg["ffn"])
+    w, x = llama_shapes(cfg["hidden"], cfg["ffn"], cfg.get("kv_rows"))
     return w, x, llama_plan()
+
+
+def candidates_of(cfg):
+    from hi2_b200.calibrate import ALL_CANDIDATES, SELECTABLE
+
+    return list(SELECTABLE if cfg.get("int8_fraction") else ALL_CANDIDATES)
 
 
 def torch_dtype(name):
@@ -325,13 +350,13 @@ class ModelJob:
         self.groups = self.n_layers // world
         self.owned = [g * world + rank for g in range(self.groups)]
         self.shapes, self.widths, self.plan = shapes_of(cfg)
-        self.qcfg = Config(candidates=list(ALL_CANDIDATES))
+        self.qcfg = Config(candidates=candidates_of(cfg))
         self.weights = {l: make_weights(cfg, self.shapes, l, device) for l in self.owned}
         lo, hi = hd.token_shard(cfg["tokens"], rank, world)
         self.inputs = make_inputs(cfg, self.widths, 0, hi - lo, lo, device)
         self.rows_layer = sum(r for r, _ in self.shapes.values())
         self.rows = self.rows_layer * self.n_layers  # whole model, all ranks
-        self.specs = [(l % world, f"L{l}.{name}", shape, list(ALL_CANDIDATES), cfg["tokens"], True)
+        self.specs = [(l % world, f"L{l}.{name}", shape, candidates_of(cfg), cfg["tokens"], True)
                       for l in range(self.n_layers) for name, shape in self.shapes.items()]
         self.stacks = None
         self.host = None
@@ -424,6 +449,13 @@ class ModelJob:
         self._mark(marks, "allocate")
         local = [state[l]["tables"][name] for l in self.owned for name in self.shapes]
         everything = hd.gather_tables_known_layout(local, self.specs, TensorTable)
+        below_floor = None
+        if self.cfg.get("int8_fraction"):
+            L.keep_int8_for_most_sensitive(everything, self.cfg["int8_fraction"])
+        if self.cfg.get("bpw_infeasible"):  # a target below the format's floor: the reference warns and
+            probe = allocate_global(everything, self.cfg["bpw_infeasible"])  # takes the cheapest assignment
+            below_floor = {"target_bpw": self.cfg["bpw_infeasible"], "feasible": probe.feasible, "bpw": probe.bpw,
+                           "rows_by_width": probe.frac_by_bits}
         alloc = allocate_global(everything, self.cfg["bpw"])
         for st in state.values():  # the allocation has read results back: the status words are there
             for sh in [st["shared"], *st["others"]]:
@@ -454,7 +486,8 @@ class ModelJob:
             for l in chunk:
                 state[l] = None  # second moments and factors of the layer are free again
         self._mark(marks, "end")
-        self.last = dict(marks=marks, alloc=alloc, packed=packed, hess_events=hess_events, timing=timing)
+        self.last = dict(marks=marks, alloc=alloc, packed=packed, hess_events=hess_events, timing=timing,
+                         below_floor=below_floor)
         return packed
 
     def collect_stage_times(self):
@@ -474,6 +507,159 @@ class ModelJob:
 
         return sum(getattr(t, f).numel() * getattr(t, f).element_size()
                    for layer in self.last["packed"].values() for t in layer.values() for f in FIELDS)
+
+
+class MoeJob:
+    """Resident workload of one rank for a mixture-of-experts model (BASELINE config 5): the expert
+    projections of ``moe_layers`` layers; expert ``e`` of every layer is owned by rank ``e mod world``.
+
+    Resident when the timed region starts: the bf16 weights of the owned experts, one set of
+    synthetic activations (hidden states ``[tokens, hidden]`` and expert-intermediate states
+    ``[tokens, expert_ffn]``, standing in for every layer's) and a seeded random router per layer.
+    A step, per layer: route (top-k of ``x W_r^T + bias``), per owned expert the second moments of
+    the tokens routed to it (gate/up share one, hi2/layerwise.py:140-154; down has its own), the
+    top-up of experts below ``expert_min_tokens x widest input`` tokens with the layer's pooled sums
+    (hi2/moe.py:152-156, hi2/layerwise.py:243-258; pooled over the ranks), statistics, factors on
+    side streams, tables; then ONE allocation over all expert tables weighted by
+    ``max(n_e / mean n, 0.05) / E`` (hi2/moe.py:188-207), then the encode with the experts of a layer
+    batched through the GPTQ column loops (row groups select their factor, hi2/hessian.py:267-315).
+    The path has no exchange of activations: every rank routes the same resident tokens."""
+
+    def __init__(self, cfg, rank, world, device):
+        from hi2_b200 import layer as L
+        from hi2_b200.calibrate import ALL_CANDIDATES, Config
+
+        self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
+        self.n_layers, self.experts = cfg["moe_layers"], cfg["experts"]
+        h, f = cfg["hidden"], cfg["expert_ffn"]
+        self.owned = [e for e in range(self.experts) if e % world == rank]
+        self.proj = {"gate_proj": (f, h), "up_proj": (f, h), "down_proj": (h, f)}
+        self.reads = {"gate_proj": "in", "up_proj": "in", "down_proj": "mid"}
+        self.qcfg = Config(candidates=list(ALL_CANDIDATES))
+        dt = torch_dtype(cfg["dtype"])
+        g = torch.Generator(device=device).manual_seed(4242)
+        self.weights = {}
+        for l in range(self.n_layers):
+            for e in self.owned:
+                ge = torch.Generator(device=device).manual_seed(100000 + 1000 * l + e)
+                for p, (r, k) in self.proj.items():
+                    self.weights[(l, e, p)] = (torch.randn(r, k, generator=ge, device=device) * 0.02).to(dt)
+        x = make_inputs(cfg, {"in": h, "mid": f}, 0, cfg["tokens"], 0, device)
+        self.x_in, self.x_mid = x["in"], x["mid"]
+        self.router = [(torch.randn(self.experts, h, generator=g, device=device) / h**0.5).to(dt) for _ in range(self.n_layers)]
+        self.bias = [cfg["router_bias"] * torch.randn(self.experts, generator=g, device=device) for _ in range(self.n_layers)]
+        self.rows_layer = self.experts * sum(r for r, _ in self.proj.values())
+        self.rows = self.rows_layer * self.n_layers
+        self.specs = [(e % world, f"L{l}.experts.{e}.{p}", shape, list(ALL_CANDIDATES), 0, True)
+                      for l in range(self.n_layers) for e in range(self.experts) for p, shape in self.proj.items()]
+        self.widths = {"in": h, "mid": f}
+        self.stage_ms: dict = {}
+        self.gptq: dict = {}
+        self.plan = L.LayerPlan({f"experts.{e}.{p}": f"experts.{e}.{self.reads[p]}" for e in self.owned for p in self.proj})
+
+    def route(self, l):
+        """Token indices per expert: ``(order [tokens * top_k] sorted by expert, counts [experts])``."""
+        logits = (self.x_in @ self.router[l].T).float() + self.bias[l]
+        top = torch.topk(logits, self.cfg["top_k"], dim=1).indices  # [tokens, top_k], distinct experts per token
+        flat = top.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=self.experts)
+        return order // self.cfg["top_k"], counts
+
+    def _mark(self, marks, name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append((name, ev))
+
+    def step(self, to_host=False):
+        import torch.distributed as dist
+
+        from hi2_b200 import dist as hd
+        from hi2_b200 import layer as L
+        from hi2_b200 import moe
+        from hi2_b200.allocate import allocate_global
+        from hi2_b200.calibrate import EncodeRequest, TensorTable, encode_many
+
+        marks: list = []
+        self._mark(marks, "tabulate")
+        state, token_counts = {}, {}
+        reduce = (lambda t: dist.all_reduce(t)) if self.world > 1 else None
+        for l in range(self.n_layers):
+            tokens_of, counts = self.route(l)
+            counts = counts.tolist()  # the one read-back of the layer
+            offs = [0]
+            for c in counts:
+                offs.append(offs[-1] + c)
+            shared = {}
+            for e in self.owned:
+                rows = tokens_of[offs[e] : offs[e + 1]]
+                if rows.numel():
+                    L.accumulate({f"experts.{e}.in": self.x_in.index_select(0, rows),
+                                  f"experts.{e}.mid": self.x_mid.index_select(0, rows)}, self.device, into=shared,
+                                 defer_check=True)
+                else:  # an expert without tokens: empty sums, filled by the top-up
+                    from hi2_b200.hessian import HessianStats
+
+                    for nm, k in (("in", self.cfg["hidden"]), ("mid", self.cfg["expert_ffn"])):
+                        shared[f"experts.{e}.{nm}"] = L.SharedInput(f"experts.{e}.{nm}", k, HessianStats(k, self.device))
+            for s_in in shared.values():
+                s_in.hessian.check()
+                s_in.moments = L.ColumnStats.from_second_moment(s_in.hessian.S, s_in.hessian.n)
+            own_tokens = {name: s_in.hessian.n for name, s_in in shared.items()}
+            # leaders named like the expert's first projection, so the grouping of hi2_b200.moe applies
+            alias = {f"experts.{e}.in": f"L{l}.experts.{e}.gate_proj" for e in self.owned}
+            alias.update({f"experts.{e}.mid": f"L{l}.experts.{e}.down_proj" for e in self.owned})
+            borrowed = moe.top_up({alias[n]: s_in.moments for n, s_in in shared.items()},
+                                  {alias[n]: s_in.hessian for n, s_in in shared.items()},
+                                  {alias[n]: s_in.k for n, s_in in shared.items()}, self.qcfg.expert_min_tokens, reduce)
+            weights = {f"experts.{e}.{p}": self.weights[(l, e, p)] for e in self.owned for p in self.proj}
+            factors, tables = {}, {}
+            for s_in in shared.values():
+                flags = torch.ones(s_in.k // 16, dtype=torch.uint8)
+                from hi2_b200.calibrate import smoothing_scale
+
+                s_in.transform = (smoothing_scale(s_in.moments, self.qcfg.smooth), flags)
+            L.start_factors(shared, self.qcfg, self.device, into=factors, release_scratch=True)
+            L.tabulate(weights, self.plan, shared, self.qcfg, into=tables)
+            for name, t in tables.items():
+                t.name = f"L{l}.{name}"
+                t.n_tokens = own_tokens[self.plan.reads[name]]  # an expert reports its own tokens (hi2/layerwise.py:230)
+            state[l] = dict(shared=shared, factors=factors, tables=tables, weights=weights, borrowed=len(borrowed))
+            token_counts[l] = counts
+        self._mark(marks, "allocate")
+        local = [state[l]["tables"][f"experts.{e}.{p}"] for l in range(self.n_layers) for e in self.owned for p in self.proj]
+        specs = [(o, n, sh, c, token_counts[int(n.split(".")[0][1:])][int(n.split(".")[2])], sc)
+                 for o, n, sh, c, _, sc in self.specs]
+        everything = hd.gather_tables_known_layout(local, specs, TensorTable)
+        share = moe.expert_weights({t.name: t for t in everything})
+        alloc = allocate_global(everything, self.cfg["bpw"], sensitivity=share)
+        self._mark(marks, "encode")
+        packed, timing = {}, []
+        for l in range(self.n_layers):
+            st = state[l]
+            reqs, keys = [], []
+            for name, w in st["weights"].items():
+                s_in = st["shared"][self.plan.reads[name]]
+                reqs.append(EncodeRequest(w, s_in.moments, st["tables"][name], alloc.picks[f"L{l}.{name}"],
+                                          sigma=s_in.hessian.S, sigma_id=s_in.name, sigma_n=s_in.hessian.n))
+                keys.append((l, name))
+            out = encode_many(reqs, self.qcfg, to_host=to_host, factors=st["factors"], timing=timing)
+            for k_, t in zip(keys, out):
+                packed[k_] = t
+            state[l] = dict(borrowed=st["borrowed"])
+        self._mark(marks, "end")
+        self.last = dict(marks=marks, alloc=alloc, packed=packed, timing=timing, token_counts=token_counts,
+                         borrowed=sum(st["borrowed"] for st in state.values()), share=share)
+        return packed
+
+    def collect_stage_times(self):
+        marks = self.last["marks"]
+        for (name, a), (_, b) in zip(marks, marks[1:]):
+            self.stage_ms[name] = self.stage_ms.get(name, 0.0) + a.elapsed_time(b)
+        for k, rows, a, b in self.last["timing"]:
+            acc = self.gptq.setdefault(k, [0, 0.0])
+            acc[0] += rows
+            acc[1] += a.elapsed_time(b)
 
 
 class PropagatedJob:
@@ -610,7 +796,7 @@ def cpu_sample(cfg, threads: int, budget_s: float = 30.0) -> dict:
 
     torch.set_num_threads(threads)
     shapes, widths, plan = shapes_of(cfg)
-    cands = [(nb, b) for nb in (2, 4) for b in (16, 32, 64)]
+    cands = candidates_of(cfg)
     dt = torch_dtype(cfg["dtype"])
     g = torch.Generator().manual_seed(0)
     t = {k: 0.0 for k in ("hessian", "statistics", "tables", "allocate", "factor", "gptq_ladders", "gptq_columns", "pack")}
@@ -890,6 +1076,7 @@ def run_ours(args, cfg):
     ms_per_step = float(ms.item())
     clock_info = clocks.stop() if rank == 0 else None
     alloc = job.last["alloc"]
+    below_floor = job.last.get("below_floor") if whole_model else None
 
     # ---- end to end: pinned host buffers in, packed buffers out ------------------------------
     e2e = None
@@ -919,7 +1106,7 @@ def run_ours(args, cfg):
 
     # ---- the same model with the activations produced on the device (calibration propagation) ----
     propagated = None
-    if whole_model and not args.no_propagate:
+    if whole_model and not args.no_propagate and not cfg.get("kv_rows"):  # the toy model builder has no GQA case
         keep = dict(stage_ms=job.stage_ms, hessian_ms=job.hessian_ms, hessian_launches=job.hessian_launches,
                     gptq=job.gptq, widths=job.widths, rows_layer=job.rows_layer)
         job.weights = job.inputs = job.host = job.stacks = job.last = None  # free HBM and pinned memory
@@ -981,7 +1168,7 @@ def run_ours(args, cfg):
         "launch_ms": hess_s * 1e3 / max(1, n_launch),
     }
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and max(job.widths.values()) <= 16384:  # wider: minutes per factor
         threads = host_threads()
         t0 = time.perf_counter()
         res = cpu_sample(cfg, threads, 25.0)
@@ -992,7 +1179,8 @@ def run_ours(args, cfg):
                "config1_in_full": None if args.no_config1 else cpu_config1_full(threads)}
     config = {"workload": cfg["workload"], "layers": cfg.get("layers", world), "rows_per_layer": job.rows_layer if whole_model else job.rows,
               "tokens_per_input": cfg["tokens"], "target_bpw": cfg["bpw"], "achieved_bpw": alloc.bpw,
-              "candidates": "int2,int4 x b16,b32,b64",
+              "candidates": "int2,int4 x b16,b32,b64" + (" + int8 x b32,b64 for the "
+                                                          f"{cfg['int8_fraction']:.0%} most sensitive rows" if cfg.get("int8_fraction") else ""),
               "parallelism": (f"layer l on rank l mod {world}, token-sharded hessian, one reduce-scatter per input and layer group"
                               if whole_model else f"layer-per-gpu x{world}, token-sharded hessian"),
               "l2": "inputs larger than L2 (12-24 GB of activations per layer)"}
@@ -1011,11 +1199,77 @@ def run_ours(args, cfg):
     }
     if propagated is not None:
         line["propagated"] = propagated
+    if whole_model and below_floor is not None:
+        line["allocation_below_format_floor"] = below_floor
+        line["rows_by_width"] = alloc.frac_by_bits
     if whole_model and job.gptq:
         # rows through the GPTQ column loop (block kernel + trailing updates) per second of that loop,
         # per width; the widths run beside each other on two streams
         line["gptq_rows_per_s"] = {str(k): rows / (ms / 1e3) for k, (rows, ms) in sorted(job.gptq.items())}
     emit(line)
+
+
+def run_moe(args, cfg):
+    """BASELINE config 5 (per-expert statistics and GPTQ, experts spread over the ranks): the resident
+    step only; prints one line with the same keys as the default workload's where they apply."""
+    import statistics
+
+    import torch.distributed as dist
+
+    from hi2_b200 import _lib
+    from hi2_b200 import dist as hd
+
+    rank, world, device = hd.init_from_env("cuda")
+    _lib.load()
+    job = MoeJob(cfg, rank, world, device)
+
+    def sync_all():
+        torch.cuda.synchronize(device)
+        hd.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        job.step()
+    sync_all()
+    clocks = Clocks(device.index or 0)
+    if rank == 0:
+        clocks.start()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        job.step()
+        torch.cuda.synchronize(device)
+        job.collect_stage_times()
+    ev1.record()
+    sync_all()
+    launches = _lib.launch_count() - launches0
+    ms = torch.tensor([ev0.elapsed_time(ev1) / args.steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clock_info = clocks.stop() if rank == 0 else None
+    if rank != 0:
+        return
+    ms_per_step = float(ms.item())
+    counts = [c for layer in job.last["token_counts"].values() for c in layer]
+    alloc = job.last["alloc"]
+    emit({
+        "metric": "ptq_encode_rows_per_s", "value": job.rows / (ms_per_step / 1e3), "unit": "rows/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg["workload"], "layers": cfg["moe_layers"], "experts": cfg["experts"], "top_k": cfg["top_k"],
+                   "rows_per_layer": job.rows_layer, "tokens": cfg["tokens"], "target_bpw": cfg["bpw"],
+                   "achieved_bpw": alloc.bpw, "parallelism": f"expert e on rank e mod {world}; no exchange of activations",
+                   "tokens_per_expert": {"min": min(counts), "median": statistics.median(counts), "max": max(counts)},
+                   "expert_inputs_topped_up": job.last["borrowed"],
+                   "activations": "one synthetic set stands in for every layer's hidden and expert-intermediate states"},
+        "encode_wall_s": ms_per_step / 1e3, "stage_ms": {k: round(v / args.steps, 3) for k, v in job.stage_ms.items()},
+        "gptq_rows_per_s": {str(k): rows / (t / 1e3) for k, (rows, t) in sorted(job.gptq.items())},
+        "roofline": None, "cpu_baseline": None,
+        "e2e": {"value": None, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "not measured for this configuration (the default workload carries the end-to-end figure)"},
+        "gpu_launches": launches, "clocks": clock_info,
+    })
 
 
 # --------------------------------------------------------------------------------------------
@@ -1183,14 +1437,20 @@ def main():
     ap.add_argument("--config", default="cfg3", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="whole-model configs: take this many layers instead of all")
     ap.add_argument("--no-config1", action="store_true", help="skip the full CPU run of config 1 in the cpu_baseline leg")
     ap.add_argument("--no-propagate", action="store_true",
                     help="skip the run with the activations produced on the device by layer forwards")
     ap.add_argument("--kernels", action="store_true", help="time every hot kernel alone against its bound")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.layers and "layers" in cfg:
+        cfg["layers"] = args.layers
+        cfg["workload"] += f"_first_{args.layers}_layers"
     if args.kernels:
         run_kernels(args, cfg)
+    elif "moe_layers" in cfg:
+        run_moe(args, cfg)
     elif args.impl == "reference":
         run_reference(args, cfg)
     else:

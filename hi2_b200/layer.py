@@ -97,7 +97,7 @@ def start_factors(shared: dict, cfg: Config, device, only: str | None = None, in
     for i, s in enumerate(shared.values()):
         if only is not None and s.name != only:
             continue
-        side = _side_stream(device, i)
+        side = _side_stream(device, i % 8)  # a layer of experts has hundreds of inputs: eight chains at a time
         side.wait_stream(main)
         with torch.cuda.stream(side):
             d, job, hs = factor_for(s.hessian.S, s.hessian.n, s.transform[0], s.transform[1], cfg)
@@ -141,13 +141,53 @@ def llama_plan() -> LayerPlan:
                       "gate": "mlp_in", "up": "mlp_in", "down": "mlp_mid"})
 
 
-def llama_shapes(hidden: int = 4096, ffn: int = 11008) -> tuple[dict, dict]:
-    """``({weight: (rows, k)}, {input: k})`` of one decoder layer."""
-    w = {"q": (hidden, hidden), "k": (hidden, hidden), "v": (hidden, hidden), "o": (hidden, hidden),
+def llama_shapes(hidden: int = 4096, ffn: int = 11008, kv_rows: int | None = None) -> tuple[dict, dict]:
+    """``({weight: (rows, k)}, {input: k})`` of one decoder layer; ``kv_rows`` is the height of the
+    k and v projections under grouped-query attention (default: ``hidden``)."""
+    kv = hidden if kv_rows is None else kv_rows
+    w = {"q": (hidden, hidden), "k": (kv, hidden), "v": (kv, hidden), "o": (hidden, hidden),
          "gate": (ffn, hidden), "up": (ffn, hidden), "down": (hidden, ffn)}
     x = {"attn_in": hidden, "attn_out": hidden, "mlp_in": hidden, "mlp_mid": ffn}
     return w, x
 
 
+def keep_int8_for_most_sensitive(tables: list, fraction: float = 0.01) -> None:
+    """Leave the INT8 candidates open only to the ``fraction`` of ALL rows whose best INT4 cost is
+    largest, and close them for the rest, in place.  A closed INT8 entry is given the error of the
+    row's best INT4 ladder: with equal error and more bits it can never be the allocator's argmin,
+    while every number stays finite (an infinite entry would break the allocator's upper multiplier,
+    hi2/allocate.py:233-240, in the reference as much as here).
+
+    The reference has INT8 as a candidate for every row (hi2/calibrate.py:30-31, chosen by the
+    allocator) or forced for whole tensors (hi2/allocate.py:62-76); "INT8 for the 1 % most
+    sensitive rows" is the harness rule between the two: the allocator may spend 8 bits only where
+    4 bits hurt most.  Cost is what the allocator minimises, ``sse / energy`` of the table
+    (hi2/allocate.py:79-85).  The threshold is one quantile over the rows of all tables."""
+    costs, best4 = [], []
+    for t in tables:
+        four = [i for i, (nb, _) in enumerate(t.candidates) if nb == 4]
+        eight = [i for i, (nb, _) in enumerate(t.candidates) if nb == 8]
+        if not four or not eight:
+            best4.append(None)
+            continue
+        e = t.energy if isinstance(t.energy, torch.Tensor) else torch.tensor(float(t.energy), device=t.sse.device)
+        floor4 = t.sse[four].min(0).values
+        c = floor4 / e.to(t.sse.device, t.sse.dtype).clamp_min(1e-30)
+        best4.append((c, eight, floor4))
+        costs.append(c)
+    if not costs:
+        return
+    allc = torch.cat(costs)
+    keep = max(1, int(round(fraction * allc.numel())))
+    threshold = torch.topk(allc, keep).values[-1]
+    for t, item in zip(tables, best4):
+        if item is None:
+            continue
+        c, eight, floor4 = item
+        closed = c < threshold
+        for i in eight:  # same error as the row's best INT4 ladder for more bits: never the argmin
+            t.sse[i] = torch.where(closed, floor4, t.sse[i])
+
+
 __all__ = ["SharedInput", "LayerPlan", "accumulate", "finish_statistics", "start_factors", "tabulate", "encode",
-           "llama_plan", "llama_shapes", "Config", "TensorTable", "HI2Tensor"]
+           "llama_plan", "llama_shapes", "keep_int8_for_most_sensitive", "Config", "TensorTable", "HI2Tensor"]

@@ -64,9 +64,13 @@ def accumulate_routed(x: torch.Tensor, top_k_index: torch.Tensor, hess: list, st
             stats[e].update(xe)
 
 
-def top_up(stats: dict, hess: dict | None, k_of: dict, min_tokens: float):
+def top_up(stats: dict, hess: dict | None, k_of: dict, min_tokens: float, all_reduce=None):
     """Top the leaders of every expert group up to ``min_tokens x widest input`` tokens with the
-    group's pooled sums; returns the set of leaders that borrowed (hi2/layerwise.py:231-257)."""
+    group's pooled sums; returns the set of leaders that borrowed (hi2/layerwise.py:231-257).
+
+    ``all_reduce`` (optional, ``tensor -> None`` in place): when the experts of a group are spread
+    over several ranks each rank passes its own experts and the pooled sums and token totals are
+    summed over the ranks through it before anybody borrows."""
     borrowed: set[str] = set()
     if min_tokens <= 0:
         return borrowed
@@ -79,10 +83,20 @@ def top_up(stats: dict, hess: dict | None, k_of: dict, min_tokens: float):
     for ld in stats:
         if expert_parts(ld) is not None:
             groups.setdefault(group_key(ld), []).append(ld)
-    for lds in groups.values():
+    for key in sorted(groups):  # the same order on every rank
+        lds = groups[key]
         tot_n = sum(stats[ld].n for ld in lds)
         tot_s = sum(stats[ld].S for ld in lds)
         tot_h = sum(hess[ld].S for ld in lds) if hess else None
+        if all_reduce is not None:
+            count = torch.tensor([tot_n], dtype=torch.int64, device=tot_s.device)
+            all_reduce(count)
+            tot_n = int(count.item())
+            tot_s = tot_s.clone()
+            all_reduce(tot_s)
+            if tot_h is not None:
+                tot_h = tot_h.clone()
+                all_reduce(tot_h)
         for ld in lds:
             need = int(min_tokens * width[expert_parts(ld)[:2]])
             if stats[ld].n >= need or tot_n == 0:

@@ -65,3 +65,47 @@ def test_top_up_borrows_the_pooled_sum():
             assert torch.equal(stats[n].S, g0 + fill * tot_s) and stats[n].n == need
         else:
             assert torch.equal(hess[n].S, s0) and hess[n].n == n0
+
+
+def test_moe_job_routes_tops_up_and_encodes_per_expert():
+    """bench.MoeJob on a toy mixture (8 experts, top-2, a strongly biased router): per-expert
+    second moments over the routed tokens only (hi2 tests/test_moe.py:157-181 semantics), starved
+    experts topped up with the pooled sums, allocation weighted by token share, every expert encoded."""
+    import bench
+    from hi2_b200 import moe
+    from hi2_b200.hessian import HessianStats
+
+    cfg = dict(bench.CONFIGS["tiny_moe"])
+    dev = torch.device(DEV, torch.cuda.current_device())
+    job = bench.MoeJob(cfg, 0, 1, dev)
+    tokens_of, counts = job.route(0)
+    counts = counts.tolist()
+    assert sum(counts) == cfg["tokens"] * cfg["top_k"] and min(counts) < max(counts)
+    # second moment of one expert = x_e^T x_e over exactly the tokens whose top-k names it
+    e = max(range(8), key=lambda i: counts[i])
+    off = sum(counts[:e])
+    rows = tokens_of[off : off + counts[e]]
+    logits = (job.x_in @ job.router[0].T).float() + job.bias[0]
+    named = (torch.topk(logits, cfg["top_k"], dim=1).indices == e).any(1).nonzero().squeeze(1)
+    assert torch.equal(rows.sort().values, named)
+    h = HessianStats(cfg["hidden"], dev)
+    h.update(job.x_in.index_select(0, rows))
+    xe = job.x_in.index_select(0, named).double()
+    ref = xe.T @ xe
+    scale = ref.diagonal().clamp_min(1e-30).sqrt()
+    assert ((h.S.double() - ref) / (scale[:, None] * scale[None, :])).abs().max().item() < 2e-5
+    packed = job.step()
+    torch.cuda.synchronize()
+    assert len(packed) == cfg["moe_layers"] * 8 * 3
+    need = int(2.0 * cfg["hidden"])
+    starved = sum(1 for layer in job.last["token_counts"].values() for c in layer if c < need)
+    assert job.last["borrowed"] == 2 * starved and starved > 0  # both inputs of a starved expert borrow
+    alloc = job.last["alloc"]
+    assert alloc.feasible and abs(alloc.bpw - cfg["bpw"]) < 0.02
+    share = job.last["share"]
+    layer0 = job.last["token_counts"][0]
+    mean = sum(layer0) / 8
+    for ex in range(8):
+        assert abs(share[f"L0.experts.{ex}.down_proj"] - max(layer0[ex] / mean, 0.05) / 8) < 1e-12
+    t = packed[(1, "experts.3.down_proj")]
+    assert t.shape == (cfg["hidden"], cfg["expert_ffn"]) and int(t.code_off[-1]) == t.codes.numel()

@@ -122,3 +122,50 @@ def test_propagated_job_runs_the_whole_model():
     t = packed["model.layers.3.mlp.down_proj.weight"]
     assert t.shape == (512, 1024) and t.codes.device.type == "cpu" and int(t.code_off[-1]) == t.codes.numel()
     assert job.d2h_bytes() > 0 and job.h2d > 0
+
+
+def test_whole_model_job_gqa_int8_rule_and_infeasible_target():
+    """The config-4 mechanics on a toy model: grouped-query shapes (k/v shorter than q), INT8
+    candidates open only to the 1 % most sensitive rows, a target below the format's floor recorded
+    as infeasible with every row at INT2 (hi2/allocate.py:248-249), the encode at the feasible one."""
+    import bench
+
+    cfg = dict(bench.CONFIGS["tiny_gqa_int8"])
+    dev = torch.device(DEV, torch.cuda.current_device())
+    job = bench.ModelJob(cfg, 0, 1, dev)
+    assert job.shapes["k"] == (128, 512) and len(job.qcfg.candidates) == 8
+    packed = job.step()
+    torch.cuda.synchronize()
+    low = job.last["below_floor"]
+    assert low["feasible"] is False and low["bpw"] > cfg["bpw_infeasible"] and low["rows_by_width"][2] == 1.0
+    alloc = job.last["alloc"]
+    assert alloc.feasible and abs(alloc.bpw - cfg["bpw"]) < 0.02
+    share8 = alloc.frac_by_bits[8]
+    assert 0.0 <= share8 <= cfg["int8_fraction"] + 1e-3, share8
+    rows8 = sum(int((t.row_nbits == 8).sum()) for layer in packed.values() for t in layer.values())
+    assert rows8 == round(share8 * job.rows)
+
+
+def test_int8_rule_closes_all_but_the_most_sensitive_rows():
+    from hi2_b200.calibrate import SELECTABLE, TensorTable
+    from hi2_b200.layer import keep_int8_for_most_sensitive
+
+    g = gen(5)
+    tabs = []
+    for i, r in enumerate((300, 700)):
+        sse = torch.rand(8, r, generator=g) + 0.1
+        sse[6:] *= 0.01  # INT8 is far more accurate
+        tabs.append(TensorTable(f"t{i}", (r, 256), torch.ones(16, dtype=torch.uint8), sse.to(DEV), list(SELECTABLE), 1.0 + i, 10))
+    before = [t.sse.clone() for t in tabs]
+    keep_int8_for_most_sensitive(tabs, 0.01)
+    cost = torch.cat([b[3:6].min(0).values / (1.0 + i) for i, b in enumerate(before)])
+    top = set(torch.topk(cost, 10).indices.tolist())
+    off = 0
+    for t, b in zip(tabs, before):
+        assert torch.equal(t.sse[:6], b[:6])
+        for row in range(b.shape[1]):
+            if off + row in top:
+                assert torch.equal(t.sse[6:, row], b[6:, row])
+            else:
+                assert bool((t.sse[6:, row] == b[3:6, row].min()).all())
+        off += b.shape[1]
