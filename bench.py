@@ -436,6 +436,9 @@ class ModelJob:
                 work.wait()
             if ready is not None:
                 cur.wait_event(ready[mine_l])
+            # The factorisations start here, on side streams, beside the table kernels.  (Starting them
+            # beside the GPTQ column loops of the encode phase instead was measured: the tables gain
+            # 16 ms per layer and the column loops lose 24.)
             factors, tables = {}, {}
             for name in order:
                 L.finish_statistics(mine, self.qcfg, only=name)
@@ -467,6 +470,7 @@ class ModelJob:
         # host reads status words back once per call, not once per layer.
         packed, timing = {}, []
         per_call = self.cfg.get("layers_per_encode", 4)
+
         for c0 in range(0, len(self.owned), per_call):
             chunk = self.owned[c0 : c0 + per_call]
             reqs, keys, fac = [], [], {}
@@ -1292,7 +1296,12 @@ def run_kernels(args, cfg):
     # larger than L2, and long enough to write that the host has queued the timed call before it ends
     flush = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
 
-    def timed(fn, reps=5, warm=3, cold=True):
+    only = set(filter(None, (args.only or "").split(",")))
+
+    def timed(fn, reps=5, warm=3, cold=True, tag=None):
+        if only and tag not in only and tag != "always":  # not asked for: run once (later sections use its results), no timing
+            fn()
+            return float("nan")
         for _ in range(warm):
             fn()
         samples = []
@@ -1310,6 +1319,8 @@ def run_kernels(args, cfg):
     rows_out = []
 
     def add(name, bound, work, unit, ms, peak, note=""):
+        if ms != ms:  # not timed (--only)
+            return
         achieved = work / (ms * 1e-3)
         rows_out.append(dict(kernel=name, bound=bound, ms=round(ms, 4), achieved=achieved, unit=unit, peak=peak,
                              frac=achieved / peak if peak else None, note=note))
@@ -1318,9 +1329,9 @@ def run_kernels(args, cfg):
     a = torch.randn(8192, 8192, device=dev, generator=g)
     b = torch.randn(8192, 8192, device=dev, generator=g)
     torch.backends.cuda.matmul.allow_tf32 = False
-    fp32_peak = 2 * 8192**3 / (timed(lambda: torch.matmul(a, b), cold=False) * 1e-3) / 1e12
+    fp32_peak = 2 * 8192**3 / (timed(lambda: torch.matmul(a, b), cold=False, tag="always") * 1e-3) / 1e12
     torch.backends.cuda.matmul.allow_tf32 = True
-    tf32_peak = 2 * 8192**3 / (timed(lambda: torch.matmul(a, b), cold=False) * 1e-3) / 1e12
+    tf32_peak = 2 * 8192**3 / (timed(lambda: torch.matmul(a, b), cold=False, tag="always") * 1e-3) / 1e12
     torch.backends.cuda.matmul.allow_tf32 = False
     del a, b
     lane_peak = fp32_peak / 2  # fp32 instructions per second (T lane-ops/s): an FMA is two flops
@@ -1331,7 +1342,7 @@ def run_kernels(args, cfg):
     for kk in (k, k_wide):
         x = torch.randn(tokens, kk, device=dev, generator=g).bfloat16()
         h = HessianStats(kk, dev)
-        ms = timed(lambda: h.update(x, defer_check=True), reps=5, warm=2)
+        ms = timed(lambda: h.update(x, defer_check=True), reps=5, warm=2, tag="hessian")
         h.check()
         nib, njb = -(-kk // 128), -(-kk // 256)
         tiles = sum(njb - (ib >> 1) for ib in range(nib))
@@ -1344,10 +1355,10 @@ def run_kernels(args, cfg):
         # basis change and inverse factor of the same input
         s16 = (torch.rand(kk, device=dev, generator=g) + 0.5).half()
         had = torch.ones(kk // 16, dtype=torch.uint8, device=dev)
-        ms = timed(lambda: transform_sigma(sig, s16, had, denom=1.0, return_diag=True))
+        ms = timed(lambda: transform_sigma(sig, s16, had, denom=1.0, return_diag=True), tag="sigma")
         add(f"transform_sigma K={kk}", "hbm", 8.0 * kk * kk / 1e9, "GB/s", ms, pk["hbm"])
         hs = transform_sigma(sig, None, had)
-        ms = timed(lambda: inverse_factor(hs, 0.01), reps=3, warm=1, cold=False)
+        ms = timed(lambda: inverse_factor(hs, 0.01), reps=3, warm=1, cold=False, tag="factor")
         add(f"inverse_factor K={kk}", "fp32-grade flops", (2.0 / 3.0) * kk**3 / 1e12, "TFLOP/s", ms, fp32_peak,
             "(2/3) K^3 against the cuBLAS fp32 peak; a chain of K/64 dependent leaves")
         if kk == k:
@@ -1357,25 +1368,28 @@ def run_kernels(args, cfg):
     wb = (torch.randn(r_wide, k, device=dev, generator=g) * 0.02).bfloat16()
     had = torch.ones(k // 16, dtype=torch.uint8, device=dev)
     s32 = torch.rand(k, device=dev, generator=g) + 0.5
-    ms = timed(lambda: fwht_groups(wb, had, col_scale=s32, out_dtype=torch.float32))
+    ms = timed(lambda: fwht_groups(wb, had, col_scale=s32, out_dtype=torch.float32), tag="rotate")
     add(f"rotate bf16->fp32 {r_wide}x{k}", "hbm", wb.numel() * 6.0 / 1e9, "GB/s", ms, pk["hbm"])
     w = fwht_groups(wb, had, col_scale=s32, out_dtype=torch.float32)
     d = torch.rand(k, device=dev, generator=g) + 0.05
     eff = EFFORT["normal"]
     ops_per_weight = 11 * len(eff["grid"]) ** 2 + 28 * eff["ls"] + 14  # fp32 operations of the reference's search
     for block in (16, 32, 64):
-        ms = timed(lambda: ladder_kernel.fit(w, d, eff["grid"], eff["ls"], 4, block))
+        ms = timed(lambda: ladder_kernel.fit(w, d, eff["grid"], eff["ls"], 4, block), tag="fit")
         add(f"fit_kernel<{block}> INT2 {r_wide}x{k}", "fp32 instruction issue", w.numel() * ops_per_weight / 1e12,
             "Tops/s", ms, lane_peak, f"{ops_per_weight} reference operations per weight; peak = cuBLAS fp32 flops / 2")
     lo, st = ladder_kernel.fit(w, d, eff["grid"], eff["ls"], 4, 32)
-    ms = timed(lambda: ladder_kernel.quantize_rows(lo, st, 2, 32, k, w, d, want_codes=True, want_sse=True))
+    ms = timed(lambda: ladder_kernel.quantize_rows(lo, st, 2, 32, k, w, d, want_codes=True, want_sse=True), tag="row")
     add(f"row_kernel<32> INT2 {r_wide}x{k}", "hbm", (w.numel() * 5.0 + lo.numel() * 10.0) / 1e9, "GB/s", ms, pk["hbm"],
         "reads fp32 rows, writes codes, parameter bytes and sse")
+    ms = timed(lambda: ladder_kernel.quantize_rows(lo, st, 2, 32, k, w, d, want_codes=False, want_sse=True), tag="row")
+    add(f"row_kernel<32> INT2 {r_wide}x{k}, table pass (no codes)", "hbm", (w.numel() * 4.0 + lo.numel() * 10.0) / 1e9,
+        "GB/s", ms, pk["hbm"], "what a table entry costs: reads fp32 rows, writes parameter bytes and sse")
     q = ladder_kernel.quantize_rows(lo, st, 2, 32, k, w, d, want_codes=True, want_decoded=True, ldp=k // 16)
     words = torch.empty(r_wide, k // 16, dtype=torch.int32, device=dev)
     bad = torch.zeros(1, dtype=torch.int32, device=dev)
     ms = timed(lambda: _lib.call("hi2_pack_codes", _lib.ptr(q["codes"]), _lib.ptr(words), r_wide, k, 2, _lib.ptr(bad),
-                                 _lib.stream(dev)))
+                                 _lib.stream(dev)), tag="pack")
     assert torch.equal(words, pack_codes(q["codes"], 2)) and int(bad.item()) == 0
     add(f"pack_codes INT2 {r_wide}x{k}", "hbm", w.numel() * 1.25 / 1e9, "GB/s", ms, pk["hbm"],
         "the C entry point alone (the Python wrapper also reads the out-of-range flag back)")
@@ -1389,19 +1403,36 @@ def run_kernels(args, cfg):
     blk = (torch.arange(k, device=dev) // 32).to(torch.int32).reshape(1, k)
     nm = torch.tensor([3.0], device=dev)
     ms_blk = timed(lambda: gptq_kernel.gptq_block(wc, 0, 128, err1, codes, q["lo_d"], q["step_d"], rg, up, blk, nm),
-                   cold=False)
+                   cold=False, tag="gptq")
     add(f"gptq_block N={n} (128 columns)", "dependent chain", n * 128 * 140.0 / 1e12, "Tops/s", ms_blk, lane_peak,
         "140 reference operations per row and column")
     parts = gptq_kernel.split_tf32_transposed(u_small)
     ms_round = timed(lambda: gptq_kernel.gptq_round_tc(wc, err1, codes, q["lo_d"], q["step_d"], rg, up, blk, nm, None,
-                                                        [0, n], [parts]), reps=3, warm=1, cold=False)
+                                                        [0, n], [parts]), reps=3, warm=1, cold=False, tag="gptq")
     lazy_flops = float(n) * k * k * (1 - 128.0 / k)
     ms_lazy = ms_round - (k // 128) * ms_blk
     add(f"lazy_tc (all {k // 128 - 1} trailing updates, N={n})", "tensor (3xTF32)", 3 * lazy_flops / 1e12, "TFLOP/s",
         max(ms_lazy, 1e-3), tf32_peak, "three TF32 products per fp32-grade product; time = column loop minus segments")
-    rows_out.append(dict(kernel=f"GPTQ column loop N={n} K={k}", bound="chain + tensor", ms=round(ms_round, 3),
-                         achieved=n / (ms_round * 1e-3), unit="rows/s", peak=None, frac=None,
-                         note="segments + trailing updates"))
+    if ms_round == ms_round:
+        rows_out.append(dict(kernel=f"GPTQ column loop N={n} K={k}", bound="chain + tensor", ms=round(ms_round, 3),
+                             achieved=n / (ms_round * 1e-3), unit="rows/s", peak=None, frac=None,
+                             note="segments + trailing updates"))
+    # refinement: two sweeps over the rows of one 4096-wide matrix (the reference's CLI default for
+    # calibrated GPTQ without QAD, hi2/__main__.py:164-172); 2 N K^2 flops for g = e Hs plus 2 N K^2 per sweep
+    from hi2_b200.encode import Encoded
+    from hi2_b200.refine import refine_groups
+
+    n_ref = 4096
+    hs_small = transform_sigma(sigma_small, None, had)
+    enc = Encoded(codes[:n_ref].clone(), q["params"][:n_ref], q["consts"][:n_ref], torch.zeros(n_ref, device=dev))
+    ms_ref = timed(lambda: refine_groups([(w[:n_ref], enc, 2, 32)], hs_small, 2), reps=3, warm=1, cold=False, tag="refine")
+    add(f"refine, 2 sweeps, N={n_ref} K={k} (block kernel + 3xTF32 products)", "tensor (3xTF32) + chain",
+        3 * 2.0 * n_ref * k * k * 3 / 1e12, "TFLOP/s", ms_ref, tf32_peak,
+        "three TF32 products per fp32-grade product; includes the 32 block-kernel launches per sweep")
+    if ms_ref == ms_ref and ms_round == ms_round:
+        rows_out.append(dict(kernel=f"refine vs GPTQ column loop (same rows, K={k})", bound="ratio", ms=round(ms_ref, 3),
+                             achieved=ms_ref / (ms_round * n_ref / n), unit="x the GPTQ column loop of the same rows",
+                             peak=None, frac=None, note="the reference reports about 1.1x fused on its hardware"))
     emit({"kernels": rows_out, "peaks": {"hbm_gbs": pk["hbm"], "bf16_tflops_burst": pk["tensor_burst"],
                                          "bf16_tflops_sustained": pk["tensor"], "fp32_tflops_cublas": fp32_peak,
                                          "tf32_tflops_cublas": tf32_peak, "source": pk["source"]},
@@ -1442,6 +1473,8 @@ def main():
     ap.add_argument("--no-propagate", action="store_true",
                     help="skip the run with the activations produced on the device by layer forwards")
     ap.add_argument("--kernels", action="store_true", help="time every hot kernel alone against its bound")
+    ap.add_argument("--only", default="", help="with --kernels: comma-separated sections to time (hessian, sigma, factor, "
+                    "rotate, fit, row, pack, gptq, refine); the others run once, untimed, for their results")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.layers and "layers" in cfg:

@@ -272,7 +272,10 @@ constexpr int ROW_UN = 4;  // quads a lane loads before it computes
 // One WARP per row: the row-wide extrema, the constants and the parameter bytes need only warp
 // shuffles, so no thread block barrier sits between the phases of a row and 64 rows are in flight
 // per SM.  Dynamic shared memory: per warp the decoded lo[nb], step[nb] of its row.
-template <int B>
+// CODES / ENERGY: whether code bytes are written and the row energy is summed.  The tables ask for
+// neither on five of their six passes, and the pass is bound by instruction issue (73 % of the
+// issue slots at a third of the copy bandwidth), so the instructions of unused outputs are compiled out.
+template <int B, bool CODES, bool ENERGY>
 __global__ void __launch_bounds__(ROW_THREADS)
 row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
            const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, float nmax,
@@ -375,17 +378,17 @@ row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
           c = clamp_keep_nan(c, 0.0f, nmax);
           const float diff = round_f16(lod + c * std_) - ws[t];
           acc += ds[t] * (diff * diff);
-          en += ds[t] * (ws[t] * ws[t]);
-          cs[t] = (uint8_t)c;
+          if (ENERGY) en += ds[t] * (ws[t] * ws[t]);
+          if (CODES) cs[t] = (uint8_t)c;
         }
-        if (codes != nullptr)
-          *reinterpret_cast<uchar4*>(codes + row * k + j) = make_uchar4(cs[0], cs[1], cs[2], cs[3]);
+        if (CODES) *reinterpret_cast<uchar4*>(codes + row * k + j) = make_uchar4(cs[0], cs[1], cs[2], cs[3]);
       }
     }
-    acc = warp_sum(acc), en = warp_sum(en);
+    acc = warp_sum(acc);
+    if (ENERGY) en = warp_sum(en);
     if (lane == 0) {
       if (sse != nullptr) sse[row] = acc;
-      if (energy != nullptr) energy[row] = en;
+      if (ENERGY) energy[row] = en;
     }
   }
 }
@@ -487,19 +490,27 @@ extern "C" int hi2_quantize_rows(const float* lo, const float* step, const float
   const unsigned grid = (unsigned)(want < 148 * 8 ? want : 148 * 8);
   const float nmax = (float)((1 << nbits) - 1);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-#define HI2_ROW(BB)                                                                                    \
-  do {                                                                                                 \
-    if (smem > 48 * 1024 &&                                                                            \
-        cudaFuncSetAttribute(row_kernel<BB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != \
-            cudaSuccess)                                                                               \
-      return fail(HI2_ERR_LAUNCH, "quantize_rows: cannot reserve shared memory");                      \
-    row_kernel<BB><<<grid, ROW_THREADS, smem, s>>>(lo, step, w, ldw, d, nmax, n_rows, k, params,       \
-                                                   consts, lo_d, step_d, ldp, codes, sse, energy);     \
+#define HI2_ROW_V(BB, CC, EE)                                                                              \
+  do {                                                                                                     \
+    if (smem > 48 * 1024 &&                                                                                \
+        cudaFuncSetAttribute(row_kernel<BB, CC, EE>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                             (int)smem) != cudaSuccess)                                                    \
+      return fail(HI2_ERR_LAUNCH, "quantize_rows: cannot reserve shared memory");                          \
+    row_kernel<BB, CC, EE><<<grid, ROW_THREADS, smem, s>>>(lo, step, w, ldw, d, nmax, n_rows, k, params,   \
+                                                           consts, lo_d, step_d, ldp, codes, sse, energy); \
+  } while (0)
+#define HI2_ROW(BB)                                     \
+  do {                                                  \
+    if (codes != nullptr && energy != nullptr) HI2_ROW_V(BB, true, true);   \
+    else if (codes != nullptr) HI2_ROW_V(BB, true, false);                  \
+    else if (energy != nullptr) HI2_ROW_V(BB, false, true);                 \
+    else HI2_ROW_V(BB, false, false);                                       \
   } while (0)
   if (block == 16) HI2_ROW(16);
   if (block == 32) HI2_ROW(32);
   if (block == 64) HI2_ROW(64);
 #undef HI2_ROW
+#undef HI2_ROW_V
   return check_launch("quantize_rows");
 }
 

@@ -590,14 +590,25 @@ int launch_lazy_tc(float* wc, int64_t n_rows, int64_t k, int64_t i1, const float
 
 // C[m, n] (ldc) = or += (+-) A . Bt^T with A = a_hi + a_lo [m, kk], Bt = b_hi + b_lo [n, kk], both with
 // leading dimension ldk (a multiple of 4 floats).  flags: GT_* above.  All bases 16-byte aligned.
+int launch_gemm_tc2(int64_t m, int64_t n, int64_t kk, const float* a_hi, const float* a_lo, int64_t lda,
+                    const float* b_hi, const float* b_lo, int64_t ldb, float* c, int64_t ldc, int flags,
+                    int* status, cudaStream_t stream);
+
 int launch_gemm_tc(int64_t m, int64_t n, int64_t kk, const float* a_hi, const float* a_lo, const float* b_hi,
                    const float* b_lo, int64_t ldk, float* c, int64_t ldc, int flags, int* status,
                    cudaStream_t stream) {
+  return launch_gemm_tc2(m, n, kk, a_hi, a_lo, ldk, b_hi, b_lo, ldk, c, ldc, flags, status, stream);
+}
+
+// The same with a leading dimension per operand (A [m, kk] with lda, Bt [n, kk] with ldb).
+int launch_gemm_tc2(int64_t m, int64_t n, int64_t kk, const float* a_hi, const float* a_lo, int64_t lda,
+                    const float* b_hi, const float* b_lo, int64_t ldb, float* c, int64_t ldc, int flags,
+                    int* status, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || kk <= 0) return HI2_OK;
   if (encoder() == nullptr) return fail(HI2_ERR_DRIVER, "gemm_tc: cuTensorMapEncodeTiled unavailable");
   CUtensorMap mah, mal, mbh, mbl, mc;
-  if (!make_map(&mah, a_hi, kk, m, ldk, 32, LM) || !make_map(&mal, a_lo, kk, m, ldk, 32, LM) ||
-      !make_map(&mbh, b_hi, kk, n, ldk, 32, LN) || !make_map(&mbl, b_lo, kk, n, ldk, 32, LN) ||
+  if (!make_map(&mah, a_hi, kk, m, lda, 32, LM) || !make_map(&mal, a_lo, kk, m, lda, 32, LM) ||
+      !make_map(&mbh, b_hi, kk, n, ldb, 32, LN) || !make_map(&mbl, b_lo, kk, n, ldb, 32, LN) ||
       !make_map(&mc, c, n, m, ldc, 32, 32))
     return fail(HI2_ERR_DRIVER, "gemm_tc: cuTensorMapEncodeTiled failed");
   if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L_SMEM) != cudaSuccess)
@@ -657,6 +668,21 @@ extern "C" int hi2_split_tf32_transposed(const float* x, float* hi, float* lo, i
   if (rows == 0 || cols == 0) return HI2_OK;
   HI2_REQUIRE(x && hi && lo, "split_tf32_transposed: null pointer");
   return launch_split_tf32_transposed(x, hi, lo, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hi2_gemm_tf32x3(int64_t m, int64_t n, int64_t kk, const float* a_hi, const float* a_lo, int64_t lda,
+                               const float* bt_hi, const float* bt_lo, int64_t ldb, float* c, int64_t ldc,
+                               int accumulate, int32_t* status, void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(m >= 0 && n >= 0 && kk >= 0, "gemm_tf32x3: negative size");
+  if (m == 0 || n == 0) return HI2_OK;
+  HI2_REQUIRE(kk > 0 && a_hi && a_lo && bt_hi && bt_lo && c && status, "gemm_tf32x3: null pointer or empty reduction");
+  HI2_REQUIRE(aligned16(a_hi) && aligned16(a_lo) && aligned16(bt_hi) && aligned16(bt_lo) && aligned16(c),
+              "gemm_tf32x3: operands must be 16-byte aligned");
+  HI2_REQUIRE(lda % 4 == 0 && ldb % 4 == 0 && ldc % 4 == 0 && lda >= kk && ldb >= kk && ldc >= n,
+              "gemm_tf32x3: leading dimensions must be multiples of 4 floats and cover the rows");
+  return launch_gemm_tc2(m, n, kk, a_hi, a_lo, lda, bt_hi, bt_lo, ldb, c, ldc, accumulate ? GT_ADD : 0,
+                         reinterpret_cast<int*>(status), static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int hi2_split_tf32(const float* x, float* hi, float* lo, int64_t n, void* stream) {

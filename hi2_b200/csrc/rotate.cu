@@ -1,12 +1,14 @@
 // Order-16 Hadamard rotation of flagged column groups, fused with the load-side cast and the
 // smoothing multiply (hi2/format.py:30-41, hi2/calibrate.py:243-251).
 //
-// Layout: the [rows, k] matrix is one flat array of 16-element groups.  A lane owns four
-// consecutive elements (one 128-bit access for fp32), so four adjacent lanes own one group and a
-// warp moves 512 contiguous bytes per access.  The twelve values a lane lacks arrive by warp
-// shuffle.  Every output is the left-to-right sum over k = 0..15 of x_k * (+-1/4): the products
-// are exact, so the result equals a row-times-matrix product accumulated in ascending k, which
-// is what the reference's CPU product gives bit for bit (a radix-2 butterfly does not).
+// Layout: the [rows, k] matrix is one flat array of 16-element groups and a THREAD owns a whole
+// group: 16 consecutive elements arrive as 128-bit loads (two for bf16/fp16, four for fp32), the
+// 16 outputs leave the same way, and nothing is exchanged between lanes.  Adjacent lanes read
+// adjacent 32- or 64-byte pieces, so a warp's accesses cover one contiguous run and every DRAM
+// sector is fetched once (the second load of a lane finds the other half of its sector in L1).
+// Every output is the left-to-right sum over k = 0..15 of x_k * (+-1/4) with compile-time signs:
+// the products are exact, so the result equals a row-times-matrix product accumulated in ascending
+// k, which is what the reference's CPU product gives bit for bit (a radix-2 butterfly does not).
 #include <type_traits>
 
 #include "common.cuh"
@@ -25,7 +27,7 @@ struct Quad<float> {
     v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
   }
   static __device__ __forceinline__ void store(float* p, const C v[4]) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));  // written once, read much later
   }
 };
 template <>
@@ -93,85 +95,63 @@ __device__ __forceinline__ void load_as_f32<__nv_bfloat16>(const __nv_bfloat16* 
 
 __device__ __forceinline__ float fma_c(float a, float b, float c) { return fmaf(a, b, c); }
 __device__ __forceinline__ double fma_c(double a, double b, double c) { return fma(a, b, c); }
-__device__ __forceinline__ float shfl_c(float v, int src) { return __shfl_sync(0xffffffffu, v, src); }
-__device__ __forceinline__ double shfl_c(double v, int src) {
-  return __shfl_sync(0xffffffffu, v, src);
-}
-
-// The four outputs j = 4*sub + jj of one group, given the lane's own quad `mine`.
-// Entry (k, j) of the matrix is (1/4) * (-1)^popcount(k & j); with k = 4*kh + kl the sign
-// splits into a compile-time part popcount(kl & jj) and a per-lane part popcount(kh & sub),
-// which is applied to the incoming quad by an exact negation.
-template <typename C>
-__device__ __forceinline__ void rotate_quad(const C mine[4], int lane, C out[4]) {
-  const int sub = lane & 3, base = lane & ~3;
-  C acc[4] = {C(0), C(0), C(0), C(0)};
-#pragma unroll
-  for (int kh = 0; kh < 4; ++kh) {
-    const bool neg = __popc(kh & sub) & 1;
-    C in[4];
-#pragma unroll
-    for (int kl = 0; kl < 4; ++kl) {
-      C v = shfl_c(mine[kl], base + kh);
-      in[kl] = neg ? -v : v;
-    }
-#pragma unroll
-    for (int kl = 0; kl < 4; ++kl) {
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const C h = (__popc(kl & jj) & 1) ? C(-0.25) : C(0.25);
-        acc[jj] = fma_c(in[kl], h, acc[jj]);
-      }
-    }
-  }
-#pragma unroll
-  for (int jj = 0; jj < 4; ++jj) out[jj] = acc[jj];
-}
 
 // Tin == Tout (C = compute type of the pair) or Tin half/bf16 with Tout float.
-// A lane takes UN quads per trip and issues all their loads before the first shuffle, so that
-// enough bytes are in flight per SM to cover the latency of HBM (one 8- or 16-byte load per lane
-// at a time left the kernel at about half of the copy bandwidth).
-constexpr int ROT_UN = 4;
-
 template <typename Tin, typename Tout, bool kSameType>
 __global__ void __launch_bounds__(256)
 rotate_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, const uint8_t* __restrict__ flags,
-              const float* __restrict__ col_scale, int64_t quads, int groups_per_row) {
+              const float* __restrict__ col_scale, int64_t groups, int groups_per_row) {
   using C = typename std::conditional<kSameType, typename Quad<Tin>::C, float>::type;
-  const int lane = threadIdx.x & 31;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  // every lane of a warp runs the same number of iterations: quads is rounded up to a warp
-  const int64_t limit = (quads + 31) & ~(int64_t)31;
-  for (int64_t q0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q0 < limit; q0 += stride * ROT_UN) {
-    C mine[ROT_UN][4];
-    int64_t qq[ROT_UN];
-    bool live[ROT_UN], on[ROT_UN];  // on: the whole warp has this trip
+  for (int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < groups; gid += stride) {
+    C v[16];
+    if constexpr (!kSameType && sizeof(Tin) == 2) {  // 32 bytes: two 128-bit loads, unpacked from registers
+      const uint4 lo = *reinterpret_cast<const uint4*>(x + gid * 16);
+      const uint4 hi = *reinterpret_cast<const uint4*>(x + gid * 16 + 8);
+      const uint32_t raw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-    for (int u = 0; u < ROT_UN; ++u) {
-      const int64_t q = q0 + u * stride;
-      on[u] = q < limit;
-      live[u] = q < quads;
-      qq[u] = live[u] ? q : quads - 1;
-      if (on[u]) {
-        if constexpr (kSameType) Quad<Tin>::load(x + qq[u] * 4, mine[u]);
-        else load_as_f32<Tin>(x + qq[u] * 4, mine[u]);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < ROT_UN; ++u) {
-      if (!on[u]) continue;
-      const int g = (int)((qq[u] >> 2) % groups_per_row);
-      const bool flagged = flags[g] != 0;
-      if constexpr (!kSameType || sizeof(Tin) == 4) {
-        if (col_scale != nullptr) {
-          float4 s = *reinterpret_cast<const float4*>(col_scale + (int64_t)g * 16 + (lane & 3) * 4);
-          mine[u][0] *= s.x, mine[u][1] *= s.y, mine[u][2] *= s.z, mine[u][3] *= s.w;
+      for (int i = 0; i < 8; ++i) {
+        if constexpr (std::is_same<Tin, __nv_bfloat16>::value) {
+          v[2 * i] = __uint_as_float(raw[i] << 16), v[2 * i + 1] = __uint_as_float(raw[i] & 0xffff0000u);
+        } else {
+          const __half2 h = *reinterpret_cast<const __half2*>(&raw[i]);
+          v[2 * i] = __low2float(h), v[2 * i + 1] = __high2float(h);
         }
       }
-      C out[4];
-      rotate_quad<C>(mine[u], lane, out);
-      if (live[u]) Quad<Tout>::store(y + qq[u] * 4, flagged ? out : mine[u]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if constexpr (kSameType) Quad<Tin>::load(x + gid * 16 + q * 4, &v[q * 4]);
+        else load_as_f32<Tin>(x + gid * 16 + q * 4, &v[q * 4]);
+      }
+    }
+    const int g = (int)(gid % groups_per_row);
+    if constexpr (!kSameType || sizeof(Tin) == 4) {
+      if (col_scale != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 sc = __ldg(reinterpret_cast<const float4*>(col_scale + (int64_t)g * 16 + q * 4));
+          v[q * 4] *= sc.x, v[q * 4 + 1] *= sc.y, v[q * 4 + 2] *= sc.z, v[q * 4 + 3] *= sc.w;
+        }
+      }
+    }
+    if (__ldg(flags + g) != 0) {
+      // All 16 outputs of the group, each the k-ascending sum.  (Measured alternatives, all slower on
+      // the 11008 x 4096 bf16 -> fp32 case at 72 us: four lanes per group with shuffles 82 us; two
+      // groups per trip, 96 registers, 81 us; four outputs at a time capped at 40 registers 85 us.)
+      C out[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        C acc = C(0);
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) acc = fma_c(v[kk], (__popc(kk & j) & 1) ? C(-0.25) : C(0.25), acc);
+        out[j] = acc;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) Quad<Tout>::store(y + gid * 16 + q * 4, &out[q * 4]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) Quad<Tout>::store(y + gid * 16 + q * 4, &v[q * 4]);
     }
   }
 }
@@ -179,13 +159,13 @@ rotate_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, const uint8_t* __
 template <typename Tin, typename Tout, bool kSame>
 int launch(const void* x, void* y, const uint8_t* flags, const float* scale, int64_t rows, int64_t k,
            cudaStream_t stream) {
-  const int64_t quads = rows * k / 4;
-  if (quads == 0) return HI2_OK;
-  int64_t blocks = ceil_div(quads, 256);
+  const int64_t groups = rows * k / 16;
+  if (groups == 0) return HI2_OK;
+  int64_t blocks = ceil_div(groups, 256);
   const int64_t cap = 148 * 8 * 4;  // a few waves of resident blocks; the loop strides the rest
   if (blocks > cap) blocks = cap;
   rotate_kernel<Tin, Tout, kSame><<<(unsigned)blocks, 256, 0, stream>>>(
-      static_cast<const Tin*>(x), static_cast<Tout*>(y), flags, scale, quads, (int)(k / 16));
+      static_cast<const Tin*>(x), static_cast<Tout*>(y), flags, scale, groups, (int)(k / 16));
   return check_launch("rotate_groups");
 }
 

@@ -13,42 +13,72 @@ namespace {
 constexpr int TS = 64;      // tile side
 constexpr int LD = TS + 1;  // odd stride: rows and columns of a tile are both conflict-free
 
-__device__ __forceinline__ float h16(int i, int j) { return (__popc(i & j) & 1) ? -0.25f : 0.25f; }
+// y = H x for the normalised order-16 Sylvester matrix, in place: four butterfly stages (64
+// additions) and one exact scaling by 1/4 instead of 256 multiply-adds.  The basis change is
+// compared with the reference by tolerance (its own product runs in a BLAS), so the order of the
+// additions is free here; the weight rotation, which must match bit for bit, keeps the plain sum.
+__device__ __forceinline__ void wht16(float (&v)[16]) {
+#pragma unroll
+  for (int h = 1; h < 16; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if ((i & h) == 0) {
+        const float a = v[i], b = v[i + h];
+        v[i] = a + b;
+        v[i + h] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] *= 0.25f;
+}
 
-// Load tile (tr, tc) of sigma/denom scaled by inv[row]*inv[col], then M . M^T on flagged groups.
-__device__ void transform_tile(float (*tile)[LD], const float* __restrict__ sigma, float denom,
+// The thread's four quads of tile (tr, tc) of sigma: 128-bit loads, all in flight at once (a scalar
+// load per trip of a rolled loop left a few KB in flight per SM and the kernel at a fifth of the
+// copy bandwidth).  k is a multiple of 16, so a quad never straddles the edge.
+__device__ __forceinline__ void load_tile(float4 (&quad)[4], const float* __restrict__ sigma, int64_t k,
+                                          int64_t tr, int64_t tc) {
+  const int tid = threadIdx.x;
+  const int64_t r0 = tr * TS, c0 = tc * TS;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int idx = tid + q * 256, i = idx >> 4, j = (idx & 15) * 4;
+    const int64_t gr = r0 + i, gc = c0 + j;
+    quad[q] = (gr < k && gc < k) ? __ldg(reinterpret_cast<const float4*>(sigma + gr * k + gc))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// Tile (tr, tc) of sigma/denom (already in `quad`) scaled by inv[row]*inv[col], then M . M^T on
+// flagged groups.
+__device__ void transform_tile(float (*tile)[LD], const float4 (&quad)[4], float denom,
                                const float* __restrict__ inv_s, const uint8_t* __restrict__ had,
                                int64_t k, int64_t tr, int64_t tc) {
   const int tid = threadIdx.x;
   const int64_t r0 = tr * TS, c0 = tc * TS;
-  for (int idx = tid; idx < TS * TS; idx += 256) {
-    const int i = idx / TS, j = idx % TS;
-    const int64_t gr = r0 + i, gc = c0 + j;
-    float v = 0.0f;
-    if (gr < k && gc < k) {
-      v = sigma[gr * k + gc];
-      if (denom != 1.0f) v = __fdiv_rn(v, denom);
-      if (inv_s != nullptr) v = (v * inv_s[i]) * inv_s[TS + j];
+  const Recip rc = make_recip(denom);  // sigma / n with the IEEE quotient, as the reference's mean()
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int idx = tid + q * 256, i = idx >> 4, j = (idx & 15) * 4;
+    float v[4] = {quad[q].x, quad[q].y, quad[q].z, quad[q].w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      if (denom != 1.0f) v[t] = div_by(v[t], denom, rc);
+      if (inv_s != nullptr) v[t] = (v[t] * inv_s[i]) * inv_s[TS + j + t];
+      tile[i][j + t] = v[t];
     }
-    tile[i][j] = v;
   }
   __syncthreads();
   {  // left product: thread = (column c, row group gi)
     const int c = tid & 63, gi = tid >> 6;
     const int64_t grp = (r0 >> 4) + gi;
     if (grp * 16 < k && had[grp]) {
-      float in[16], out[16];
+      float v[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) in[j] = tile[gi * 16 + j][c];
+      for (int j = 0; j < 16; ++j) v[j] = tile[gi * 16 + j][c];
+      wht16(v);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float acc = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc = fmaf(h16(i, j), in[j], acc);
-        out[i] = acc;
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) tile[gi * 16 + i][c] = out[i];
+      for (int i = 0; i < 16; ++i) tile[gi * 16 + i][c] = v[i];
     }
   }
   __syncthreads();
@@ -56,18 +86,12 @@ __device__ void transform_tile(float (*tile)[LD], const float* __restrict__ sigm
     const int i = tid & 63, gj = tid >> 6;
     const int64_t grp = (c0 >> 4) + gj;
     if (grp * 16 < k && had[grp]) {
-      float in[16], out[16];
+      float v[16];
 #pragma unroll
-      for (int q = 0; q < 16; ++q) in[q] = tile[i][gj * 16 + q];
+      for (int q = 0; q < 16; ++q) v[q] = tile[i][gj * 16 + q];
+      wht16(v);
 #pragma unroll
-      for (int l = 0; l < 16; ++l) {
-        float acc = 0.0f;
-#pragma unroll
-        for (int q = 0; q < 16; ++q) acc = fmaf(in[q], h16(l, q), acc);
-        out[l] = acc;
-      }
-#pragma unroll
-      for (int l = 0; l < 16; ++l) tile[i][gj * 16 + l] = out[l];
+      for (int l = 0; l < 16; ++l) tile[i][gj * 16 + l] = v[l];
     }
   }
   __syncthreads();
@@ -91,26 +115,37 @@ transform_sigma_kernel(const float* __restrict__ sigma, float denom,
     inv_rc[tid] = v;
   }
   __syncthreads();
+  // both tiles' loads go out before anything is computed: 128 bytes in flight per thread
+  float4 quad_p[4], quad_q[4];
+  load_tile(quad_p, sigma, k, bi, bj);
+  if (bi != bj) load_tile(quad_q, sigma, k, bj, bi);
   // tile (bi, bj): rows scaled by inv[bi-range], columns by inv[bj-range]
-  transform_tile(P, sigma, denom, scaled ? inv_rc : nullptr, had, k, bi, bj);
+  transform_tile(P, quad_p, denom, scaled ? inv_rc : nullptr, had, k, bi, bj);
   if (bi != bj) {
     // tile (bj, bi) wants the two halves of inv_rc swapped
     __shared__ float inv_cr[2 * TS];
     if (scaled && tid < 2 * TS) inv_cr[tid] = inv_rc[(tid + TS) % (2 * TS)];
     __syncthreads();
-    transform_tile(Q, sigma, denom, scaled ? inv_cr : nullptr, had, k, bj, bi);
+    transform_tile(Q, quad_q, denom, scaled ? inv_cr : nullptr, had, k, bj, bi);
   }
   const int64_t r0 = bi * TS, c0 = bj * TS;
-  for (int idx = tid; idx < TS * TS; idx += 256) {
-    const int i = idx / TS, j = idx % TS;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int idx = tid + q * 256, i = idx >> 4, j = (idx & 15) * 4;
     // upper tile (bi, bj), element (i, j) = 0.5 * (P[i][j] + Q[j][i])
     if (r0 + i < k && c0 + j < k) {
-      const float other = (bi == bj) ? P[j][i] : Q[j][i];
-      hs[(r0 + i) * k + c0 + j] = 0.5f * (P[i][j] + other);
+      float o[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) o[t] = 0.5f * (P[i][j + t] + ((bi == bj) ? P[j + t][i] : Q[j + t][i]));
+      *reinterpret_cast<float4*>(hs + (r0 + i) * k + c0 + j) = make_float4(o[0], o[1], o[2], o[3]);
     }
     // lower tile (bj, bi), element (i, j) = 0.5 * (Q[i][j] + P[j][i]): the same sum, mirrored
-    if (bi != bj && c0 + i < k && r0 + j < k)
-      hs[(c0 + i) * k + r0 + j] = 0.5f * (P[j][i] + Q[i][j]);
+    if (bi != bj && c0 + i < k && r0 + j < k) {
+      float o[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) o[t] = 0.5f * (P[j + t][i] + Q[i][j + t]);
+      *reinterpret_cast<float4*>(hs + (c0 + i) * k + r0 + j) = make_float4(o[0], o[1], o[2], o[3]);
+    }
   }
   if (bi == bj && diag != nullptr && tid < TS && r0 + tid < k)
     diag[r0 + tid] = 0.5f * (P[tid][tid] + P[tid][tid]);

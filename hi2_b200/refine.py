@@ -1,8 +1,9 @@
 """Local code refinement after GPTQ on B200 (interface of hi2/refine.py:24-162).
 
 A sweep visits the columns in blocks of 128: one launch of the block kernel decides every column
-of the block for every row (csrc/refine.cu), one fp32 FMA product brings ``g = e Hs`` up to date
-for the other columns.  Ladders are never touched.
+of the block for every row (csrc/refine.cu), one fp32-grade product (three TF32 tcgen05 products,
+csrc/lazy_tc.cu; fp32 FMA for narrow inputs and 256-level rows) brings ``g = e Hs`` up to date for
+the other columns.  Ladders are never touched.
 """
 
 from __future__ import annotations
@@ -13,6 +14,7 @@ from . import _lib, refine_kernel
 from .format import decode_params
 
 BLOCK_COLUMNS = 128
+TC_MIN_K = 512  # inputs at least this wide take the tensor-core products
 
 
 @torch.no_grad()
@@ -44,7 +46,16 @@ def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
     hs = hs.float().contiguous()
     e = ((lo_x + c * st_x).half().float() - w.float()).contiguous()
     g = torch.empty(n_rows, k, dtype=torch.float32, device=dev)
-    refine_kernel.gemm(e, hs, g)
+    # The two products of a sweep, g = e Hs and g += dw Hs[b0:b1], run on the tensor cores as three
+    # TF32 products (fp32-grade; Hs is symmetric, so its rows are the K-major right operand as they
+    # lie).  Rows with 256 levels and narrow inputs keep the fp32 FMA product, as in the GPTQ path.
+    use_tc = k >= TC_MIN_K and k % 4 == 0 and bool((top <= 15).all())
+    if use_tc:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        hs_split = refine_kernel.split_tf32(hs)
+        refine_kernel.gemm_tc(refine_kernel.split_tf32(e), hs_split, g, status)
+    else:
+        refine_kernel.gemm(e, hs, g)
     del e
     for _ in range(passes):
         start = c.clone()
@@ -53,9 +64,14 @@ def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
             gb = g[:, b0:b1].contiguous()
             dw_block = torch.empty(n_rows, b1 - b0, dtype=torch.float32, device=dev)
             refine_kernel.refine_block(gb, c, lo_x, st_x, top, hs, b0, b1 - b0, dw_block)
-            refine_kernel.gemm(dw_block, hs[b0:b1], g, alpha=1.0, beta=1.0)
+            if use_tc and (b1 - b0) % 4 == 0:
+                refine_kernel.gemm_tc(refine_kernel.split_tf32(dw_block), hs_split[:, :, b0:b1], g, status, accumulate=True)
+            else:
+                refine_kernel.gemm(dw_block, hs[b0:b1], g, alpha=1.0, beta=1.0)
         if bool((c == start).all()):
             break
+    if use_tc and int(status.item()):
+        raise RuntimeError("refine: a bounded device-side wait ran out in a tensor-core product")
     return c
 
 

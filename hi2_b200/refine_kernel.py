@@ -58,3 +58,31 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, alpha=1.0, beta=0.
         "hi2_gemm_f32", 0, 0, m, n, kk, float(alpha), _lib.ptr(a), a.stride(0), _lib.ptr(b),
         b.stride(0), float(beta), _lib.ptr(out), out.stride(0), _lib.stream(dev),
     )
+
+
+def split_tf32(x: torch.Tensor) -> torch.Tensor:
+    """``[2, *x.shape]``: the TF32 parts ``hi = tf32(x)``, ``lo = tf32(x - hi)`` of a contiguous fp32
+    tensor, the operand form of :func:`gemm_tc`."""
+    dev = _lib.need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.numel() % 4:
+        raise ValueError("split_tf32: a contiguous fp32 tensor with a multiple of 4 elements")
+    out = torch.empty(2, *x.shape, dtype=torch.float32, device=dev)
+    _lib.call("hi2_split_tf32", _lib.ptr(x), _lib.ptr(out[0]), _lib.ptr(out[1]), x.numel(), _lib.stream(dev))
+    return out
+
+
+def gemm_tc(a_split: torch.Tensor, bt_split: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+            accumulate: bool = False) -> None:
+    """``out (+)= a @ bt^T`` with fp32-grade accuracy on the tensor cores; ``a_split [2, m, kk]`` and
+    ``bt_split [2, n, kk]`` are TF32 parts (views with unit column stride are fine, both parts of an
+    operand with the same row stride)."""
+    dev = _lib.need_cuda(a_split, bt_split, out, status)
+    _, m, kk = a_split.shape
+    n = bt_split.shape[1]
+    if bt_split.shape[2] != kk or out.shape != (m, n) or a_split.stride(2) != 1 or bt_split.stride(2) != 1:
+        raise ValueError("gemm_tc: shape mismatch")
+    _lib.call(
+        "hi2_gemm_tf32x3", m, n, kk, _lib.ptr(a_split[0]), _lib.ptr(a_split[1]), a_split.stride(1),
+        _lib.ptr(bt_split[0]), _lib.ptr(bt_split[1]), bt_split.stride(1), _lib.ptr(out), out.stride(0),
+        1 if accumulate else 0, _lib.ptr(status), _lib.stream(dev),
+    )

@@ -143,6 +143,16 @@ int hi2_split_tf32(const float* x, float* hi, float* lo, int64_t n, void* stream
 int hi2_split_tf32_transposed(const float* x, float* hi, float* lo, int64_t rows, int64_t cols,
                               void* stream);
 
+/* c[m, n] (ldc) = or += a . bt^T in fp32-grade arithmetic on the tensor cores: both operands as
+ * their TF32 parts from hi2_split_tf32 (a [m, kk] with leading dimension lda, bt [n, kk] with ldb,
+ * both K-major), three tcgen05 TF32 products per tile accumulated in windows of 64 values of k.
+ * Replaces the fp32 library products of the refinement, g = e @ Hs and g += dw @ Hs[b0:b1]
+ * (hi2/refine.py:64, :83, :103; Hs is symmetric, so its rows serve as bt).  *status (device int,
+ * caller zeroes it) is raised by a bounded wait that ran out. */
+int hi2_gemm_tf32x3(int64_t m, int64_t n, int64_t kk, const float* a_hi, const float* a_lo, int64_t lda,
+                    const float* bt_hi, const float* bt_lo, int64_t ldb, float* c, int64_t ldc, int accumulate,
+                    int32_t* status, void* stream);
+
 /* hi2/hessian.py:331-338 (_finish): sse[r] = sum_j d[j] * (fp16(lo + code*step) - w[r, j])^2
  * with the decoded ladders lo/st [n_rows, ldp] of block size `block`. */
 int hi2_ladder_sse(const uint8_t* codes, const float* w, int64_t ldw, const float* d,

@@ -3,8 +3,7 @@ Linear with 4 outlier columns, 2048 calibration tokens, six candidates, 3.0 bpw)
 the oracle's own inputs, then end to end; and one wide matrix (K = 11008, a row sample) through
 tables and GPTQ.  The oracle needs about a minute of host time per module.
 
-Bars (the contract's): rotation, allocation and packing bit-exact; codes >= 99.9 % (asserted at
-99.99 %); parameter bytes and row constants (the scales) equal on every row; Hessian-weighted
+Bars (the contract's): rotation, allocation and packing bit-exact; codes >= 99.9 %; parameter bytes and row constants (the scales) equal on every row; Hessian-weighted
 error within 1 %.  The agreement per (nbits, block) is printed as a table."""
 
 import pytest
@@ -108,7 +107,9 @@ def test_factor_gptq_and_packing_given_oracle_inputs(cfg1, capsys):
         e_g = weighted_error(ref["wt"][rows], ref["hs"], got.codes, got.params, got.consts, b)
         e_o = weighted_error(ref["wt"][rows], ref["hs"], want.codes, want.params, want.consts, b)
         lines.append(f"INT{nb}/B{b:<3}   {rows.numel():5d}  {lad.float().mean().item():8.6f}  {codes:8.6f}   {e_g / e_o:.6f}")
-        assert bool(lad.all()) and codes >= 0.9999 and abs(e_g - e_o) <= 0.01 * e_o, lines[-1]
+        # the contract's bar; measured 99.98-100 % (a code the 3 x TF32 trailing update rounds the other
+        # way changes the rest of its 4096-column row)
+        assert bool(lad.all()) and codes >= 0.999 and abs(e_g - e_o) <= 0.01 * e_o, lines[-1]
         pieces.append((rows.to(DEV), got.codes, got.params, got.consts, nb, b))
     # with the GPU's own factor (another fp32 rounding of an ill-conditioned inverse, see above) the
     # codes are no longer "identical inputs"; what must hold is the error bar

@@ -122,3 +122,30 @@ def test_refine_block_entry_point():
     assert torch.equal(c_new.cpu(), cc)
     assert torch.equal(dwb.cpu(), moved)
     assert torch.equal(c_new[:, :b0], c[:, :b0])
+
+
+def test_refine_with_tensor_core_products():
+    """K = 1024: the sweep's products g = e Hs and g += dw Hs[b0:b1] run as three TF32 tcgen05
+    products; codes against the oracle's fp32 column loop, and the general product entry point
+    against an fp64 product."""
+    from hi2_b200 import refine_kernel
+    from hi2_b200.refine import refine_groups
+
+    groups, hs = _groups(23, k=1024, rows=(150, 70))
+    want = po.refine_groups(groups, hs, 2)
+    got = refine_groups(_to_dev(groups), hs.to(DEV), 2)
+    for g, w_ in zip(got, want):
+        assert agreement(g, w_) >= 0.999, agreement(g, w_)
+    gen_ = torch.Generator().manual_seed(5)
+    a = torch.randn(333, 1024, generator=gen_)
+    b = torch.randn(517, 1024, generator=gen_)
+    out = torch.full((333, 520), 7.0, device=DEV)  # a view with a wider leading dimension
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    view = out[:, :517]
+    refine_kernel.gemm_tc(refine_kernel.split_tf32(a.to(DEV)), refine_kernel.split_tf32(b.to(DEV)), view, status)
+    ref = a.double() @ b.double().T
+    assert int(status.item()) == 0 and bool((out[:, 517:] == 7.0).all())
+    assert ((view.double().cpu() - ref).abs().max() / ref.abs().max()).item() < 3e-6
+    refine_kernel.gemm_tc(refine_kernel.split_tf32(a.to(DEV)), refine_kernel.split_tf32(b.to(DEV)), view, status,
+                          accumulate=True)
+    assert ((view.double().cpu() - 2 * ref).abs().max() / ref.abs().max()).item() < 6e-6
