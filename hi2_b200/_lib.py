@@ -31,6 +31,7 @@ SIGNATURES = {
     "hi2_rotate_groups": (_I, [_P, _I, _P, _I, _P, _P, _L, _L, _P]),
     "hi2_pack_codes": (_I, [_P, _P, _L, _L, _I, _P, _P]),
     "hi2_assemble_piece": (_I, [_P, _L, _P, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "hi2_dequantize": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _I, _P, _I, _P, _P]),
     "hi2_ladder_grid": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _P, _P, _P, _P]),
     "hi2_fit_ladder": (_I, [_P, _L, _P, _P, _I, _I, _I, _L, _L, _I, _P, _P, _P]),
     "hi2_quantize_rows": (

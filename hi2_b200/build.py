@@ -24,6 +24,7 @@ SOURCES = [
     "common.cu",
     "rotate.cu",
     "pack.cu",
+    "dequant.cu",
     "ladder.cu",
     "gptq.cu",
     "lazy_tc.cu",

@@ -191,3 +191,47 @@ def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=N
         shape=(r, k),
         col_scale=col_scale.cpu() if (to_host and col_scale is not None and col_scale.is_cuda) else col_scale,
     )
+
+
+# ---- the inverse path ---------------------------------------------------------------------------
+def _dequantize(t: HI2Tensor, device, original: bool, dtype: torch.dtype) -> torch.Tensor:
+    if dtype not in (torch.float64, torch.float32):
+        raise ValueError("dequantize: dtype must be float64 or float32")
+    dev = torch.device(device) if device is not None else (
+        t.codes.device if t.codes.is_cuda else torch.device("cuda", torch.cuda.current_device()))
+    if dev.type != "cuda":
+        raise RuntimeError("hi2_b200 runs on CUDA devices only; there is no CPU path")
+    r, k = t.shape
+    out = torch.empty(r, k, dtype=dtype, device=dev)
+    if r == 0:
+        return out
+    codes = _lib.upload(t.codes, dev, torch.int32)
+    code_off = _lib.upload(t.code_off, dev, torch.int32)
+    params = _lib.upload(t.blk_params, dev, torch.uint8)
+    param_off = _lib.upload(t.param_off, dev, torch.int32)
+    consts = _lib.upload(t.row_consts, dev, torch.float16)
+    nbits = _lib.upload(t.row_nbits, dev, torch.uint8)
+    block = _lib.upload(t.row_block, dev, torch.uint8)
+    had = _lib.upload(t.had, dev, torch.uint8)
+    cs = None if t.col_scale is None else _lib.upload(t.col_scale, dev, torch.float16)
+    bad = torch.zeros(1, dtype=torch.int32, device=dev)
+    _lib.call(
+        "hi2_dequantize", _lib.ptr(codes), _lib.ptr(code_off), _lib.ptr(params), _lib.ptr(param_off),
+        _lib.ptr(consts), _lib.ptr(nbits), _lib.ptr(block), _lib.ptr(had), _lib.ptr(cs), r, k, 1 if original else 0,
+        _lib.ptr(out), _lib.DTYPES[dtype], _lib.ptr(bad), _lib.stream(dev),
+    )
+    if int(bad.item()):
+        raise ValueError("dequantize: a row's code width or block size is not one of the format's")
+    return out
+
+
+def dequantize_stored(t: HI2Tensor, device=None, dtype: torch.dtype = torch.float64) -> torch.Tensor:
+    """fp16 reconstruction in the stored (rotated, smoothed) basis as ``[R, K]`` on the device
+    (hi2/format.py:195-228).  Every step is exact, so the float64 result equals the reference's."""
+    return _dequantize(t, device, False, dtype)
+
+
+def dequantize(t: HI2Tensor, device=None, dtype: torch.dtype = torch.float64) -> torch.Tensor:
+    """Reconstruction in the original basis: the rotation is its own inverse and the smoothing
+    vector is divided back out (hi2/format.py:231-239)."""
+    return _dequantize(t, device, True, dtype)

@@ -70,6 +70,17 @@ int hi2_assemble_piece(const int64_t* rows, int64_t n_rows, const uint8_t* codes
                        int32_t* out_codes, uint8_t* out_params, uint16_t* out_consts,
                        int32_t* bad, void* stream);
 
+/* hi2/format.py:195-239 dequantize_stored / dequantize: the fp16 reconstruction of every weight of
+ * a packed tensor (the flat buffers of hi2_assemble_piece), as fp64 (the reference's type; equal
+ * bit for bit on any device, every step being exact or correctly rounded) or fp32 [rows, k].
+ * original_basis = 0: the stored basis; 1: rotated back (had [k/16]) and divided by the smoothing
+ * vector (col_scale fp16 [k], may be null).  *bad (device int, caller zeroes it) is raised by a row
+ * whose code width or block size is not one of the format's. */
+int hi2_dequantize(const int32_t* codes, const int32_t* code_off, const uint8_t* blk_params,
+                   const int32_t* param_off, const uint16_t* row_consts, const uint8_t* row_nbits,
+                   const uint8_t* row_block, const uint8_t* had, const uint16_t* col_scale, int64_t rows,
+                   int64_t k, int original_basis, void* out, int out_dtype, int32_t* bad, void* stream);
+
 /* ---- ladder search -------------------------------------------------------------------------
  * hi2/ladder_kernel.py:44-101 ladder_grid: wb [n_rows, nb, block] fp32, db [nb, block],
  * grid_host[g] (host floats, g <= 8), n = number of codes.  Outputs [n_rows, nb] fp32. */

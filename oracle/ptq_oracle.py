@@ -29,6 +29,7 @@ Reference locations (paths inside the hi2 project):
   hi2/format.py:73-184   packing / layout    -> pack_words, unpack_words, assemble_flat
   hi2/allocate.py:79-261 allocation          -> allocate_rows
   hi2/calibrate.py:114-209 transform choice  -> pick_rotation, transform_cost, pick_transform
+  hi2/format.py:195-239  inverse path        -> reconstruct_flat
 """
 
 from __future__ import annotations
@@ -597,6 +598,25 @@ def assemble_flat(pieces, row_nbits, row_block, had, k: int, col_scale=None) -> 
         (r, k),
         col_scale,
     )
+
+
+def reconstruct_flat(flat, original: bool = True) -> torch.Tensor:
+    """fp64 ``[R, K]`` reconstruction of a :class:`Flat` tensor, row by row: stored basis, or
+    (``original``) rotated back and divided by the smoothing vector."""
+    r, k = flat.shape
+    out = torch.zeros(r, k, dtype=F64)
+    for row in range(r):
+        nb, bl = int(flat.row_nbits[row]), int(flat.row_block[row])
+        codes = unpack_words(flat.codes[flat.code_off[row] : flat.code_off[row + 1]], nb)
+        p = flat.blk_params[2 * flat.param_off[row] : 2 * flat.param_off[row + 1]].reshape(-1, 2)
+        c = flat.row_consts[row]
+        lo, step = decode_ladders(p[:, 0], p[:, 1], c[0], c[1], c[2])
+        out[row] = reconstruct(codes.reshape(-1, bl), lo, step).double().reshape(-1)
+    if original:
+        out = rotate_groups(out, flat.had)
+        if flat.col_scale is not None:
+            out = out / flat.col_scale.double()
+    return out
 
 
 # --------------------------------------------------------------------------- allocation

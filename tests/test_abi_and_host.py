@@ -200,3 +200,25 @@ def test_host_side_helpers_need_no_device():
         HessianStats(8, "cpu", out=torch.zeros(8, 8, dtype=torch.float64))
     with pytest.raises(RuntimeError):
         h.update(torch.zeros(4, 8))  # no CPU path
+
+
+def test_checkpoint_names_and_batches():
+    """hi2/checkpoint.py:142-157 tensor names and :234-247 batching under a byte budget (host only)."""
+    from types import SimpleNamespace
+
+    from hi2_b200.checkpoint import batches, from_tensors, to_tensors
+    from hi2_b200.format import FIELDS, HI2Tensor
+
+    t = HI2Tensor(codes=torch.arange(8, dtype=torch.int32), code_off=torch.tensor([0, 4, 8], dtype=torch.int32),
+                  blk_params=torch.zeros(16, dtype=torch.uint8), param_off=torch.tensor([0, 4, 8], dtype=torch.int32),
+                  row_consts=torch.zeros(2, 3, dtype=torch.float16), row_nbits=torch.tensor([2, 2], dtype=torch.uint8),
+                  row_block=torch.tensor([16, 16], dtype=torch.uint8), had=torch.ones(4, dtype=torch.uint8), shape=(2, 64),
+                  col_scale=torch.ones(64, dtype=torch.float16))
+    d = to_tensors(t, "model.layers.0.mlp.up_proj")
+    assert set(d) == {f"model.layers.0.mlp.up_proj.hi2_{f}" for f in FIELDS} | {"model.layers.0.mlp.up_proj.hi2_col_scale"}
+    back = from_tensors(d, "model.layers.0.mlp.up_proj")
+    assert back.shape == (2, 64) and torch.equal(back.codes, t.codes) and back.col_scale is not None
+    tables = {f"t{i}": SimpleNamespace(shape=(100, 256)) for i in range(5)}
+    one = 4 * (256 * 256 + 3 * 100 * 256)
+    assert [len(g) for g in batches(list(tables), tables, 2 * one)] == [2, 2, 1]
+    assert [len(g) for g in batches(list(tables), tables, 1)] == [1] * 5

@@ -224,3 +224,13 @@ def test_transform_choice_matches_reference():
         for alpha, want in c["costs"].items():
             s_a, had_a = po._transform_for(ws, gm, c["mode"], alpha)
             assert abs(po.transform_cost(ws, gm, s_a, had_a) - want) <= 1e-6 * want
+
+
+def test_inverse_path_matches_reference():
+    """Reconstruction of a mixed-row packed tensor against hi2's own dequantize / dequantize_stored
+    (tests/golden/dequant_golden.pt): every step is exact in fp64, so the results are equal."""
+    cases = torch.load(ROOT / "tests" / "golden" / "dequant_golden.pt", weights_only=False)
+    for case in cases.values():
+        flat = po.Flat(**case["fields"], shape=case["shape"], col_scale=case["col_scale"])
+        assert torch.equal(po.reconstruct_flat(flat, original=False), case["stored"])
+        assert torch.equal(po.reconstruct_flat(flat, original=True), case["original"])
