@@ -276,7 +276,7 @@ constexpr int ROW_UN = 4;  // quads a lane loads before it computes
 // neither on five of their six passes, and the pass is bound by instruction issue (73 % of the
 // issue slots at a third of the copy bandwidth), so the instructions of unused outputs are compiled out.
 template <int B, bool CODES, bool ENERGY>
-__global__ void __launch_bounds__(ROW_THREADS)
+__global__ void __launch_bounds__(ROW_THREADS, 4)
 row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
            const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, float nmax,
            int64_t n_rows, int64_t k, uint8_t* __restrict__ params, uint16_t* __restrict__ consts,
