@@ -1039,6 +1039,19 @@ def mem_available_bytes() -> int:
     return 0
 
 
+def all_ranks_agree(flag: bool, world: int, device) -> bool:
+    """True only if ``flag`` holds on EVERY rank.  A per-rank decision that steers collectives (whether
+    the end-to-end leg runs: its steps reduce-scatter and gather) must be the same everywhere; free
+    host memory is read at slightly different moments by ranks that are pinning buffers meanwhile."""
+    if world == 1:
+        return bool(flag)
+    import torch.distributed as dist
+
+    t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
 def run_ours(args, cfg):
     import torch.distributed as dist
 
@@ -1088,7 +1101,8 @@ def run_ours(args, cfg):
     if args.no_e2e:
         e2e = {"value": None, "unit": "rows/s", "h2d_bytes_per_step": need * world, "d2h_bytes_per_step": 0,
                "note": "skipped (--no-e2e)"}
-    elif mem_available_bytes() > 3 * need * max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world))):
+    elif all_ranks_agree(mem_available_bytes() > 3 * need * max(1, int(os.environ.get("LOCAL_WORLD_SIZE", world))),
+                         world, device):
         job.pin_host_copies()
         job.step(from_host=True, to_host=True)  # warm-up of the copy path
         sync_all()

@@ -1,7 +1,7 @@
 """Make an unmodified hi2 checkout call the B200 kernels.
 
-hi2 binds ``hi2.hessian``, ``hi2.encode``, ``hi2.ladder_kernel``, ``hi2.gptq_kernel`` and
-``hi2.refine_kernel`` at import time (``from .encode import encode_rows`` in hi2/calibrate.py:17,
+hi2 binds ``hi2.hessian``, ``hi2.encode``, ``hi2.ladder_kernel``, ``hi2.gptq_kernel``,
+``hi2.refine_kernel`` (and ``hi2.refine``, ``hi2.stats``) at import time (``from .encode import encode_rows`` in hi2/calibrate.py:17,
 ``from . import ladder_kernel`` in hi2/encode.py:15, ...), so the replacements have to be in
 ``sys.modules`` under those names BEFORE ``hi2.calibrate`` / ``hi2.pipeline`` are imported:
 
@@ -18,7 +18,7 @@ from __future__ import annotations
 import importlib
 import sys
 
-REPLACED = ("hessian", "encode", "ladder_kernel", "gptq_kernel", "refine_kernel", "refine")
+REPLACED = ("hessian", "encode", "ladder_kernel", "gptq_kernel", "refine_kernel", "refine", "stats")
 PATCHED_FORMAT = ("fwht_groups", "pack_codes", "assemble")
 
 

@@ -222,3 +222,46 @@ def test_checkpoint_names_and_batches():
     one = 4 * (256 * 256 + 3 * 100 * 256)
     assert [len(g) for g in batches(list(tables), tables, 2 * one)] == [2, 2, 1]
     assert [len(g) for g in batches(list(tables), tables, 1)] == [1] * 5
+
+
+def test_install_wires_an_unmodified_hi2():
+    """With a hi2 checkout importable (the build container has one; elsewhere the test is skipped),
+    ``install()`` must put the replacements under hi2's module names BEFORE hi2.calibrate binds them,
+    so that hi2's own ``build_table`` ends up in THIS package's ``encode_rows`` - which, on a machine
+    without a GPU, refuses the CPU tensors it is given (there is no CPU path)."""
+    import importlib
+    import subprocess
+    import sys
+
+    ref = "/root/reference"
+    if not (ROOT.parent / "reference" / "hi2" / "calibrate.py").exists():
+        pytest.skip("no hi2 checkout beside the repository")
+    code = f"""
+import sys
+sys.path[:0] = [{str(ROOT)!r}, {ref!r}]
+import torch
+import hi2_b200.install as inst
+done = inst.install()
+assert "hi2.stats" in done and "hi2.format.assemble" in done
+import hi2.calibrate as cal, hi2.encode, hi2.hessian, hi2.stats, hi2.format
+import hi2_b200.encode, hi2_b200.hessian, hi2_b200.stats, hi2_b200.format
+assert hi2.encode is hi2_b200.encode and hi2.hessian is hi2_b200.hessian and hi2.stats is hi2_b200.stats
+assert cal.encode_rows is hi2_b200.encode.encode_rows and cal.ColumnStats is hi2_b200.stats.ColumnStats
+assert hi2.format.fwht_groups is hi2_b200.format.fwht_groups and cal.fwht_groups is hi2_b200.format.fwht_groups
+from hi2.executor import Executor
+try:
+    cal.build_table("w", torch.randn(8, 64), None, cal.Config(), Executor("cpu"))
+except RuntimeError as e:
+    assert "CUDA devices only" in str(e), e
+else:
+    raise SystemExit("hi2.calibrate.build_table did not reach the replaced kernels")
+try:
+    inst.install()
+except RuntimeError as e:
+    assert "before" in str(e)
+else:
+    raise SystemExit("a late install() was accepted")
+print("wired")
+"""
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "wired" in out.stdout, out.stdout + out.stderr
