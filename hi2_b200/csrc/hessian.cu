@@ -354,7 +354,10 @@ hessian_tc_kernel(const __grid_constant__ CUtensorMap map, const TcParams p) {
 // S[i][j] += sum over splits (ascending) of the item tiles, for i <= j; S[j][i] = S[i][j].
 __global__ void __launch_bounds__(256)
 hessian_reduce_kernel(const float* __restrict__ scratch, int splits, int tiles, int njb, int64_t k,
-                      float* __restrict__ s) {
+                      float* __restrict__ s, const int* __restrict__ status) {
+  // a product that gave up on a bounded wait left stale or partial tiles: S stays as it was and the
+  // caller sees the status word
+  if (*status != 0) return;
   const int64_t j = (int64_t)blockIdx.x * 256 + threadIdx.x;
   const int64_t i = blockIdx.y;
   if (j >= k || j < i) return;
@@ -466,7 +469,7 @@ int accumulate_tc(const void* x, int dtype, int64_t tokens, int64_t k, float* s,
   int rc = check_launch("hessian_accumulate (tcgen05)");
   if (rc != HI2_OK) return rc;
   dim3 rgrid((unsigned)ceil_div(k, 256), (unsigned)k);
-  hessian_reduce_kernel<<<rgrid, 256, 0, stream>>>(scratch, pl.splits, pl.tiles, pl.njb, k, s);
+  hessian_reduce_kernel<<<rgrid, 256, 0, stream>>>(scratch, pl.splits, pl.tiles, pl.njb, k, s, status);
   return check_launch("hessian_accumulate (reduce)");
 }
 
@@ -619,6 +622,7 @@ extern "C" int hi2_hessian_accumulate_noalloc(const void* x, int dtype, int64_t 
   int rc = check_launch("hessian_accumulate_noalloc (tcgen05)");
   if (rc != HI2_OK) return rc;
   dim3 rgrid((unsigned)ceil_div(k, 256), (unsigned)k);
-  hessian_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, pl.splits, pl.tiles, pl.njb, k, s);
+  hessian_reduce_kernel<<<rgrid, 256, 0, st>>>(tiles, pl.splits, pl.tiles, pl.njb, k, s,
+                                               reinterpret_cast<const int*>(status));
   return check_launch("hessian_accumulate_noalloc (reduce)");
 }

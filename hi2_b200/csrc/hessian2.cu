@@ -324,7 +324,10 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap map, const Params p) {
 // S[i][j] += sum over splits (ascending) of the item tiles, for i <= j; S[j][i] = S[i][j].
 __global__ void __launch_bounds__(256)
 pair_reduce_kernel(const float* __restrict__ scratch, int splits, int tiles, int nb, int64_t k,
-                   float* __restrict__ s) {
+                   float* __restrict__ s, const int* __restrict__ status) {
+  // a product that gave up on a bounded wait left stale or partial tiles: S stays as it was and the
+  // caller sees the status word
+  if (*status != 0) return;
   const int64_t j = (int64_t)blockIdx.x * 256 + threadIdx.x;
   const int64_t i = blockIdx.y;
   if (j >= k || j < i) return;
@@ -431,7 +434,7 @@ int accumulate_pair(const void* x, int dtype, int64_t tokens, int64_t k, float* 
   int rc = check_launch("hessian_accumulate (tcgen05 pair)");
   if (rc != HI2_OK) return rc;
   dim3 rgrid((unsigned)ceil_div(k, (int64_t)256), (unsigned)k);
-  pair_reduce_kernel<<<rgrid, 256, 0, stream>>>(scratch, pl.splits, pl.tiles, pl.nb, k, s);
+  pair_reduce_kernel<<<rgrid, 256, 0, stream>>>(scratch, pl.splits, pl.tiles, pl.nb, k, s, status);
   return check_launch("hessian_accumulate (reduce)");
 }
 

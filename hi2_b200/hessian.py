@@ -30,19 +30,34 @@ BLOCK_COLUMNS = 128  # lazy-update block of GPTQ
 ROW_ELEMS = 1 << 26  # rows per unit, as in the reference (results do not depend on it)
 BATCH_ELEMS = int(os.environ.get("HI2_BATCH_ELEMS", 1 << 27))
 
-_workspaces: dict = {}
+class _Scratch:
+    """Grow-only scratch buffers, one per (device, stream): a kernel's scratch is only ever touched
+    by work queued on the stream it was allocated for, so when a buffer is outgrown and dropped the
+    caching allocator (which hands a block back only to later work of the same stream) cannot give
+    it to anybody while its last user is still running, and two streams never share a buffer.  The
+    registry belongs to the process, not to a call, but holds nothing a caller could observe."""
+
+    def __init__(self):
+        self._buffers: dict = {}
+
+    def get(self, dev: torch.device, nbytes: int) -> torch.Tensor:
+        stream = torch.cuda.current_stream(dev)
+        key = (stream.device.index, stream.cuda_stream)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < nbytes:
+            self._buffers.pop(key, None)
+            del buf
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+            self._buffers[key] = buf
+        return buf
+
+
+_scratch = _Scratch()
 
 
 def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
-    """Grow-only scratch buffer of one device (uint8), shared by the kernels that need scratch."""
-    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
-    buf = _workspaces.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = None
-        _workspaces.pop(key, None)
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
-        _workspaces[key] = buf
-    return buf
+    """Scratch of at least ``nbytes`` for a kernel launched on the current stream of ``dev``."""
+    return _scratch.get(dev, nbytes)
 
 
 _side_streams: dict = {}

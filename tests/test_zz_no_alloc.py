@@ -70,3 +70,23 @@ def test_sizes_beyond_the_fixed_scratch_are_refused():
         _noalloc(torch.zeros(64, 512, dtype=torch.bfloat16, device=DEV), torch.zeros(512, 512, device=DEV), status)
     with pytest.raises(ValueError):
         _noalloc(torch.zeros(512, 512, device=DEV), torch.zeros(512, 512, device=DEV), status)
+
+
+def test_widest_input_of_the_fixed_scratch_and_the_first_one_beyond():
+    """K = 5632 fills the 512-tile array (506 upper-triangle tiles): with enough tokens for the
+    planner to want several token splits, the split count must be clamped to what the array holds and
+    the sum still be right; K = 5648 (the next multiple of 16) is refused."""
+    from hi2_b200.hessian import HessianStats
+
+    k, tokens = 5632, 40000
+    x = activations(tokens, k, 43, dtype=torch.bfloat16).to(DEV)
+    ref = HessianStats(k, DEV)
+    ref.update(x)
+    s = torch.zeros(k, k, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _noalloc(x, s, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert _norm_err(s, ref.S) < 1e-5 and torch.equal(s, s.T)
+    with pytest.raises(RuntimeError, match="fixed scratch"):
+        _noalloc(torch.zeros(256, 5648, dtype=torch.bfloat16, device=DEV), torch.zeros(5648, 5648, device=DEV), status)
