@@ -265,3 +265,47 @@ print("wired")
 """
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "wired" in out.stdout, out.stdout + out.stderr
+
+
+STALL_WORKER = """
+import os, sys, time, datetime
+sys.path.insert(0, os.environ["HI2_ROOT"])
+import torch
+import torch.distributed as dist
+from hi2_b200 import dist as hd
+rank, world, device = hd.init_from_env("cpu", timeout_s=4.0)
+s = torch.ones(8, 8)
+hd.reduce_second_moment(s, 3, 0, n_total=6)           # a step both ranks take
+if rank == 1:
+    time.sleep(30)                                     # a rank that stops answering between steps
+    sys.exit(0)
+t0 = time.time()
+try:
+    hd.reduce_second_moment(s, 3, 0, n_total=6)        # the survivor's next collective
+    dist.barrier()
+except Exception as e:                                 # the process-group timeout ends it with an error
+    print("collective failed after %.1f s: %s" % (time.time() - t0, type(e).__name__))
+    os._exit(7)
+print("no error")
+"""
+
+
+def test_a_stalled_rank_ends_the_others_collective_by_timeout(tmp_path):
+    """Failure detection without a GPU: one of two gloo ranks stops answering between steps; the
+    other's next collective must end with an error within the process-group timeout that
+    ``init_from_env(timeout_s=...)`` sets, not hang."""
+    import time
+
+    script = tmp_path / "stall.py"
+    script.write_text(STALL_WORKER)
+    env = dict(os.environ, HI2_ROOT=str(ROOT), MASTER_ADDR="127.0.0.1", MASTER_PORT="29641", WORLD_SIZE="2",
+               CUDA_VISIBLE_DEVICES="")
+    t0 = time.time()
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    out0 = procs[0].communicate(timeout=120)[0]
+    took = time.time() - t0
+    procs[1].kill()
+    procs[1].communicate()
+    assert procs[0].returncode == 7 and "collective failed" in out0, out0
+    assert took < 60, took

@@ -149,3 +149,31 @@ def test_refine_with_tensor_core_products():
     refine_kernel.gemm_tc(refine_kernel.split_tf32(a.to(DEV)), refine_kernel.split_tf32(b.to(DEV)), view, status,
                           accumulate=True)
     assert ((view.double().cpu() - 2 * ref).abs().max() / ref.abs().max()).item() < 6e-6
+
+
+def test_block_kernel_mappings_agree():
+    """The block entry point maps a lane to a row when the rows fill the SMs (>= 148 x 64) and a warp
+    to a row below that: both must give the same codes and the same dw, bit for bit."""
+    from hi2_b200 import refine_kernel
+
+    g_ = torch.Generator().manual_seed(9)
+    n, k, b0, length = 148 * 64 + 37, 256, 128, 128
+    x = torch.randn(1024, k, generator=g_)
+    hs = (x.T @ x / 1024).to(DEV).contiguous()
+    c = torch.randint(0, 4, (n, k), generator=g_).float().to(DEV)
+    lo = (torch.randn(n, k // 32, generator=g_) * 0.1).repeat_interleave(32, 1).to(DEV).contiguous()
+    st = (torch.rand(n, k // 32, generator=g_) * 0.05 + 0.01).repeat_interleave(32, 1).to(DEV).contiguous()
+    st[5] = 0.0  # a row that cannot move
+    top = torch.full((n,), 3.0, device=DEV)
+    gb = torch.randn(n, length, generator=g_).to(DEV) * 0.02
+    outs = []
+    for parts in ([slice(0, n)], [slice(0, 5000), slice(5000, n)]):  # one launch with a lane per row; two with a warp per row
+        cc, dw = c.clone(), torch.zeros(n, length, device=DEV)
+        for s in parts:
+            cs, ds = cc[s].contiguous(), torch.empty(s.stop - s.start, length, device=DEV)
+            refine_kernel.refine_block(gb[s].contiguous(), cs, lo[s].contiguous(), st[s].contiguous(), top[s].contiguous(),
+                                       hs, b0, length, ds)
+            cc[s], dw[s] = cs, ds
+        outs.append((cc, dw))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert bool((outs[0][0] != c).any()) and torch.equal(outs[0][0][5], c[5])
