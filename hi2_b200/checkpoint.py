@@ -140,13 +140,14 @@ def write_shard(path: Path, packed: dict, passthrough: dict | None = None, table
 
 
 def write_checkpoints(shards: dict, tables: dict, picks: dict, sigma_of, cfg: Config, out_dir,
-                      budget: int = ENCODE_BATCH_BYTES, log=print) -> dict:
+                      budget: int = ENCODE_BATCH_BYTES, log=print, factors: dict | None = None) -> dict:
     """Encode and write a model shard by shard.
 
     ``shards``: ``{file name: {tensor name: tensor on the device}}`` in source order; tensors with a
     table are quantised with ``picks[name]``, the others are passed through.  ``sigma_of(name)`` returns
     ``(second moment sum or None, tokens, sigma_id, ColumnStats or None)`` for a tensor - what
-    :class:`hi2_b200.layerwise.DeviceSink` holds.  Returns ``{file name: marker}``."""
+    :class:`hi2_b200.layerwise.DeviceSink` holds; ``factors`` (optional) its ``factors``: inverse
+    factors already started while tabulating, by ``sigma_id``.  Returns ``{file name: marker}``."""
     out_dir = Path(out_dir)
     copy_stream = torch.cuda.Stream()
     markers = {}
@@ -159,7 +160,7 @@ def write_checkpoints(shards: dict, tables: dict, picks: dict, sigma_of, cfg: Co
                 sigma, tokens, sid, stats = sigma_of(n)
                 reqs.append(EncodeRequest(tensors[n], stats, tables[n], picks[n], sigma=sigma, sigma_id=sid,
                                           sigma_n=max(int(tokens), 1)))
-            packed = dict(zip(group, encode_many(reqs, cfg, to_host=False)))
+            packed = dict(zip(group, encode_many(reqs, cfg, to_host=False, factors=factors)))
             pending.append(_HostCopy(packed, copy_stream))  # D2H runs beside the next group's encode
         host: dict = {}
         for p in pending:

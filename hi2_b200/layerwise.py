@@ -28,7 +28,7 @@ import torch
 from torch import nn
 
 from . import dist as hd
-from .calibrate import Config, TensorTable, build_table, shared_transform
+from .calibrate import Config, TensorTable, build_table, factor_for, shared_transform
 from .hessian import HessianStats
 from .moe import expert_parts, sibling_leader, top_up
 from .stats import ColumnStats
@@ -201,6 +201,7 @@ class DeviceSink:
     stats: dict = field(default_factory=dict)
     leader: dict = field(default_factory=dict)
     groups: list = field(default_factory=list)
+    factors: dict = field(default_factory=dict)  # leader -> (d, FactorJob, None), started while tabulating
 
     def hessians(self, lead, hess, linears):
         for ld, h in hess.items():
@@ -213,6 +214,17 @@ class DeviceSink:
             self.leader[m] = leader_name
 
 
+_factor_streams: dict = {}
+
+
+def _factor_stream(device, i: int) -> torch.cuda.Stream:
+    """High-priority side streams for the factor chains, made once per device and reused."""
+    key = (torch.device(device).index, i)
+    if key not in _factor_streams:
+        _factor_streams[key] = torch.cuda.Stream(device, priority=-1)
+    return _factor_streams[key]
+
+
 def _eligible(name: str, shape, include, exclude) -> bool:
     if len(shape) != 2 or shape[1] % 64:
         return False
@@ -223,12 +235,15 @@ def _eligible(name: str, shape, include, exclude) -> bool:
 
 def calibrate_layerwise(model: nn.Module, ids: torch.Tensor, cfg: Config, ex=None, workdir=None, include=None,
                         exclude=None, limit_layers: int | None = None, log=print, resolve=None,
-                        sink: DeviceSink | None = None, device=None, batch: int = 32) -> dict:
+                        sink: DeviceSink | None = None, device=None, batch: int = 32, prefactor: bool = True) -> dict:
     """``{checkpoint tensor name: TensorTable}`` for every eligible Linear of every decoder layer
     (of the layers this rank owns when several ranks run), statistics left in ``sink``.
 
     ``model`` must live on ``device`` (every rank holds the whole model); ``ids [sequences, tokens]``
-    are the calibration ids of ALL ranks, of which rank r takes sequences ``r, r + world, ...``."""
+    are the calibration ids of ALL ranks, of which rank r takes sequences ``r, r + world, ...``.
+    With ``prefactor`` (and GPTQ rounding without act-order) the basis change and the inverse factor
+    of every shared input are started on side streams as soon as its transform is known, so that they
+    run beside the tables; the encode stage finds them in ``sink.factors``."""
     del ex, workdir
     sink = sink if sink is not None else DeviceSink()
     device = torch.device(device) if device is not None else next(model.parameters()).device
@@ -285,6 +300,13 @@ def calibrate_layerwise(model: nn.Module, ids: torch.Tensor, cfg: Config, ex=Non
             ws = [layer.get_submodule(n).weight.detach() for n in names]
             transform = shared_transform(ws, st, cfg)
             sink.group(linears[ld], [linears[n] for n in names], st)
+            if prefactor and want_h and not cfg.act_order and ld in hess and hess[ld].n > 0:
+                side = _factor_stream(device, len(sink.factors) % 4)
+                side.wait_stream(torch.cuda.current_stream(device))
+                with torch.cuda.stream(side):
+                    d, job, _ = factor_for(hess[ld].S, hess[ld].n, transform[0], transform[1], cfg)
+                    job.release_scratch()
+                sink.factors[linears[ld]] = (d, job, None)
             for n, w in zip(names, ws):
                 if st is None:
                     log(f"warning: {linears[n]} saw no calibration tokens; data-free weights")
@@ -315,7 +337,7 @@ def encode_layerwise(model: nn.Module, tables: dict, picks: dict, sink: DeviceSi
                                           sigma_n=1 if sigma is None else sigma[1]))
                 names.append(m)
         if reqs:
-            out.update(zip(names, encode_many(reqs, cfg, to_host=to_host)))
+            out.update(zip(names, encode_many(reqs, cfg, to_host=to_host, factors=sink.factors or None)))
     return out
 
 

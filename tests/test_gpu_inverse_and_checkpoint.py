@@ -78,7 +78,9 @@ def test_write_and_verify_checkpoint(tmp_path):
         s, n = sink.sigma[leader]
         return s, n, leader, sink.stats[leader]
 
-    markers = write_checkpoints(shards, tables, alloc.picks, sigma_of, cfg, tmp_path, budget=1 << 18, log=lambda *_: None)
+    assert len(sink.factors) == len(sink.groups)  # started beside the tables
+    markers = write_checkpoints(shards, tables, alloc.picks, sigma_of, cfg, tmp_path, budget=1 << 18, log=lambda *_: None,
+                                factors=sink.factors)
     assert set(markers) == set(shards)
     for shard, tensors in shards.items():
         path = tmp_path / shard
