@@ -606,8 +606,8 @@ class MoeJob:
 
                     for nm, k in (("in", self.cfg["hidden"]), ("mid", self.cfg["expert_ffn"])):
                         shared[f"experts.{e}.{nm}"] = L.SharedInput(f"experts.{e}.{nm}", k, HessianStats(k, self.device))
+            L.HessianStats.check_all([s_in.hessian for s_in in shared.values()])
             for s_in in shared.values():
-                s_in.hessian.check()
                 s_in.moments = L.ColumnStats.from_second_moment(s_in.hessian.S, s_in.hessian.n)
             own_tokens = {name: s_in.hessian.n for name, s_in in shared.items()}
             # leaders named like the expert's first projection, so the grouping of hi2_b200.moe applies

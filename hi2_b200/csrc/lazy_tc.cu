@@ -261,14 +261,15 @@ lazy_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
 // leading dimension.  Triangular operands are expressed as reduction ranges per tile (the same
 // flags as gemm.cuh): the skipped range holds exact zeros, so taking whole 32-wide stages of it
 // changes nothing.  The reduction of a tile is cut into windows of G_WINDOW stages (64 values of
-// k): each window is accumulated in its own TMEM buffer and ADDED to C by TMA (round-to-nearest
-// adds in L2), the windows of a tile in order.  The tensor core's own accumulator truncates, so a
+// k): each window is accumulated in its own TMEM buffer and added, round-to-nearest, into fp32
+// registers of the eight epilogue warps while the next window accumulates in the other buffer;
+// the finished tile is ADDED to C by TMA once.  The tensor core's own accumulator truncates, so a
 // chain of thousands of accumulation steps loses a decimal digit that the heavy cancellation of
 // the factor recursion then exposes.  Measured on a rank-deficient 4096-wide Hessian (2048 tokens,
 // condition 1e5), error of U against an fp64 solution over max|U|: one chain per tile 4.4e-4,
-// windows of 256 4.1e-5, of 128 2.0e-5, of 64 1.2e-5 (the reference's fp32 LAPACK path: 8e-6), at
-// the same speed.  C therefore always receives adds: for a plain store the launcher zeroes C
-// first.  TMA clips the boxes at the edge of C, so m and n need no alignment.
+// windows of 256 4.1e-5, of 128 2.0e-5, of 64 1.2e-5 (the reference's fp32 LAPACK path: 8e-6).
+// C always receives adds: for a plain store the launcher zeroes C first.  TMA clips the boxes at
+// the edge of C, so m and n need no alignment.
 constexpr int GT_KB_LE_J = 1, GT_KB_GE_J = 2, GT_KA_LE_I = 4, GT_LOWER_OUT = 8, GT_NEGATE = 16, GT_ADD = 32;
 
 struct GParams {
@@ -296,9 +297,10 @@ __device__ __forceinline__ void tile_range(const GParams& p, int tr, int tc, int
   if (s1 < s0) s1 = s0;  // an empty range adds nothing: the tile of C keeps its (zeroed) content
   if ((p.flags & GT_LOWER_OUT) && tc * LN > tr * LM + LM - 1) s1 = s0;
 }
-constexpr int G_WINDOW = 2;  // stages per accumulation window
+constexpr int G_WINDOW = 2;     // stages per accumulation window
+constexpr int G_THREADS = 320;  // warps 0..7 epilogue, warp 8 TMA, warp 9 MMA
 
-__global__ void __launch_bounds__(L_THREADS, 1)
+__global__ void __launch_bounds__(G_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                const __grid_constant__ CUtensorMap map_bhi, const __grid_constant__ CUtensorMap map_blo,
                const __grid_constant__ CUtensorMap map_c, const GParams p) {
@@ -310,11 +312,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < LSTAGES; ++s) bar_init(&ctl->full[s], 1), bar_init(&ctl->empty[s], 1);
-    for (int b = 0; b < 2; ++b) bar_init(&ctl->acc_full[b], 1), bar_init(&ctl->acc_empty[b], 4);
+    for (int b = 0; b < 2; ++b) bar_init(&ctl->acc_full[b], 1), bar_init(&ctl->acc_empty[b], 8);
     ctl->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&ctl->tmem_base)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -324,7 +326,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
   const uint32_t tmem_base = ctl->tmem_base;
   const int tiles = p.row_tiles * p.col_tiles;
 
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
     int stage = 0;
     uint32_t phase = 0;
@@ -349,7 +351,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
       while (clock64() - t0 < 2000000LL) {
       }
     }
-  } else if (warp == 5 && lane == 0) {
+  } else if (warp == 9 && lane == 0) {
     // ------------------------------------------------------------ MMA issuer
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((p.flags & GT_NEGATE) ? (1u << 13) : 0u) |
                            ((uint32_t)(LN >> 3) << 17) | ((uint32_t)(LM >> 4) << 24);
@@ -386,46 +388,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
         ++n;
       }
     }
-  } else if (warp < 4) {
+  } else if (warp < 8) {
     // ------------------------------------------------------------ epilogue
-    uint32_t n = 0, chunk_no = 0;
+    // Warp w owns tensor-memory lanes 32 (w mod 4) .. +31 (the rows of the tile) and columns
+    // 128 (w / 4) .. +127.  A finished window is added into fp32 registers (round-to-nearest), so
+    // the tensor-memory accumulator, which truncates, never carries more than G_WINDOW stages, and
+    // C sees one add per element and tile.
+    const int quarter = warp & 3, half = warp >> 2;
+    uint32_t n = 0;
     bool ok = true;
-    uint8_t* my_boxes = stage_c + warp * (2 * C_BOX / 4);  // two 4 KiB boxes per warp
+    uint8_t* box = stage_c + warp * (C_BOX / 4);  // one 32 x 32 staging box per warp
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
       const int tr = tile % p.row_tiles, tc = tile / p.row_tiles;
       int s0, s1;
       tile_range(p, tr, tc, s0, s1);
+      if (s1 <= s0) continue;
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
       for (int w0 = s0; w0 < s1 && ok; w0 += G_WINDOW) {
         const int buf = n & 1;
         if (!(ok = bar_wait(&ctl->acc_full[buf], (n >> 1) & 1, ctl, p.status))) break;
         fence_after();
-        // the adds of the previous window of this tile have landed before this window's are sent:
-        // the windows reach every element of C in one fixed order (same bits on every run)
-        if (w0 > s0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-        __syncwarp();
-        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * LN;
-        for (int c = 0; c < LN / 32; ++c, ++chunk_no) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * LN + half * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
           tmem_ld32(taddr + c * 32, v);
-          uint8_t* box = my_boxes + (chunk_no & 1) * (C_BOX / 4);
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-          uint8_t* rowp = box + lane * 128;
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) =
-                make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            tma_reduce_add(&map_c, box, tc * LN + c * 32, tr * LM + warp * 32);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(v[i]);
         }
         fence_before();
         __syncwarp();
         if (lane == 0) bar_arrive(&ctl->acc_empty[buf]);
         ++n;
+      }
+      if (!ok) break;
+      uint8_t* rowp = box + lane * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the box is free again
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) =
+              make_float4(acc[c * 32 + 4 * q], acc[c * 32 + 4 * q + 1], acc[c * 32 + 4 * q + 2], acc[c * 32 + 4 * q + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add(&map_c, box, tc * LN + half * 128 + c * 32, tr * LM + quarter * 32);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
       }
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -433,7 +446,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constan
 
   fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
@@ -625,7 +638,7 @@ int launch_gemm_tc2(int64_t m, int64_t n, int64_t kk, const float* a_hi, const f
   int device = 0, sms = 148;
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  gemm_tc_kernel<<<tiles < sms ? tiles : sms, L_THREADS, L_SMEM, stream>>>(mah, mal, mbh, mbl, mc, p);
+  gemm_tc_kernel<<<tiles < sms ? tiles : sms, G_THREADS, L_SMEM, stream>>>(mah, mal, mbh, mbl, mc, p);
   return check_launch("gemm_tc");
 }
 

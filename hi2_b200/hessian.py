@@ -99,6 +99,15 @@ class HessianStats:
                     f"hessian_accumulate: a bounded device-side wait ran out (status {status})"
                 )
 
+    @staticmethod
+    def check_all(many) -> None:
+        """:meth:`check` for several accumulators with ONE read-back (a layer of experts has hundreds)."""
+        words = [w for h in many for w in h._unchecked]
+        for h in many:
+            h._unchecked = []
+        if words and any(torch.cat(words).tolist()):
+            raise RuntimeError("hessian_accumulate: a bounded device-side wait ran out")
+
     @torch.no_grad()
     def update(self, x: torch.Tensor, chunk: int = 4096, defer_check: bool = False) -> None:
         """``S += x^T x`` for ``x [..., K]``.  bf16 / fp16 activations feed the tensor cores

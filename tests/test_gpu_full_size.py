@@ -29,6 +29,27 @@ def test_second_moment_k11008_against_fp64_columns():
     assert err < 2e-5, err
 
 
+def test_second_moment_wide_input_off_the_tile_grid():
+    """Inputs wider than 8192 columns (the one-block tensor-core kernel): K past a multiple of the
+    256-wide tile, a token count that is no multiple of the stage, and a second call on top."""
+    from hi2_b200.hessian import HessianStats
+
+    g = _gen(3)
+    k, tokens = 8208, 40000 + 37
+    x = (torch.randn(tokens, k, generator=g, device=DEV) * torch.exp(torch.randn(1, k, generator=g, device=DEV))).bfloat16()
+    h = HessianStats(k, DEV)
+    h.update(x)
+    h.update(x[:9000])
+    assert h.n == tokens + 9000 and torch.equal(h.S, h.S.T)
+    cols = torch.cat([torch.randint(0, k, (40,), generator=g, device=DEV),
+                      torch.tensor([0, 255, 256, 8191, 8192, 8207], device=DEV)])
+    xd = x.double()
+    want = xd.T[cols] @ xd + xd[:9000].T[cols] @ xd[:9000]
+    scale = ((xd**2).sum(0) + (xd[:9000] ** 2).sum(0)).sqrt()
+    err = ((h.S[cols].double() - want) / (scale[cols, None] * scale[None, :])).abs().max().item()
+    assert err < 2e-5, err
+
+
 def test_inverse_factor_k11008_inverts_the_damped_hessian():
     from hi2_b200.hessian import HessianStats, inverse_factor, transform_sigma
 
