@@ -390,7 +390,7 @@ class ModelJob:
         from hi2_b200 import dist as hd
         from hi2_b200 import layer as L
         from hi2_b200.allocate import allocate_global
-        from hi2_b200.calibrate import EncodeRequest, TensorTable, encode_many
+        from hi2_b200.calibrate import EncodeRequest, TensorTable, encode_many, group_rows
 
         marks: list = []
         cur = torch.cuda.current_stream(self.device)
@@ -460,17 +460,17 @@ class ModelJob:
             below_floor = {"target_bpw": self.cfg["bpw_infeasible"], "feasible": probe.feasible, "bpw": probe.bpw,
                            "rows_by_width": probe.frac_by_bits}
         alloc = allocate_global(everything, self.cfg["bpw"])
-        for st in state.values():  # the allocation has read results back: the status words are there
-            for sh in [st["shared"], *st["others"]]:
-                for s_in in sh.values():
-                    s_in.hessian.check()
+        # the allocation has read results back: the status words are there
+        L.HessianStats.check_all([s_in.hessian for st in state.values() for sh in [st["shared"], *st["others"]]
+                                  for s_in in sh.values()])
+        for st in state.values():
             st["others"] = None
         self._mark(marks, "encode")
         # Several layers per call: rows of equal width from all of them share the column loops, and the
         # host reads status words back once per call, not once per layer.
         packed, timing = {}, []
         per_call = self.cfg.get("layers_per_encode", 4)
-
+        calls = []
         for c0 in range(0, len(self.owned), per_call):
             chunk = self.owned[c0 : c0 + per_call]
             reqs, keys, fac = [], [], {}
@@ -484,9 +484,16 @@ class ModelJob:
                     keys.append((l, name))
                 for iname, f in st["factors"].items():
                     fac[f"L{l}.{iname}"] = f
+            calls.append((chunk, reqs, keys, fac))
+        # rows by candidate for the whole model with one read-back, now that the device is idle anyway:
+        # the calls below then start without waiting for it
+        group_rows([r for _, reqs, _, _ in calls for r in reqs])
+        while calls:
+            chunk, reqs, keys, fac = calls.pop(0)
             out = encode_many(reqs, self.qcfg, to_host=to_host, factors=fac, timing=timing)
             for (l, name), t in zip(keys, out):
                 packed.setdefault(l, {})[name] = t
+            del reqs, fac
             for l in chunk:
                 state[l] = None  # second moments and factors of the layer are free again
         self._mark(marks, "end")

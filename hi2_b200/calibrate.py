@@ -55,6 +55,10 @@ class TensorTable:
     energy: float | torch.Tensor  # sum d * w^2; a 0-dim device tensor until someone reads it
     n_tokens: int
     col_scale: torch.Tensor | None = None  # fp16 [K]; on the device when the table was built there
+    # the (smoothing vector, flags) objects handed to build_table, when it was handed some: tables and
+    # factor jobs made from the same objects are recognised as sharing a transform without reading
+    # the vector back from the device
+    transform_ref: tuple | None = None
 
 
 def candidate_row_bits(nbits: int, block: int, k: int) -> float:
@@ -202,6 +206,7 @@ def build_table(name: str, w: torch.Tensor, stats: ColumnStats | None, cfg: Conf
         s16, had = transform
         s16 = None if s16 is None else s16.clone()
         had = had.clone()
+    given = tuple(transform) if transform is not None else None
     wt = stored_rows(w, s16, had)
     inv = None if s16 is None else 1.0 / s16.to(dev, torch.float32)
     d = _weights(stats, k, had, dev, inv)
@@ -216,6 +221,7 @@ def build_table(name: str, w: torch.Tensor, stats: ColumnStats | None, cfg: Conf
     return TensorTable(
         name, (r, k), had.cpu(), torch.stack(sse), list(cfg.candidates), energy.sum(),
         n_tokens if n_tokens is not None else (stats.n if stats else 0), s16,
+        transform_ref=given,
     )
 
 
@@ -232,6 +238,7 @@ class EncodeRequest:
     sigma_id: str | None = None
     comp_out: dict | None = None
     sigma_n: int = 1  # divide sigma by this (lets the raw sum be passed without a copy)
+    groups: tuple | None = None  # (row order, rows per candidate) from :func:`group_rows`
 
 
 def _transform_key(col_scale, had):
@@ -248,7 +255,42 @@ def _job_key(job):
 def _factor_key(req: EncodeRequest, i: int):
     t = req.table
     sid = req.sigma_id if req.sigma_id is not None else f"#{i}"
+    if t.transform_ref is not None:  # no read-back: the objects the table was built from stand for their content
+        return (sid, "ref", id(t.transform_ref[0]), id(t.transform_ref[1]))
     return (sid, *_transform_key(t.col_scale, t.had))
+
+
+def _same_transform(t: TensorTable, job) -> bool:
+    """Whether a factor job started earlier belongs to the transform of table ``t``."""
+    ref = t.transform_ref
+    if ref is not None and job.transform is not None and ref[0] is job.transform[0] and ref[1] is job.transform[1]:
+        return True
+    return _job_key(job) == _transform_key(t.col_scale, t.had)
+
+
+def group_rows(reqs: list) -> None:
+    """Rows of every request grouped by candidate, with ONE read-back for all of them: a stable sort
+    of the picks and their histogram, left in ``req.groups``.  (A ``nonzero()`` per request and
+    candidate costs a host synchronisation each: 42 per decoder layer, 1152 per layer of 64 experts;
+    so does ``torch.bincount``.)  :func:`encode_many` calls this for requests that come without;
+    a caller that encodes a model in several calls groups all requests once, while the device is idle
+    after the allocation anyway, and the calls then start without waiting for the device."""
+    todo = [r for r in reqs if r.groups is None]
+    if not todo:
+        return
+    hist, by_dev = [], {}
+    for i, r in enumerate(todo):
+        dev = _lib.need_cuda(r.w)
+        picks = r.picks if r.picks.device == dev else _lib.upload(r.picks, dev)
+        c = len(r.table.candidates)
+        hist.append((picks[None, :] == torch.arange(c, device=dev)[:, None]).sum(1))
+        r.groups = (torch.argsort(picks, stable=True), None)
+        by_dev.setdefault(dev, []).append(i)
+    cmax = max(h.numel() for h in hist)
+    for idxs in by_dev.values():
+        table = torch.stack([torch.nn.functional.pad(hist[i], (0, cmax - hist[i].numel())) for i in idxs])
+        for i, row in zip(idxs, table.tolist()):
+            todo[i].groups = (todo[i].groups[0], row)
 
 
 def factor_for(sigma, sigma_n, col_scale, had, cfg: Config):
@@ -287,23 +329,7 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
     pieces: dict[int, list] = {}
     jobs, where, refine_with = [], [], []
     stored: dict[int, torch.Tensor] = {}
-    # Rows of every request grouped by candidate with ONE read-back for all requests: a stable sort of
-    # the picks and their histogram (a `nonzero()` per request and candidate costs a host
-    # synchronisation each: 42 per decoder layer, 1152 per layer of 64 experts).
-    grouped = []
-    for r in reqs:
-        dev = _lib.need_cuda(r.w)
-        picks = r.picks.to(dev)
-        grouped.append((torch.argsort(picks, stable=True), torch.bincount(picks, minlength=len(r.table.candidates))))
-    cmax = max((g[1].numel() for g in grouped), default=0)
-    by_dev: dict = {}
-    for i, (_, c) in enumerate(grouped):
-        by_dev.setdefault(c.device, []).append(i)
-    counts_host: dict[int, list] = {}
-    for idxs in by_dev.values():
-        table = torch.stack([torch.nn.functional.pad(grouped[i][1], (0, cmax - grouped[i][1].numel())) for i in idxs])
-        for i, row in zip(idxs, table.tolist()):
-            counts_host[i] = row
+    group_rows(reqs)
     for ri, r in enumerate(reqs):
         dev = _lib.need_cuda(r.w)
         t = r.table
@@ -313,7 +339,7 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
         use_gptq = cfg.rounding == "gptq" and r.sigma is not None
         if use_gptq:
             fk = _factor_key(r, ri)
-            if fk not in factors and r.sigma_id in ready and _job_key(ready[r.sigma_id][1]) == fk[1:]:
+            if fk not in factors and r.sigma_id in ready and _same_transform(t, ready[r.sigma_id][1]):
                 # started earlier on a side stream for this very (input, smoothing vector, flags):
                 # order after it on the device, never on the host, so the narrow matrices are rounded
                 # while the widest factor is still being computed.  d is complete at d_ready; U only
@@ -339,9 +365,9 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
             inv = None if t.col_scale is None else 1.0 / t.col_scale.to(dev, torch.float32)
             d = _weights(r.stats, k, had, dev, inv)
         out = pieces.setdefault(ri, [])
-        order, off = grouped[ri][0], 0
+        (order, counts), off = r.groups, 0
         for ci, (nb, b) in enumerate(t.candidates):
-            n_ci = int(counts_host[ri][ci])
+            n_ci = int(counts[ci])
             rows = order[off : off + n_ci]  # ascending row indices of this candidate (the sort is stable)
             off += n_ci
             if n_ci == 0:

@@ -14,6 +14,18 @@ from . import _lib
 from .format import GROUP, hadamard16
 
 
+_basis: dict = {}
+
+
+def _hadamard_on(dev: torch.device) -> torch.Tensor:
+    """The fp64 rotation matrix on ``dev``, uploaded once per device: a fresh blocking copy per call
+    would make the host wait for everything queued on the stream."""
+    key = (dev.type, dev.index)
+    if key not in _basis:
+        _basis[key] = hadamard16(torch.float64, dev)
+    return _basis[key]
+
+
 class ColumnStats:
     def __init__(self, k: int, device="cuda"):
         if k % GROUP:
@@ -68,10 +80,10 @@ class ColumnStats:
         unrotated = moment.diagonal(dim1=-2, dim2=-1)
         if flags is None:
             return unrotated.flatten().float()
-        basis = hadamard16(torch.float64, dev)
+        basis = _hadamard_on(dev)
         # (T M T^T)_ii = sum_jk T_ij M_jk T_ik
         rotated = torch.einsum("ij,gjk,ik->gi", basis, moment, basis)
-        chosen = torch.where(flags.to(dev).reshape(-1, 1) != 0, rotated, unrotated)
+        chosen = torch.where(_lib.upload(flags, dev).reshape(-1, 1) != 0, rotated, unrotated)
         return chosen.flatten().float()
 
     def state(self) -> dict:
