@@ -428,9 +428,9 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
         picks = r.picks.cpu()
         out.append(
             assemble(pieces[ri], cand[picks, 0], cand[picks, 1], t.had, t.shape[1], t.col_scale,
-                     to_host=to_host, bad=bad)
+                     to_host=to_host, bad=bad, wait=False)
         )
-    if any(int(f.item()) for f in flags.values()):
+    if any(int(f.item()) for f in flags.values()):  # also the one wait for the copies to the host queued above
         raise ValueError("code outside the ladder")
     return out
 

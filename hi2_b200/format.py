@@ -123,8 +123,17 @@ class HI2Tensor:
 FIELDS = ("codes", "code_off", "blk_params", "param_off", "row_consts", "row_nbits", "row_block", "had")
 
 
+def _to_pinned(t: torch.Tensor) -> torch.Tensor:
+    """A copy of device tensor ``t`` in page-locked host memory, queued on the current stream (the
+    caller synchronises before reading).  A plain ``.cpu()`` goes through pageable memory at a
+    fraction of the link's speed and makes the host wait for every buffer in turn."""
+    h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+    h.copy_(t, non_blocking=True)
+    return h
+
+
 def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=None,
-             to_host: bool = True, bad: torch.Tensor | None = None) -> HI2Tensor:
+             to_host: bool = True, bad: torch.Tensor | None = None, wait: bool = True) -> HI2Tensor:
     """Flat buffers from per-candidate pieces ``(rows, codes[r, K] u8, params[r, nb, 2] u8,
     consts[r, 3] fp16)``.  A piece may carry its ``(nbits, block)`` as fifth and sixth entry, which
     saves reading ``rows[0]`` back from the device; ``bad`` (optional, a device int32) collects the
@@ -133,8 +142,9 @@ def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=N
 
     The packing and the scatters run on the device of the first piece.  As in the reference the
     result is returned on the host (``to_host=False`` keeps the three big buffers on the device,
-    which is what a caller that overlaps the copy wants); ``stager`` is accepted for signature
-    compatibility and ignored (B200 copies from ordinary pinned or pageable memory)."""
+    which is what a caller that overlaps the copy wants); the host buffers are page-locked, and with
+    ``wait=False`` their copies are only queued on the current stream: the caller synchronises once
+    for several tensors.  ``stager`` is accepted for signature compatibility and ignored."""
     del stager
     r = row_nbits.numel()
     nb = row_nbits.to("cpu", torch.int64)
@@ -177,8 +187,12 @@ def assemble(pieces, row_nbits, row_block, had, k: int, col_scale=None, stager=N
             )
         if check_here and int(bad.item()):
             raise ValueError("code outside the ladder")
-    if to_host:
-        codes, params, consts = codes.cpu(), params.cpu(), consts.cpu()
+    if to_host and codes.is_cuda:
+        codes, params, consts = _to_pinned(codes), _to_pinned(params), _to_pinned(consts)
+        if col_scale is not None and col_scale.is_cuda:
+            col_scale = _to_pinned(col_scale)
+        if wait:
+            torch.cuda.current_stream(dev).synchronize()
     return HI2Tensor(
         codes=codes,
         code_off=code_off.to(torch.int32),

@@ -92,8 +92,9 @@ class HessianStats:
         """Raise if a launch made with ``defer_check=True`` gave up on a bounded device-side wait
         (synchronises with those launches)."""
         pending, self._unchecked = self._unchecked, []
-        for word in pending:
-            status = int(word.item())
+        if not pending:
+            return
+        for status in torch.cat([w.reshape(1) for w in pending]).tolist():  # one read-back for all launches
             if status:
                 raise RuntimeError(
                     f"hessian_accumulate: a bounded device-side wait ran out (status {status})"

@@ -179,13 +179,20 @@ def leaders(linears, leader_of: dict) -> dict:
     return lead
 
 
-def finish_stats(lead: dict, linears, k_of: dict, stats: dict, hess: dict, dev, want_hessian: bool) -> None:
+def finish_stats(lead: dict, linears, k_of: dict, stats: dict, hess: dict, dev, want_hessian: bool,
+                 unchecked: list | None = None) -> None:
     """Make sure every leader has both accumulators (empty ones for Linears that saw no token) and,
-    with full second moments, read the group moments out of them."""
+    with full second moments, read the group moments out of them.  The status words of the
+    second-moment launches are read here (a wait for the device), or, when the caller passes a list
+    as ``unchecked``, left to it: the accumulators are appended and the caller settles them all with
+    one ``HessianStats.check_all`` later."""
     for ld in dict.fromkeys(lead[n] for n in linears):
         if want_hessian:
             h = hess.setdefault(ld, HessianStats(k_of[ld], dev))
-            h.check()
+            if unchecked is None:
+                h.check()
+            else:
+                unchecked.append(h)
             stats[ld] = ColumnStats.from_second_moment(h.S, h.n) if h.n else ColumnStats(k_of[ld], dev)
         else:
             stats.setdefault(ld, ColumnStats(k_of[ld], dev))
@@ -255,6 +262,7 @@ def calibrate_layerwise(model: nn.Module, ids: torch.Tensor, cfg: Config, ex=Non
     log(f"captured {hidden.shape[0]} calibration sequences of {tuple(hidden.shape[1:])}")
     want_h = cfg.rounding == "gptq" and not cfg.sequential
     tables: dict = {}
+    unchecked: list = []  # status words are read once, after the last layer: the host never waits in between
     for li, layer in enumerate(layers):
         if limit_layers is not None and li >= limit_layers:
             break
@@ -285,7 +293,7 @@ def calibrate_layerwise(model: nn.Module, ids: torch.Tensor, cfg: Config, ex=Non
                 acc.n = int(count.item())
             if rank != owner:
                 continue
-        finish_stats(lead, linears, k_of, stats, hess, device, want_h)
+        finish_stats(lead, linears, k_of, stats, hess, device, want_h, unchecked)
         counts = {n: stats[lead[n]].n for n in linears}
         borrowed = top_up({linears[ld]: st for ld, st in stats.items()},
                           {linears[ld]: h for ld, h in hess.items()} if want_h else None,
@@ -314,6 +322,7 @@ def calibrate_layerwise(model: nn.Module, ids: torch.Tensor, cfg: Config, ex=Non
         if borrowed:
             log(f"  layer {li}: {len(borrowed)} expert inputs topped up with the layer average")
         log(f"layer {li}: {len(linears)} linears tabulated")
+    HessianStats.check_all(unchecked)
     return tables
 
 
