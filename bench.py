@@ -350,7 +350,7 @@ class ModelJob:
         self.groups = self.n_layers // world
         self.owned = [g * world + rank for g in range(self.groups)]
         self.shapes, self.widths, self.plan = shapes_of(cfg)
-        self.qcfg = Config(candidates=candidates_of(cfg))
+        self.qcfg = Config(candidates=candidates_of(cfg), refine_passes=int(cfg.get("refine_passes", 0)))
         self.weights = {l: make_weights(cfg, self.shapes, l, device) for l in self.owned}
         lo, hi = hd.token_shard(cfg["tokens"], rank, world)
         self.inputs = make_inputs(cfg, self.widths, 0, hi - lo, lo, device)
@@ -1210,6 +1210,8 @@ def run_ours(args, cfg):
               "parallelism": (f"layer l on rank l mod {world}, token-sharded hessian, one reduce-scatter per input and layer group"
                               if whole_model else f"layer-per-gpu x{world}, token-sharded hessian"),
               "l2": "inputs larger than L2 (12-24 GB of activations per layer)"}
+    if cfg.get("refine_passes"):
+        config["refine_passes"] = cfg["refine_passes"]
     if whole_model:
         config["activations"] = ("one synthetic set (four tensors) stands in for the inputs of every layer; each layer's "
                                  "statistics are computed from it anew")
@@ -1491,6 +1493,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="whole-model configs: take this many layers instead of all")
+    ap.add_argument("--refine-passes", type=int, default=0,
+                    help="whole-model configs: sweeps of the +-1 code refinement after GPTQ (the reference's CLI default is 2; "
+                         "the headline metric is quoted without)")
     ap.add_argument("--no-config1", action="store_true", help="skip the full CPU run of config 1 in the cpu_baseline leg")
     ap.add_argument("--no-propagate", action="store_true",
                     help="skip the run with the activations produced on the device by layer forwards")
@@ -1502,6 +1507,9 @@ def main():
     if args.layers and "layers" in cfg:
         cfg["layers"] = args.layers
         cfg["workload"] += f"_first_{args.layers}_layers"
+    if args.refine_passes and "layers" in cfg:
+        cfg["refine_passes"] = args.refine_passes
+        cfg["workload"] += f"_refine_{args.refine_passes}"
     if args.kernels:
         run_kernels(args, cfg)
     elif "moe_layers" in cfg:

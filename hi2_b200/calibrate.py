@@ -252,6 +252,19 @@ def _job_key(job):
     return job.transform_key
 
 
+REFINE_STREAMS = 8
+_refine_streams: dict = {}
+
+
+def _refine_stream(dev: torch.device, i: int) -> torch.cuda.Stream:
+    """Side streams for the refinement loops, made once per device and reused (the caching allocator
+    keeps a pool per stream)."""
+    key = (dev.index, i)
+    if key not in _refine_streams:
+        _refine_streams[key] = torch.cuda.Stream(dev)
+    return _refine_streams[key]
+
+
 def _factor_key(req: EncodeRequest, i: int):
     t = req.table
     sid = req.sigma_id if req.sigma_id is not None else f"#{i}"
@@ -392,17 +405,39 @@ def encode_many(reqs: list[EncodeRequest], cfg: Config, ex=None, to_host: bool =
     if any(h is not None for h in refine_with):
         from .refine import refine_groups
 
-        by_tensor: dict[int, list[int]] = {}
-        for x, (ri, _) in enumerate(where):
+        # Rows that share a transformed Hessian (all candidates of a tensor, and all tensors reading
+        # the same input) go through one column loop; the loops of different inputs are chains of
+        # short dependent launches, so they run side by side on streams, nothing read back in between.
+        by_hs: dict[int, list[int]] = {}
+        for x in range(len(where)):
             if refine_with[x] is not None:
-                by_tensor.setdefault(ri, []).append(x)
-        for xs in by_tensor.values():
-            new = refine_groups(
-                [(jobs[x].w, encs[x], jobs[x].nbits, jobs[x].block) for x in xs],
-                refine_with[xs[0]], cfg.refine_passes,
-            )
+                by_hs.setdefault(id(refine_with[x]), []).append(x)
+        # longest loops first, each on the stream with the least work so far: a loop costs its number
+        # of column blocks times a step that grows with rows x width
+        def cost(xs):
+            k = jobs[xs[0]].w.shape[1]
+            return (k / 128) * (0.1 + 3e-9 * k * sum(jobs[x].w.shape[0] for x in xs))
+
+        load = [0.0] * REFINE_STREAMS
+        pending = []
+        for xs in sorted(by_hs.values(), key=cost, reverse=True):
+            dev = _lib.need_cuda(jobs[xs[0]].w)
+            si = load.index(min(load))
+            load[si] += cost(xs)
+            main, side = torch.cuda.current_stream(dev), _refine_stream(dev, si)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                new, status = refine_groups([(jobs[x].w, encs[x], jobs[x].nbits, jobs[x].block) for x in xs],
+                                            refine_with[xs[0]], cfg.refine_passes, wait=False)
+            pending.append((xs, new, status, main, side))
+        for xs, new, status, main, side in pending:
+            main.wait_stream(side)
             for x, codes in zip(xs, new):
+                codes.record_stream(main)
                 encs[x] = type(encs[x])(codes, encs[x].params, encs[x].consts, encs[x].sse, encs[x].comp)
+        words = [st for _, _, st, _, _ in pending if st is not None]
+        if words and any(torch.cat(words).tolist()):
+            raise RuntimeError("refine: a bounded device-side wait ran out in a tensor-core product")
     slot = {ri: iter([j for j, p in enumerate(pieces[ri]) if p is None]) for ri in pieces}
     comps: dict[int, list] = {}
     for (ri, rows), enc, job in zip(where, encs, jobs):

@@ -33,9 +33,11 @@ def _expand(lo: torch.Tensor, step: torch.Tensor, block: int):
 
 
 @torch.no_grad()
-def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
-    """Refined codes (float) of rows ``w [N, K]`` with per-column ladders ``lo_x``/``st_x`` and
-    the highest code of each row ``top [N]``; stops early when a sweep moves no code."""
+def _sweeps(w, codes, lo_x, st_x, top, hs, passes: int, use_tc: bool | None, wait: bool):
+    """``(refined codes (float), status word or None)``.  With ``wait`` the host follows the device:
+    it stops after a sweep that moved no code and raises on a raised status word.  Without, nothing
+    is read back: every sweep is queued (one that moves nothing changes nothing) and the status
+    word is left to the caller, so several tensors can be refined side by side on streams."""
     dev = _lib.need_cuda(w, codes, lo_x, st_x, top, hs)
     if not refine_kernel.available(dev):
         raise RuntimeError(f"refine kernel unavailable on {dev}: {refine_kernel.failure()}")
@@ -49,7 +51,10 @@ def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
     # The two products of a sweep, g = e Hs and g += dw Hs[b0:b1], run on the tensor cores as three
     # TF32 products (fp32-grade; Hs is symmetric, so its rows are the K-major right operand as they
     # lie).  Rows with 256 levels and narrow inputs keep the fp32 FMA product, as in the GPTQ path.
-    use_tc = k >= TC_MIN_K and k % 4 == 0 and bool((top <= 15).all())
+    if use_tc is None:
+        use_tc = bool((top <= 15).all())
+    use_tc = use_tc and k >= TC_MIN_K and k % 4 == 0
+    status = None
     if use_tc:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         hs_split = refine_kernel.split_tf32(hs)
@@ -58,7 +63,7 @@ def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
         refine_kernel.gemm(e, hs, g)
     del e
     for _ in range(passes):
-        start = c.clone()
+        start = c.clone() if wait else None
         for b0 in range(0, k, BLOCK_COLUMNS):
             b1 = min(b0 + BLOCK_COLUMNS, k)
             gb = g[:, b0:b1].contiguous()
@@ -68,11 +73,17 @@ def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
                 refine_kernel.gemm_tc(refine_kernel.split_tf32(dw_block), hs_split[:, :, b0:b1], g, status, accumulate=True)
             else:
                 refine_kernel.gemm(dw_block, hs[b0:b1], g, alpha=1.0, beta=1.0)
-        if bool((c == start).all()):
+        if wait and bool((c == start).all()):
             break
-    if use_tc and int(status.item()):
+    if wait and use_tc and int(status.item()):
         raise RuntimeError("refine: a bounded device-side wait ran out in a tensor-core product")
-    return c
+    return c, status
+
+
+def refine_expanded(w, codes, lo_x, st_x, top, hs, passes: int) -> torch.Tensor:
+    """Refined codes (float) of rows ``w [N, K]`` with per-column ladders ``lo_x``/``st_x`` and
+    the highest code of each row ``top [N]``; stops early when a sweep moves no code."""
+    return _sweeps(w, codes, lo_x, st_x, top, hs, passes, None, True)[0]
 
 
 def refine_codes(w, codes, lo, step, hs, nbits: int, block: int, passes: int) -> torch.Tensor:
@@ -91,9 +102,11 @@ def _decoded(enc):
     return lo.float(), step.float()
 
 
-def refine_groups(groups, hs: torch.Tensor, passes: int) -> list[torch.Tensor]:
-    """One sweep over the rows of every ``(w, enc, nbits, block)`` group of a tensor (rows of
-    different candidates share the column loop); returns the refined codes per group."""
+def refine_groups(groups, hs: torch.Tensor, passes: int, wait: bool = True):
+    """One sweep over the rows of every ``(w, enc, nbits, block)`` group (rows of different
+    candidates, and of different tensors that read the same input, share the column loop); returns
+    the refined codes per group.  ``wait=False`` reads nothing back and returns ``(codes per group,
+    status word or None)``: the caller checks the word once it has queued everything."""
     parts = []
     for w, enc, nbits, block in groups:
         lo, step = _decoded(enc)
@@ -101,9 +114,10 @@ def refine_groups(groups, hs: torch.Tensor, passes: int) -> list[torch.Tensor]:
         top = torch.full((w.shape[0],), float(2**nbits - 1), device=w.device)
         parts.append((w.float(), enc.codes.float(), lo_x, st_x, top))
     cat = [torch.cat([p[i] for p in parts]) for i in range(5)]
-    out = refine_expanded(*cat, hs, passes)
+    out, status = _sweeps(*cat, hs, passes, max(g[2] for g in groups) <= 4, wait)
     sizes = [p[0].shape[0] for p in parts]
-    return [c.to(groups[i][1].codes.dtype) for i, c in enumerate(out.split(sizes))]
+    codes = [c.to(groups[i][1].codes.dtype) for i, c in enumerate(out.split(sizes))]
+    return codes if wait else (codes, status)
 
 
 def refine_encoded(enc, w, hs, nbits: int, block: int, passes: int):

@@ -169,3 +169,32 @@ def test_int8_rule_closes_all_but_the_most_sensitive_rows():
             else:
                 assert bool((t.sse[6:, row] == b[3:6, row].min()).all())
         off += b.shape[1]
+
+
+def test_rows_grouped_by_candidate_with_one_read_back():
+    """``group_rows``: per request the rows of each candidate in ascending order, candidates in
+    order, counts on the host; picks given on the host or on the device; a candidate nobody picked;
+    requests with different numbers of candidates; already grouped requests are left alone."""
+    from hi2_b200.calibrate import EncodeRequest, TensorTable, group_rows
+
+    g = gen(11)
+    reqs = []
+    for rows, cands, on_dev in ((257, [(2, 16), (2, 32), (4, 64)], True), (64, [(2, 64), (4, 16)], False),
+                                (1000, [(2, 16), (2, 32), (2, 64), (4, 16), (4, 32), (4, 64)], True)):
+        picks = torch.randint(0, len(cands), (rows,), generator=g)
+        picks[picks == 1] = 0  # candidate 1 is never picked
+        w = torch.zeros(rows, 32, device=DEV)
+        table = TensorTable("t", (rows, 32), torch.ones(2, dtype=torch.uint8), torch.zeros(len(cands), rows, device=DEV),
+                            cands, 0.0, 0)
+        reqs.append(EncodeRequest(w, None, table, picks.to(DEV) if on_dev else picks))
+    group_rows(reqs)
+    for r in reqs:
+        order, counts = r.groups
+        picks = r.picks.cpu()
+        assert counts[: len(r.table.candidates)] == [int((picks == c).sum()) for c in range(len(r.table.candidates))]
+        assert sum(counts) == picks.numel() and counts[1] == 0
+        want = torch.cat([torch.nonzero(picks == c).flatten() for c in range(len(r.table.candidates))])
+        assert torch.equal(order.cpu(), want)
+    before = [r.groups for r in reqs]
+    group_rows(reqs)
+    assert all(a is b for a, b in zip(before, [r.groups for r in reqs]))

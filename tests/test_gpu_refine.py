@@ -177,3 +177,39 @@ def test_block_kernel_mappings_agree():
         outs.append((cc, dw))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     assert bool((outs[0][0] != c).any()) and torch.equal(outs[0][0][5], c[5])
+
+
+def test_refinement_of_tensors_side_by_side_equals_one_by_one():
+    """``encode_many`` with refinement: tensors that read the same input share one column loop, the
+    loops of different inputs run on side streams with nothing read back in between.  Rows are
+    refined independently of each other, so the result must equal encoding every tensor alone."""
+    from hi2_b200 import layer as L
+    from hi2_b200.allocate import allocate_global
+    from hi2_b200.calibrate import Config, EncodeRequest, encode_many
+    from tests.helpers import activations, gen
+
+    g = gen(31)
+    cfg = Config(effort="fast", refine_passes=2)
+    plan = L.LayerPlan({"a": "x", "b": "x", "c": "y"})
+    shapes = {"a": (96, 512), "b": (40, 512), "c": (64, 1024)}
+    weights = {n: (torch.randn(r, k, generator=g) * 0.02).bfloat16().to(DEV) for n, (r, k) in shapes.items()}
+    acts = {"x": activations(4096, 512, 5, spread=1.0, dtype=torch.bfloat16).to(DEV),
+            "y": activations(4096, 1024, 6, spread=1.0, dtype=torch.bfloat16).to(DEV)}
+    shared = L.accumulate(acts, DEV)
+    L.finish_statistics(shared, cfg)
+    tables = L.tabulate(weights, plan, shared, cfg)
+    picks = allocate_global(list(tables.values()), 3.0).picks
+
+    def request(n):
+        s = shared[plan.reads[n]]
+        return EncodeRequest(weights[n], s.moments, tables[n], picks[n], sigma=s.hessian.S, sigma_id=s.name,
+                             sigma_n=s.hessian.n)
+
+    together = encode_many([request(n) for n in shapes], cfg)
+    alone = [encode_many([request(n)], cfg)[0] for n in shapes]
+    plain = encode_many([request(n) for n in shapes], Config(effort="fast"))
+    for t, u, p in zip(together, alone, plain):
+        for f in ("codes", "blk_params", "row_consts", "row_nbits", "row_block", "code_off", "param_off"):
+            assert torch.equal(getattr(t, f), getattr(u, f)), f
+        assert torch.equal(t.blk_params, p.blk_params)  # ladders are never touched
+    assert any(not torch.equal(t.codes, p.codes) for t, p in zip(together, plain))  # the sweeps did move codes
