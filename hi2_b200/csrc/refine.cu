@@ -48,6 +48,27 @@ __device__ __forceinline__ void decide(float gj, float cc, float lo_j, float st_
   c_out = take ? (pick_m ? cm : cp) : cc;
 }
 
+// hi = tf32(x), lo = tf32(x - hi), round-to-nearest: the operand form of the tensor-core product
+// that follows the block (lazy_tc.cu).
+__device__ __forceinline__ void tf32_parts(float x, float& hi, float& lo) {
+  uint32_t hb, lb;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
+  hi = __uint_as_float(hb);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(x - hi));
+  lo = __uint_as_float(lb);
+}
+// Four changes dw: as they are, or (dw_lo given) as their TF32 parts.
+__device__ __forceinline__ void store_dw(float* dw, float* dw_lo, float a, float b, float c, float d) {
+  if (dw_lo == nullptr) {
+    *reinterpret_cast<float4*>(dw) = make_float4(a, b, c, d);
+    return;
+  }
+  float h[4], l[4];
+  tf32_parts(a, h[0], l[0]), tf32_parts(b, h[1], l[1]), tf32_parts(c, h[2], l[2]), tf32_parts(d, h[3], l[3]);
+  *reinterpret_cast<float4*>(dw) = make_float4(h[0], h[1], h[2], h[3]);
+  *reinterpret_cast<float4*>(dw_lo) = make_float4(l[0], l[1], l[2], l[3]);
+}
+
 struct Quad4 {
   float v[4];
 };
@@ -61,7 +82,7 @@ template <int W>
 __device__ __forceinline__ void run_phase(float2 (&g)[LMAX / 2], int& j, int len, float tp,
                                           const float* __restrict__ h_stage, const float* c_in,
                                           const float* lo_in, const float* st_in, Quad4& cq, Quad4& lq, Quad4& sq,
-                                          bool live, float* c_out, float* dw_out) {
+                                          bool live, float* c_out, float* dw_out, float* dw_lo_out) {
   constexpr int P = W / 2;
 #pragma unroll 1
   while (len - j > W - 32 && j < len) {
@@ -91,7 +112,7 @@ __device__ __forceinline__ void run_phase(float2 (&g)[LMAX / 2], int& j, int len
     }
     if (live) {
       *reinterpret_cast<float4*>(c_out + j0) = make_float4(cnew[0], cnew[1], cnew[2], cnew[3]);
-      *reinterpret_cast<float4*>(dw_out + j0) = make_float4(dws[0], dws[1], dws[2], dws[3]);
+      store_dw(dw_out + j0, dw_lo_out ? dw_lo_out + j0 : nullptr, dws[0], dws[1], dws[2], dws[3]);
     }
     cq = cn, lq = ln, sq = sn;
     j = j0 + 4;
@@ -99,10 +120,10 @@ __device__ __forceinline__ void run_phase(float2 (&g)[LMAX / 2], int& j, int len
 }
 
 __global__ void __launch_bounds__(ROWS_PER_CTA, 3)
-refine_block_kernel(const float* __restrict__ gb, int len, float* __restrict__ c,
+refine_block_kernel(const float* __restrict__ gb, int64_t ldg, int len, float* __restrict__ c,
                     const float* __restrict__ lo, const float* __restrict__ st,
                     const float* __restrict__ top, const float* __restrict__ hs, int64_t n_rows,
-                    int64_t k, int64_t b0, float* __restrict__ dwb) {
+                    int64_t k, int64_t b0, float* __restrict__ dwb, float* __restrict__ dw_lo) {
   extern __shared__ float4 h_stage4[];
   float* h_stage = reinterpret_cast<float*>(h_stage4);
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -135,11 +156,12 @@ refine_block_kernel(const float* __restrict__ gb, int len, float* __restrict__ c
   const bool live = row_raw < n_rows;
   const int64_t row = live ? row_raw : n_rows - 1;  // spare lanes shadow the last row and store nothing
   const float tp = top[row];
-  const float* grow = gb + row * len;
+  const float* grow = gb + row * ldg;
   float* crow = c + row * k + b0;
   const float* lorow = lo + row * k + b0;
   const float* strow = st + row * k + b0;
   float* dwrow = dwb + row * len;
+  float* dwlrow = dw_lo ? dw_lo + row * len : nullptr;
 
   float2 g[LMAX / 2];
 #pragma unroll
@@ -149,10 +171,10 @@ refine_block_kernel(const float* __restrict__ gb, int len, float* __restrict__ c
   }
   Quad4 cq = load4(crow), lq = load4(lorow), sq = load4(strow);
   int j = 0;
-  run_phase<128>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow);
-  run_phase<96>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow);
-  run_phase<64>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow);
-  run_phase<32>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow);
+  run_phase<128>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow, dwlrow);
+  run_phase<96>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow, dwlrow);
+  run_phase<64>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow, dwlrow);
+  run_phase<32>(g, j, len, tp, h_stage, crow, lorow, strow, cq, lq, sq, live, crow, dwrow, dwlrow);
 }
 
 // The same block with a WARP per row, four consecutive columns per lane: the lane that owns column j
@@ -164,10 +186,10 @@ refine_block_kernel(const float* __restrict__ gb, int len, float* __restrict__ c
 constexpr int WARP_ROWS_PER_CTA = 8;
 
 __global__ void __launch_bounds__(WARP_ROWS_PER_CTA * 32)
-refine_block_warp_kernel(const float* __restrict__ gb, int len, float* __restrict__ c,
+refine_block_warp_kernel(const float* __restrict__ gb, int64_t ldg, int len, float* __restrict__ c,
                     const float* __restrict__ lo, const float* __restrict__ st,
                     const float* __restrict__ top, const float* __restrict__ hs, int64_t n_rows,
-                    int64_t k, int64_t b0, float* __restrict__ dwb) {
+                    int64_t k, int64_t b0, float* __restrict__ dwb, float* __restrict__ dw_lo) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * WARP_ROWS_PER_CTA + (threadIdx.x >> 5);
   if (row >= n_rows) return;
@@ -179,7 +201,7 @@ refine_block_warp_kernel(const float* __restrict__ gb, int len, float* __restric
   float g[4] = {0.f, 0.f, 0.f, 0.f}, cj[4] = {0.f, 0.f, 0.f, 0.f}, lo_c[4] = {0.f, 0.f, 0.f, 0.f},
         st_c[4] = {0.f, 0.f, 0.f, 0.f}, dw_keep[4] = {0.f, 0.f, 0.f, 0.f};
   if (mine) {
-    const float4 gv = *reinterpret_cast<const float4*>(gb + row * len + c0);
+    const float4 gv = *reinterpret_cast<const float4*>(gb + row * ldg + c0);
     const float4 cv = *reinterpret_cast<const float4*>(c + base);
     const float4 lv = *reinterpret_cast<const float4*>(lo + base);
     const float4 sv = *reinterpret_cast<const float4*>(st + base);
@@ -239,11 +261,33 @@ refine_block_warp_kernel(const float* __restrict__ gb, int len, float* __restric
 
   if (mine) {
     *reinterpret_cast<float4*>(c + base) = make_float4(cj[0], cj[1], cj[2], cj[3]);
-    *reinterpret_cast<float4*>(dwb + row * len + c0) =
-        make_float4(dw_keep[0], dw_keep[1], dw_keep[2], dw_keep[3]);
+    store_dw(dwb + row * len + c0, dw_lo ? dw_lo + row * len + c0 : nullptr, dw_keep[0], dw_keep[1], dw_keep[2],
+             dw_keep[3]);
   }
 }
 
+}  // namespace
+}  // namespace hi2
+
+namespace hi2 {
+namespace {
+int launch_refine_block(const float* gb, int64_t ldg, int len, float* c, const float* lo, const float* st,
+                        const float* top, const float* hs, int64_t n_rows, int64_t k, int64_t b0, float* dwb,
+                        float* dw_lo, cudaStream_t stream) {
+  if (n_rows < (int64_t)148 * ROWS_PER_CTA) {  // too few rows to fill the SMs at a lane per row
+    const unsigned wgrid = (unsigned)ceil_div(n_rows, WARP_ROWS_PER_CTA);
+    refine_block_warp_kernel<<<wgrid, WARP_ROWS_PER_CTA * 32, 0, stream>>>(gb, ldg, len, c, lo, st, top, hs, n_rows,
+                                                                            k, b0, dwb, dw_lo);
+    return check_launch("refine_block");
+  }
+  const unsigned grid = (unsigned)ceil_div(n_rows, ROWS_PER_CTA);
+  const int smem = H_STAGE_FLOATS * (int)sizeof(float);
+  if (cudaFuncSetAttribute(refine_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return fail(HI2_ERR_LAUNCH, "refine_block: cannot reserve shared memory");
+  refine_block_kernel<<<grid, ROWS_PER_CTA, smem, stream>>>(gb, ldg, len, c, lo, st, top, hs, n_rows, k, b0, dwb,
+                                                             dw_lo);
+  return check_launch("refine_block");
+}
 }  // namespace
 }  // namespace hi2
 
@@ -259,17 +303,22 @@ extern "C" int hi2_refine_block(const float* gb, int len, float* c, const float*
   HI2_REQUIRE(aligned16(gb) && aligned16(c) && aligned16(lo) && aligned16(st) && aligned16(hs) &&
                   aligned16(dwb),
               "refine_block: buffers must be 16-byte aligned");
-  if (n_rows < (int64_t)148 * ROWS_PER_CTA) {  // too few rows to fill the SMs at a lane per row
-    const unsigned wgrid = (unsigned)ceil_div(n_rows, WARP_ROWS_PER_CTA);
-    refine_block_warp_kernel<<<wgrid, WARP_ROWS_PER_CTA * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        gb, len, c, lo, st, top, hs, n_rows, k, b0, dwb);
-    return check_launch("refine_block");
-  }
-  const unsigned grid = (unsigned)ceil_div(n_rows, ROWS_PER_CTA);
-  const int smem = H_STAGE_FLOATS * (int)sizeof(float);
-  if (cudaFuncSetAttribute(refine_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-    return fail(HI2_ERR_LAUNCH, "refine_block: cannot reserve shared memory");
-  refine_block_kernel<<<grid, ROWS_PER_CTA, smem, static_cast<cudaStream_t>(stream)>>>(
-      gb, len, c, lo, st, top, hs, n_rows, k, b0, dwb);
-  return check_launch("refine_block");
+  return launch_refine_block(gb, len, len, c, lo, st, top, hs, n_rows, k, b0, dwb, nullptr,
+                             static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hi2_refine_block_in_place(const float* g, int len, float* c, const float* lo, const float* st,
+                                         const float* top, const float* hs, int64_t n_rows, int64_t k,
+                                         int64_t b0, float* dw_hi, float* dw_lo, void* stream) {
+  using namespace hi2;
+  HI2_REQUIRE(k > 0 && k % 16 == 0, "refine_block_in_place: k must be a positive multiple of 16");
+  HI2_REQUIRE(len > 0 && len <= LMAX && len % 16 == 0, "refine_block_in_place: block length must be 16..128");
+  HI2_REQUIRE(b0 >= 0 && b0 % 16 == 0 && b0 + len <= k, "refine_block_in_place: block outside the row");
+  if (n_rows == 0) return HI2_OK;
+  HI2_REQUIRE(g && c && lo && st && top && hs && dw_hi && dw_lo, "refine_block_in_place: null pointer");
+  HI2_REQUIRE(aligned16(g) && aligned16(c) && aligned16(lo) && aligned16(st) && aligned16(hs) &&
+                  aligned16(dw_hi) && aligned16(dw_lo),
+              "refine_block_in_place: buffers must be 16-byte aligned");
+  return launch_refine_block(g + b0, k, len, c, lo, st, top, hs, n_rows, k, b0, dw_hi, dw_lo,
+                             static_cast<cudaStream_t>(stream));
 }

@@ -62,16 +62,23 @@ def _sweeps(w, codes, lo_x, st_x, top, hs, passes: int, use_tc: bool | None, wai
     else:
         refine_kernel.gemm(e, hs, g)
     del e
+    # with tensor-core products a step of the sweep is two launches: the block kernel reads its slice
+    # of g in place and leaves the changes as TF32 parts, the product adds them into g
+    parts = {}  # block length -> [2, N, length]: a step's product has read them before the next step writes
     for _ in range(passes):
         start = c.clone() if wait else None
         for b0 in range(0, k, BLOCK_COLUMNS):
             b1 = min(b0 + BLOCK_COLUMNS, k)
-            gb = g[:, b0:b1].contiguous()
-            dw_block = torch.empty(n_rows, b1 - b0, dtype=torch.float32, device=dev)
-            refine_kernel.refine_block(gb, c, lo_x, st_x, top, hs, b0, b1 - b0, dw_block)
-            if use_tc and (b1 - b0) % 4 == 0:
-                refine_kernel.gemm_tc(refine_kernel.split_tf32(dw_block), hs_split[:, :, b0:b1], g, status, accumulate=True)
+            if use_tc:
+                if b1 - b0 not in parts:
+                    parts[b1 - b0] = torch.empty(2, n_rows, b1 - b0, dtype=torch.float32, device=dev)
+                dw_split = parts[b1 - b0]
+                refine_kernel.refine_block_in_place(g, c, lo_x, st_x, top, hs, b0, b1 - b0, dw_split)
+                refine_kernel.gemm_tc(dw_split, hs_split[:, :, b0:b1], g, status, accumulate=True)
             else:
+                gb = g[:, b0:b1].contiguous()
+                dw_block = torch.empty(n_rows, b1 - b0, dtype=torch.float32, device=dev)
+                refine_kernel.refine_block(gb, c, lo_x, st_x, top, hs, b0, b1 - b0, dw_block)
                 refine_kernel.gemm(dw_block, hs[b0:b1], g, alpha=1.0, beta=1.0)
         if wait and bool((c == start).all()):
             break

@@ -213,3 +213,28 @@ def test_refinement_of_tensors_side_by_side_equals_one_by_one():
             assert torch.equal(getattr(t, f), getattr(u, f)), f
         assert torch.equal(t.blk_params, p.blk_params)  # ladders are never touched
     assert any(not torch.equal(t.codes, p.codes) for t, p in zip(together, plain))  # the sweeps did move codes
+
+
+@pytest.mark.parametrize("n", [37, 148 * 64 + 5])
+def test_block_in_place_equals_block_then_split(n):
+    """The folded entry point (slice of g read where it lies, changes written as TF32 parts) against
+    the plain one followed by the split, for both row mappings: same codes, same parts."""
+    from hi2_b200 import refine_kernel
+
+    g = torch.Generator().manual_seed(n)
+    k, b0, length = 384, 128, 128
+    a = torch.randn(k, k, generator=g)
+    hs = (a @ a.T / k).to(DEV).contiguous()
+    c = torch.randint(0, 16, (n, k), generator=g).float().to(DEV)
+    lo = (torch.randn(n, k, generator=g) * 0.1).half().float().to(DEV)
+    st = (torch.rand(n, k, generator=g) * 0.05).half().float().to(DEV)
+    top = torch.full((n,), 15.0, device=DEV)
+    gfull = torch.randn(n, k, generator=g).to(DEV)
+    c1, c2 = c.clone(), c.clone()
+    dwb = torch.empty(n, length, device=DEV)
+    refine_kernel.refine_block(gfull[:, b0 : b0 + length].contiguous(), c1, lo, st, top, hs, b0, length, dwb)
+    want = refine_kernel.split_tf32(dwb)
+    parts = torch.full((2, n, length), 7.0, device=DEV)
+    refine_kernel.refine_block_in_place(gfull, c2, lo, st, top, hs, b0, length, parts)
+    assert torch.equal(c1, c2) and torch.equal(parts, want)
+    assert bool((dwb != 0).any())
