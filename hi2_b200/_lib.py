@@ -161,8 +161,15 @@ def ptr(t: torch.Tensor | None):
 def stream(device=None) -> StreamArg:
     """The current CUDA stream of ``device`` (default: the current device), tagged with the
     device's index."""
+    if _raw_stream is not None:  # the handle without building a Stream object: a few microseconds per launch
+        dev = torch.device(device) if device is not None else None
+        index = dev.index if dev is not None and dev.index is not None else torch.cuda.current_device()
+        return StreamArg(_raw_stream(index), index)
     st = torch.cuda.current_stream(device)
     return StreamArg(st.cuda_stream, st.device.index)
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def upload(t: torch.Tensor, dev: torch.device, dtype: torch.dtype | None = None) -> torch.Tensor:
