@@ -54,7 +54,7 @@ SIGNATURES = {
     "hi2_gemm_tf32x3": (_I, [_L, _L, _L, _P, _P, _L, _P, _P, _L, _P, _L, _I, _P, _P]),
     "hi2_ladder_sse": (_I, [_P, _P, _L, _P, _P, _P, _L, _L, _L, _I, _P, _P]),
     "hi2_refine_block": (_I, [_P, _I, _P, _P, _P, _P, _P, _L, _L, _L, _P, _P]),
-    "hi2_refine_block_in_place": (_I, [_P, _I, _P, _P, _P, _P, _P, _L, _L, _L, _P, _P, _P]),
+    "hi2_refine_block_in_place": (_I, [_P, _I, _P, _P, _P, _P, _P, _L, _L, _L, _P, _P, _L, _P]),
     "hi2_gemm_f32": (_I, [_I, _I, _L, _L, _L, _F, _P, _L, _P, _L, _F, _P, _L, _P]),
     "hi2_hessian_workspace_bytes": (_Z, [_L, _L, _I]),
     "hi2_hessian_accumulate": (_I, [_P, _I, _L, _L, _P, _P, _Z, _P]),

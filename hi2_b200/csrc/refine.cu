@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(ROWS_PER_CTA, 3)
 refine_block_kernel(const float* __restrict__ gb, int64_t ldg, int len, float* __restrict__ c,
                     const float* __restrict__ lo, const float* __restrict__ st,
                     const float* __restrict__ top, const float* __restrict__ hs, int64_t n_rows,
-                    int64_t k, int64_t b0, float* __restrict__ dwb, float* __restrict__ dw_lo) {
+                    int64_t k, int64_t b0, float* __restrict__ dwb, float* __restrict__ dw_lo, int64_t lddw) {
   extern __shared__ float4 h_stage4[];
   float* h_stage = reinterpret_cast<float*>(h_stage4);
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -160,8 +160,8 @@ refine_block_kernel(const float* __restrict__ gb, int64_t ldg, int len, float* _
   float* crow = c + row * k + b0;
   const float* lorow = lo + row * k + b0;
   const float* strow = st + row * k + b0;
-  float* dwrow = dwb + row * len;
-  float* dwlrow = dw_lo ? dw_lo + row * len : nullptr;
+  float* dwrow = dwb + row * lddw;
+  float* dwlrow = dw_lo ? dw_lo + row * lddw : nullptr;
 
   float2 g[LMAX / 2];
 #pragma unroll
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(WARP_ROWS_PER_CTA * 32)
 refine_block_warp_kernel(const float* __restrict__ gb, int64_t ldg, int len, float* __restrict__ c,
                     const float* __restrict__ lo, const float* __restrict__ st,
                     const float* __restrict__ top, const float* __restrict__ hs, int64_t n_rows,
-                    int64_t k, int64_t b0, float* __restrict__ dwb, float* __restrict__ dw_lo) {
+                    int64_t k, int64_t b0, float* __restrict__ dwb, float* __restrict__ dw_lo, int64_t lddw) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * WARP_ROWS_PER_CTA + (threadIdx.x >> 5);
   if (row >= n_rows) return;
@@ -261,7 +261,7 @@ refine_block_warp_kernel(const float* __restrict__ gb, int64_t ldg, int len, flo
 
   if (mine) {
     *reinterpret_cast<float4*>(c + base) = make_float4(cj[0], cj[1], cj[2], cj[3]);
-    store_dw(dwb + row * len + c0, dw_lo ? dw_lo + row * len + c0 : nullptr, dw_keep[0], dw_keep[1], dw_keep[2],
+    store_dw(dwb + row * lddw + c0, dw_lo ? dw_lo + row * lddw + c0 : nullptr, dw_keep[0], dw_keep[1], dw_keep[2],
              dw_keep[3]);
   }
 }
@@ -273,11 +273,11 @@ namespace hi2 {
 namespace {
 int launch_refine_block(const float* gb, int64_t ldg, int len, float* c, const float* lo, const float* st,
                         const float* top, const float* hs, int64_t n_rows, int64_t k, int64_t b0, float* dwb,
-                        float* dw_lo, cudaStream_t stream) {
+                        float* dw_lo, int64_t lddw, cudaStream_t stream) {
   if (n_rows < (int64_t)148 * ROWS_PER_CTA) {  // too few rows to fill the SMs at a lane per row
     const unsigned wgrid = (unsigned)ceil_div(n_rows, WARP_ROWS_PER_CTA);
     refine_block_warp_kernel<<<wgrid, WARP_ROWS_PER_CTA * 32, 0, stream>>>(gb, ldg, len, c, lo, st, top, hs, n_rows,
-                                                                            k, b0, dwb, dw_lo);
+                                                                            k, b0, dwb, dw_lo, lddw);
     return check_launch("refine_block");
   }
   const unsigned grid = (unsigned)ceil_div(n_rows, ROWS_PER_CTA);
@@ -285,7 +285,7 @@ int launch_refine_block(const float* gb, int64_t ldg, int len, float* c, const f
   if (cudaFuncSetAttribute(refine_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return fail(HI2_ERR_LAUNCH, "refine_block: cannot reserve shared memory");
   refine_block_kernel<<<grid, ROWS_PER_CTA, smem, stream>>>(gb, ldg, len, c, lo, st, top, hs, n_rows, k, b0, dwb,
-                                                             dw_lo);
+                                                             dw_lo, lddw);
   return check_launch("refine_block");
 }
 }  // namespace
@@ -303,22 +303,23 @@ extern "C" int hi2_refine_block(const float* gb, int len, float* c, const float*
   HI2_REQUIRE(aligned16(gb) && aligned16(c) && aligned16(lo) && aligned16(st) && aligned16(hs) &&
                   aligned16(dwb),
               "refine_block: buffers must be 16-byte aligned");
-  return launch_refine_block(gb, len, len, c, lo, st, top, hs, n_rows, k, b0, dwb, nullptr,
+  return launch_refine_block(gb, len, len, c, lo, st, top, hs, n_rows, k, b0, dwb, nullptr, len,
                              static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int hi2_refine_block_in_place(const float* g, int len, float* c, const float* lo, const float* st,
                                          const float* top, const float* hs, int64_t n_rows, int64_t k,
-                                         int64_t b0, float* dw_hi, float* dw_lo, void* stream) {
+                                         int64_t b0, float* dw_hi, float* dw_lo, int64_t lddw, void* stream) {
   using namespace hi2;
   HI2_REQUIRE(k > 0 && k % 16 == 0, "refine_block_in_place: k must be a positive multiple of 16");
   HI2_REQUIRE(len > 0 && len <= LMAX && len % 16 == 0, "refine_block_in_place: block length must be 16..128");
   HI2_REQUIRE(b0 >= 0 && b0 % 16 == 0 && b0 + len <= k, "refine_block_in_place: block outside the row");
+  HI2_REQUIRE(lddw >= len && lddw % 4 == 0, "refine_block_in_place: lddw must cover the block and be a multiple of 4");
   if (n_rows == 0) return HI2_OK;
   HI2_REQUIRE(g && c && lo && st && top && hs && dw_hi && dw_lo, "refine_block_in_place: null pointer");
   HI2_REQUIRE(aligned16(g) && aligned16(c) && aligned16(lo) && aligned16(st) && aligned16(hs) &&
                   aligned16(dw_hi) && aligned16(dw_lo),
               "refine_block_in_place: buffers must be 16-byte aligned");
-  return launch_refine_block(g + b0, k, len, c, lo, st, top, hs, n_rows, k, b0, dw_hi, dw_lo,
+  return launch_refine_block(g + b0, k, len, c, lo, st, top, hs, n_rows, k, b0, dw_hi, dw_lo, lddw,
                              static_cast<cudaStream_t>(stream));
 }

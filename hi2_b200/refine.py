@@ -14,6 +14,8 @@ from . import _lib, refine_kernel
 from .format import decode_params
 
 BLOCK_COLUMNS = 128
+GROUP_BLOCKS = 4  # blocks whose moves reach the far columns of g in one product
+GROUP_MIN_ELEMS = 1 << 25  # rows x columns from which grouping pays (below, a step is a latency chain)
 TC_MIN_K = 512  # inputs at least this wide take the tensor-core products
 
 
@@ -62,24 +64,49 @@ def _sweeps(w, codes, lo_x, st_x, top, hs, passes: int, use_tc: bool | None, wai
     else:
         refine_kernel.gemm(e, hs, g)
     del e
-    # with tensor-core products a step of the sweep is two launches: the block kernel reads its slice
-    # of g in place and leaves the changes as TF32 parts, the product adds them into g
-    parts = {}  # block length -> [2, N, length]: a step's product has read them before the next step writes
+    # With tensor-core products the block kernel reads its slice of g in place and leaves the changes
+    # as TF32 parts, and g is brought up to date lazily, as the GPTQ loop does: after a block only the
+    # later blocks of its group of GROUP_BLOCKS need its moves now (a narrow product); the columns
+    # outside the group take the moves of the whole group in one product with a reduction of up to
+    # 512 (a 128 KiB tile of g is then read and written once per 100 MFLOP instead of once per 25);
+    # the group's own columns at or before each block, needed by the next sweep only, follow per
+    # column block.  The contributions to every g are the same, in another order.  Few rows make
+    # every step a latency chain, where more launches cost more than the better products gain: then
+    # a group is one block and its update one product.
+    width = (GROUP_BLOCKS if n_rows * k >= GROUP_MIN_ELEMS else 1) * BLOCK_COLUMNS
+    moves = torch.empty(2, n_rows, min(width, k), dtype=torch.float32, device=dev) if use_tc else None
     for _ in range(passes):
         start = c.clone() if wait else None
-        for b0 in range(0, k, BLOCK_COLUMNS):
-            b1 = min(b0 + BLOCK_COLUMNS, k)
-            if use_tc:
-                if b1 - b0 not in parts:
-                    parts[b1 - b0] = torch.empty(2, n_rows, b1 - b0, dtype=torch.float32, device=dev)
-                dw_split = parts[b1 - b0]
-                refine_kernel.refine_block_in_place(g, c, lo_x, st_x, top, hs, b0, b1 - b0, dw_split)
-                refine_kernel.gemm_tc(dw_split, hs_split[:, :, b0:b1], g, status, accumulate=True)
-            else:
+        if not use_tc:
+            for b0 in range(0, k, BLOCK_COLUMNS):
+                b1 = min(b0 + BLOCK_COLUMNS, k)
                 gb = g[:, b0:b1].contiguous()
                 dw_block = torch.empty(n_rows, b1 - b0, dtype=torch.float32, device=dev)
                 refine_kernel.refine_block(gb, c, lo_x, st_x, top, hs, b0, b1 - b0, dw_block)
                 refine_kernel.gemm(dw_block, hs[b0:b1], g, alpha=1.0, beta=1.0)
+            if wait and bool((c == start).all()):
+                break
+            continue
+        for g0 in range(0, k, width):
+            g1 = min(g0 + width, k)
+            for b0 in range(g0, g1, BLOCK_COLUMNS):
+                b1 = min(b0 + BLOCK_COLUMNS, g1)
+                dw = moves[:, :, b0 - g0 : b1 - g0]
+                refine_kernel.refine_block_in_place(g, c, lo_x, st_x, top, hs, b0, b1 - b0, dw)
+                if b1 < g1:
+                    refine_kernel.gemm_tc(dw, hs_split[:, b1:g1, b0:b1], g[:, b1:g1], status, accumulate=True)
+            if width == BLOCK_COLUMNS:  # groups of one block: the whole update in one product
+                refine_kernel.gemm_tc(moves[:, :, : g1 - g0], hs_split[:, :, g0:g1], g, status, accumulate=True)
+                continue
+            group = moves[:, :, : g1 - g0]
+            if g0 > 0:
+                refine_kernel.gemm_tc(group, hs_split[:, :g0, g0:g1], g[:, :g0], status, accumulate=True)
+            if g1 < k:
+                refine_kernel.gemm_tc(group, hs_split[:, g1:, g0:g1], g[:, g1:], status, accumulate=True)
+            for b0 in range(g0, g1, BLOCK_COLUMNS):
+                b1 = min(b0 + BLOCK_COLUMNS, g1)
+                refine_kernel.gemm_tc(moves[:, :, b0 - g0 : g1 - g0], hs_split[:, b0:b1, b0:g1], g[:, b0:b1], status,
+                                      accumulate=True)
         if wait and bool((c == start).all()):
             break
     if wait and use_tc and int(status.item()):

@@ -45,21 +45,25 @@ def refine_block(gb, c, lo_x, st_x, top, hs, b0, length, dw_block) -> None:
 
 def refine_block_in_place(g, c, lo_x, st_x, top, hs, b0, length, dw_split) -> None:
     """:func:`refine_block` reading the block's slice of ``g [N, K]`` where it lies and writing the
-    changes as TF32 parts ``dw_split [2, N, length]``, the left operand of :func:`gemm_tc`."""
+    changes as TF32 parts ``dw_split [2, N, length]``, the left operand of :func:`gemm_tc`;
+    ``dw_split`` may be a column slice of a wider ``[2, N, W]`` buffer (unit column stride)."""
     dev = _lib.need_cuda(g, c, lo_x, st_x, top, hs, dw_split)
-    for t, name in ((g, "g"), (c, "c"), (lo_x, "lo"), (st_x, "st"), (top, "top"), (hs, "hs"), (dw_split, "dw_split")):
+    for t, name in ((g, "g"), (c, "c"), (lo_x, "lo"), (st_x, "st"), (top, "top"), (hs, "hs")):
         if t.dtype != torch.float32 or not t.is_contiguous():
             raise ValueError(f"refine_block_in_place: {name} must be a contiguous float32 tensor")
     n, k = c.shape
     if not (0 < length <= BLOCK_COLUMNS) or g.shape != (n, k) or dw_split.shape != (2, n, length):
         raise ValueError("refine_block_in_place: bad block length or shape")
+    if dw_split.dtype != torch.float32 or dw_split.stride(2) != 1 or (n > 1 and dw_split[0].stride(0) != dw_split[1].stride(0)):
+        raise ValueError("refine_block_in_place: dw_split must be float32 with unit column stride")
     if b0 < 0 or b0 + length > k or hs.shape != (k, k):
         raise ValueError("refine_block_in_place: block outside the row or hs of the wrong shape")
     if n == 0:
         return
     _lib.call(
         "hi2_refine_block_in_place", _lib.ptr(g), int(length), _lib.ptr(c), _lib.ptr(lo_x), _lib.ptr(st_x),
-        _lib.ptr(top), _lib.ptr(hs), n, k, int(b0), _lib.ptr(dw_split[0]), _lib.ptr(dw_split[1]), _lib.stream(dev),
+        _lib.ptr(top), _lib.ptr(hs), n, k, int(b0), _lib.ptr(dw_split[0]), _lib.ptr(dw_split[1]),
+        dw_split.stride(1), _lib.stream(dev),
     )
 
 

@@ -179,11 +179,12 @@ int hi2_refine_block(const float* gb, int len, float* c, const float* lo, const 
                      float* dwb, void* stream);
 /* The same block for the sweep of hi2/refine.py:60-84 with two copies folded in: the block's slice
  * of g is read where it lies (g [n_rows, k], columns b0 .. b0+len), and the changes are written as
- * the two TF32 parts dw_hi/dw_lo [n_rows, len] that hi2_gemm_tf32x3 takes for g += dw Hs[b0:b0+len]
- * (dw_hi + dw_lo differs from dw by at most 2^-22 |dw|).  Same decisions as hi2_refine_block. */
+ * the two TF32 parts dw_hi/dw_lo (rows of len floats, lddw floats apart: the parts of several
+ * blocks can lie side by side) that hi2_gemm_tf32x3 takes for g += dw Hs[b0:b0+len] (dw_hi + dw_lo
+ * differs from dw by at most 2^-22 |dw|).  Same decisions as hi2_refine_block. */
 int hi2_refine_block_in_place(const float* g, int len, float* c, const float* lo, const float* st,
                               const float* top, const float* hs, int64_t n_rows, int64_t k,
-                              int64_t b0, float* dw_hi, float* dw_lo, void* stream);
+                              int64_t b0, float* dw_hi, float* dw_lo, int64_t lddw, void* stream);
 
 /* ---- dense helpers of the path -------------------------------------------------------------
  * C = alpha * op(A) op(B) + beta * C in fp32 (fused multiply-add accumulation, fp32 operands):

@@ -238,3 +238,21 @@ def test_block_in_place_equals_block_then_split(n):
     refine_kernel.refine_block_in_place(gfull, c2, lo, st, top, hs, b0, length, parts)
     assert torch.equal(c1, c2) and torch.equal(parts, want)
     assert bool((dwb != 0).any())
+
+
+def test_grouped_updates_of_the_sweep_against_the_oracle(monkeypatch):
+    """Tensors with many rows bring g up to date lazily, in groups of four blocks (near columns after
+    every block, far columns once per group, the group's own columns for the next sweep): forced
+    here on a small case whose width is no multiple of the group (1152 = 2 groups + 1 block), against
+    the oracle's fp32 column loop and against the block-by-block update."""
+    from hi2_b200 import refine
+    from hi2_b200.refine import refine_groups
+
+    groups, hs = _groups(29, k=1152, rows=(150, 70))
+    want = po.refine_groups(groups, hs, 2)
+    plain = refine_groups(_to_dev(groups), hs.to(DEV), 2)
+    monkeypatch.setattr(refine, "GROUP_MIN_ELEMS", 0)
+    got = refine_groups(_to_dev(groups), hs.to(DEV), 2)
+    for g, w_, p in zip(got, want, plain):
+        assert agreement(g, w_) >= 0.999, agreement(g, w_)
+        assert agreement(g, p.cpu()) >= 0.9995
