@@ -233,7 +233,7 @@ def test_install_wires_an_unmodified_hi2():
     import subprocess
     import sys
 
-    ref = "/root/reference"
+    ref = str(ROOT.parent / "reference")
     if not (ROOT.parent / "reference" / "hi2" / "calibrate.py").exists():
         pytest.skip("no hi2 checkout beside the repository")
     code = f"""
