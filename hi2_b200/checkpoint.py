@@ -10,8 +10,11 @@ temporary file and renamed, and a JSON marker beside it carrying the file's SHA-
 report per tensor.  What is B200-specific: a batch is encoded with the packed buffers LEFT ON THE
 DEVICE, copied to pinned host memory on a copy stream while the next batch is being encoded, and
 only then handed to the safetensors writer (the reference assembles on the device but copies
-synchronously, hi2/format.py:172-184).  Reading source shards, resuming, validation of foreign
-files and the dense / portable exports stay with the reference's ``checkpoint.py``.
+synchronously, hi2/format.py:172-184).  With ``moe_layout="stacked"`` the routed experts of a layer
+and projection group are written as one stack (hi2/stack.py, ``--moe-layout stacked``), assembled on
+the device from the packed buffers of the shard before the copy to the host.  Reading source
+shards, resuming, validation of foreign files and the dense / portable exports stay with the
+reference's ``checkpoint.py``.
 """
 
 from __future__ import annotations
@@ -25,6 +28,8 @@ import torch
 
 from .calibrate import Config, EncodeRequest, encode_many
 from .format import FIELDS, HI2Tensor, dequantize
+from .moe import expert_parts
+from .stack import LAYOUTS, MARK, PART_GROUP, split_stack, stack_packed
 
 ENCODE_BATCH_BYTES = int(float(os.environ.get("HI2_ENCODE_BATCH_GB", "6")) * 2**30)
 
@@ -78,31 +83,28 @@ def _report(t: HI2Tensor, table) -> dict:
 
 
 class _HostCopy:
-    """Packed buffers of one batch on their way to pinned host memory (a copy stream beside the
-    encode of the next batch)."""
+    """Packed buffers of one batch (and, in the stacked layout, the expert stacks of a shard) on their
+    way to pinned host memory, on a copy stream beside the encode of the next batch."""
 
-    def __init__(self, packed: dict, stream: torch.cuda.Stream):
+    def __init__(self, packed: dict, stream: torch.cuda.Stream, stacks: dict | None = None):
         self.done = torch.cuda.Event()
-        self.host = {}
+        self.host, self.stacks = {}, {}
         stream.wait_stream(torch.cuda.current_stream())
+
+        def pinned(v):
+            if v is None or not v.is_cuda:
+                return v
+            h = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
+            h.copy_(v, non_blocking=True)
+            v.record_stream(stream)
+            return h
+
         with torch.cuda.stream(stream):
             for name, t in packed.items():
-                fields = {}
-                for f in FIELDS:
-                    v = getattr(t, f)
-                    if v.is_cuda:
-                        h = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
-                        h.copy_(v, non_blocking=True)
-                        v.record_stream(stream)
-                        v = h
-                    fields[f] = v
-                cs = t.col_scale
-                if cs is not None and cs.is_cuda:
-                    h = torch.empty(cs.shape, dtype=cs.dtype, pin_memory=True)
-                    h.copy_(cs, non_blocking=True)
-                    cs.record_stream(stream)
-                    cs = h
-                self.host[name] = HI2Tensor(**fields, shape=t.shape, col_scale=cs)
+                self.host[name] = HI2Tensor(**{f: pinned(getattr(t, f)) for f in FIELDS}, shape=t.shape,
+                                            col_scale=pinned(t.col_scale))
+            for base, arrays in (stacks or {}).items():
+                self.stacks[base] = {f: pinned(v) for f, v in arrays.items()}
             self.done.record(stream)
 
     def result(self) -> dict:
@@ -110,21 +112,25 @@ class _HostCopy:
         return self.host
 
 
-def write_shard(path: Path, packed: dict, passthrough: dict | None = None, tables: dict | None = None) -> dict:
+def write_shard(path: Path, packed: dict, passthrough: dict | None = None, tables: dict | None = None,
+                stacks: dict | None = None, reports: dict | None = None) -> dict:
     """One safetensors file with the packed tensors of ``packed`` (``{'<base>.weight': HI2Tensor}``, on
-    the host) and the tensors of ``passthrough`` as they are; written to ``<path>.tmp`` and renamed;
-    ``<path>.done.json`` records the SHA-256 of the file, its tensor names and a report per tensor.
-    Returns the marker."""
+    the host), the expert stacks of ``stacks`` (``{stack base: arrays}``, :func:`hi2_b200.stack.build_stack`)
+    and the tensors of ``passthrough`` as they are; written to ``<path>.tmp`` and renamed;
+    ``<path>.done.json`` records the SHA-256 of the file, its tensor names and a report per tensor
+    (``reports`` carries those of tensors that went into stacks).  Returns the marker."""
     from safetensors.torch import save_file
 
     path = Path(path)
     path.parent.mkdir(parents=True, exist_ok=True)
-    out, reports = {}, {}
+    out, reports = {}, dict(reports or {})
     for name, t in packed.items():
         base = name.removesuffix(".weight")
         out.update({k: v.contiguous() for k, v in to_tensors(t, base).items()})
         if tables is not None and name in tables:
             reports[name] = _report(t, tables[name])
+    for base, arrays in (stacks or {}).items():
+        out.update({f"{base}.hi2_{f}": v.cpu().contiguous() for f, v in arrays.items()})
     for name, v in (passthrough or {}).items():
         out[name] = v.detach().cpu().contiguous()
     tmp = path.with_name(path.name + ".tmp")
@@ -140,20 +146,27 @@ def write_shard(path: Path, packed: dict, passthrough: dict | None = None, table
 
 
 def write_checkpoints(shards: dict, tables: dict, picks: dict, sigma_of, cfg: Config, out_dir,
-                      budget: int = ENCODE_BATCH_BYTES, log=print, factors: dict | None = None) -> dict:
+                      budget: int = ENCODE_BATCH_BYTES, log=print, factors: dict | None = None,
+                      moe_layout: str = "per-expert") -> dict:
     """Encode and write a model shard by shard.
 
     ``shards``: ``{file name: {tensor name: tensor on the device}}`` in source order; tensors with a
     table are quantised with ``picks[name]``, the others are passed through.  ``sigma_of(name)`` returns
     ``(second moment sum or None, tokens, sigma_id, ColumnStats or None)`` for a tensor - what
     :class:`hi2_b200.layerwise.DeviceSink` holds; ``factors`` (optional) its ``factors``: inverse
-    factors already started while tabulating, by ``sigma_id``.  Returns ``{file name: marker}``."""
+    factors already started while tabulating, by ``sigma_id``.  ``moe_layout="stacked"`` writes the
+    routed experts of every layer and projection group that is complete in a shard as one stack; the
+    packed buffers of the shard then stay on the device until the shard is encoded (a few GB), the
+    stacks are put together there and copied to the host once.  Returns ``{file name: marker}``."""
+    if moe_layout not in LAYOUTS:
+        raise ValueError(f"moe_layout must be one of {LAYOUTS} (got {moe_layout!r})")
     out_dir = Path(out_dir)
     copy_stream = torch.cuda.Stream()
     markers = {}
     for shard, tensors in shards.items():
         quant = [n for n in tensors if n in tables]
         pending: list[_HostCopy] = []
+        on_device: dict = {}
         for group in batches(quant, tables, budget):
             reqs = []
             for n in group:
@@ -161,20 +174,33 @@ def write_checkpoints(shards: dict, tables: dict, picks: dict, sigma_of, cfg: Co
                 reqs.append(EncodeRequest(tensors[n], stats, tables[n], picks[n], sigma=sigma, sigma_id=sid,
                                           sigma_n=max(int(tokens), 1)))
             packed = dict(zip(group, encode_many(reqs, cfg, to_host=False, factors=factors)))
-            pending.append(_HostCopy(packed, copy_stream))  # D2H runs beside the next group's encode
-        host: dict = {}
+            if moe_layout == "stacked":
+                on_device.update(packed)
+            else:
+                pending.append(_HostCopy(packed, copy_stream))  # D2H runs beside the next group's encode
+        reports = {}
+        if on_device:
+            stacks, rest = stack_packed(on_device)
+            reports = {n: _report(t, tables[n]) for n, t in on_device.items() if n not in rest}
+            pending.append(_HostCopy(rest, copy_stream, stacks))
+            del on_device
+        host, host_stacks = {}, {}
         for p in pending:
             host.update(p.result())
-        markers[shard] = write_shard(out_dir / shard, host, {n: v for n, v in tensors.items() if n not in tables}, tables)
-        log(f"{shard}: {len(quant)} tensors encoded, {len(tensors) - len(quant)} passed through")
+            host_stacks.update(p.stacks)
+        markers[shard] = write_shard(out_dir / shard, host, {n: v for n, v in tensors.items() if n not in tables}, tables,
+                                     host_stacks, reports)
+        log(f"{shard}: {len(quant)} tensors encoded ({len(host_stacks)} expert stacks), "
+            f"{len(tensors) - len(quant)} passed through")
     return markers
 
 
 def verify_checkpoint(out_dir, shards: dict, tables: dict, rtol: float = 0.35, log=print) -> dict:
     """Read every written shard back, check the marker's digest and tensor coverage, rebuild each
-    packed tensor, dequantise it on the device (:func:`hi2_b200.format.dequantize`) and compare it
-    with the source weight: ``{tensor name: relative Frobenius error}``; raises on a digest or
-    coverage mismatch or an error above ``rtol``."""
+    packed tensor (from its own arrays, or out of the expert stack that holds it), dequantise it on
+    the device (:func:`hi2_b200.format.dequantize`) and compare it with the source weight:
+    ``{tensor name: relative Frobenius error}``; raises on a digest or coverage mismatch or an error
+    above ``rtol``."""
     from safetensors import safe_open
 
     out_dir = Path(out_dir)
@@ -185,16 +211,33 @@ def verify_checkpoint(out_dir, shards: dict, tables: dict, rtol: float = 0.35, l
         if marker.get("sha256") != file_digest(path):
             raise ValueError(f"{path}: digest differs from its marker")
         with safe_open(str(path), "pt") as f:
-            if set(f.keys()) != set(marker["tensor_names"]):
+            keys = set(f.keys())
+            if keys != set(marker["tensor_names"]):
                 raise ValueError(f"{path}: tensor coverage differs from its marker")
+            members: dict = {}  # stack base -> its pieces, split once
+
+            def packed_tensor(base):
+                if f"{base}.hi2_codes" in keys:
+                    return from_tensors({k: f.get_tensor(k) for k in keys if k.startswith(base + ".hi2_")}, base)
+                ep = expert_parts(base)
+                if ep is None or ep[2] not in PART_GROUP:
+                    raise ValueError(f"{path}: no packed tensor for {base}")
+                group, part = PART_GROUP[ep[2]]
+                stack = f"{ep[0]}.{group}"
+                if f"{stack}.hi2_{MARK}" not in keys:
+                    raise ValueError(f"{path}: no packed tensor and no stack for {base}")
+                if stack not in members:
+                    arrays = {k.rsplit(".hi2_", 1)[1]: f.get_tensor(k) for k in keys if k.startswith(stack + ".hi2_")}
+                    nparts = sum(1 for p, (g, _) in PART_GROUP.items() if g == group)
+                    members[stack] = split_stack(arrays, nparts)
+                return members[stack][ep[1]][part]
+
             for name, w in tensors.items():
                 if name not in tables:
                     if not torch.equal(f.get_tensor(name), w.detach().cpu()):
                         raise ValueError(f"{path}: {name} was not passed through unchanged")
                     continue
-                base = name.removesuffix(".weight")
-                d = {k: f.get_tensor(k) for k in f.keys() if k.startswith(base + ".hi2_")}  # noqa: SIM118
-                rec = dequantize(from_tensors(d, base), w.device)
+                rec = dequantize(packed_tensor(name.removesuffix(".weight")), w.device)
                 err = float((rec - w.double()).norm() / w.double().norm().clamp_min(1e-30))
                 errors[name] = err
                 if not err <= rtol:

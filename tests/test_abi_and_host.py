@@ -309,3 +309,50 @@ def test_a_stalled_rank_ends_the_others_collective_by_timeout(tmp_path):
     procs[1].communicate()
     assert procs[0].returncode == 7 and "collective failed" in out0, out0
     assert took < 60, took
+
+
+def test_stacked_expert_layout_against_the_reference_fixture():
+    """``stack.build_stack`` / ``split_stack`` and the naming rules against what hi2's own functions
+    made of the same packed tensors (``tests/golden/stack_golden.pt``): every array byte for byte,
+    the inverse, and the refusals."""
+    from hi2_b200 import stack
+    from hi2_b200.format import FIELDS, HI2Tensor
+
+    gold = torch.load(ROOT / "tests" / "golden" / "stack_golden.pt")
+
+    def tensor(rec):
+        return HI2Tensor(**rec["fields"], shape=tuple(rec["shape"]), col_scale=rec["col_scale"])
+
+    for group in ("gate_up", "down"):
+        experts = [[tensor(p) for p in parts] for parts in gold[group]["experts"]]
+        want = gold[group]["stack"]
+        got = stack.build_stack(experts)
+        assert set(got) == set(want) and stack.GROUPS[group] == tuple(gold[group]["parts"])
+        for f in want:
+            assert got[f].dtype == want[f].dtype and torch.equal(got[f], want[f]), (group, f)
+        back = stack.split_stack(got, len(experts[0]))
+        for parts, again in zip(experts, back):
+            for a, b in zip(parts, again):
+                assert a.shape == b.shape and all(torch.equal(getattr(a, f), getattr(b, f)) for f in FIELDS)
+                assert (a.col_scale is None) == (b.col_scale is None)
+                assert a.col_scale is None or torch.equal(a.col_scale, b.col_scale)
+    names = gold["names"]
+    single, stacked = stack.hi2_bases(names["names"])
+    assert single == names["single"] and stacked == names["stacked"]
+    assert stack.stack_groups(single) == names["groups"]
+    assert stack.hi2_bases([f"a.experts.gate_up.hi2_{f}" for f in (*FIELDS, stack.MARK)]) == ([], ["a.experts.gate_up"])
+    # refusals: parts of one expert with different flags, smoothing for some experts only, unequal K
+    experts = [[tensor(p) for p in parts] for parts in gold["gate_up"]["experts"]]
+    experts[1][1].had = 1 - experts[1][1].had
+    with pytest.raises(stack.StackError):
+        stack.build_stack(experts)
+    experts = [[tensor(p) for p in parts] for parts in gold["gate_up"]["experts"]]
+    for p in experts[2]:
+        p.col_scale = None
+    with pytest.raises(stack.StackError):
+        stack.build_stack(experts)
+    with pytest.raises(stack.StackError):
+        stack.build_stack([])
+    # an incomplete group (expert 1 lacks up_proj) is not offered for stacking
+    some = [n for n in single if not n.endswith("experts.1.up_proj")]
+    assert "model.layers.0.mlp.experts.gate_up" not in stack.stack_groups(some)
