@@ -4,8 +4,9 @@ hi2/layerwise.py:231-257).
 The encode path treats every expert projection as its own matrix: its second moment sums only the
 tokens routed to it, gate and up of one expert share that sum, and an expert that saw too few
 tokens borrows the pooled sum of its layer for the missing ones.  This module holds that logic for
-accumulators that live in HBM (``HessianStats`` / ``ColumnStats``); checkpoint surgery (unfusing
-3-D expert parameters) is not part of the encode path and is not here.
+accumulators that live in HBM (``HessianStats`` / ``ColumnStats``), and the per-expert view of fused
+3-D expert parameters (hi2/moe.py:53-121) that lets the calibration hooks see, expert by expert, the
+tokens routed there.
 """
 
 from __future__ import annotations
@@ -13,6 +14,7 @@ from __future__ import annotations
 import re
 
 import torch
+from torch import nn
 
 from .hessian import HessianStats
 from .stats import ColumnStats
@@ -110,6 +112,85 @@ def top_up(stats: dict, hess: dict | None, k_of: dict, min_tokens: float, all_re
     return borrowed
 
 
+# ---- per-expert views of fused experts -------------------------------------------------------------
+def _linear_over(weight: torch.Tensor) -> nn.Linear:
+    """An ``nn.Linear`` whose weight IS ``weight`` (a slice of the fused parameter; nothing is copied)."""
+    lin = nn.Linear(weight.shape[1], weight.shape[0], bias=False, device="meta")
+    lin.weight = nn.Parameter(weight, requires_grad=False)
+    return lin
+
+
+class _Expert(nn.Module):
+    def __init__(self, gate, up, down):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = _linear_over(gate), _linear_over(up), _linear_over(down)
+
+
+def is_fused_experts(mod: nn.Module) -> bool:
+    """Experts stored as ``gate_up_proj [E, 2I, H]`` and ``down_proj [E, H, I]`` with an ``act_fn`` and no
+    bias (the layout of recent ``transformers`` MoE blocks)."""
+    gu, dn = getattr(mod, "gate_up_proj", None), getattr(mod, "down_proj", None)
+    return (torch.is_tensor(gu) and torch.is_tensor(dn) and gu.dim() == 3 and dn.dim() == 3
+            and hasattr(mod, "act_fn") and not getattr(mod, "has_bias", False))
+
+
+class ExpertViews(nn.Module):
+    """Drop-in for a fused-experts module: children ``0 .. E-1``, each with ``gate_proj`` / ``up_proj`` /
+    ``down_proj`` Linears over slices of the fused parameters, and the fused module's call
+    ``(hidden_states, top_k_index, top_k_weights)``.  The (token, slot) pairs are sorted by expert
+    once (a stable sort keeps the token order inside an expert) and their counts read back once;
+    every expert that received tokens then runs its three Linears on its own rows, gate and up on
+    the SAME gathered tensor, so hooks on them see one shared input per expert."""
+
+    def __init__(self, fused: nn.Module):
+        super().__init__()
+        gu, down = fused.gate_up_proj.data, fused.down_proj.data
+        n_exp, twice, hidden = gu.shape
+        inner = twice // 2
+        if twice % 2 or tuple(down.shape) != (n_exp, hidden, inner):
+            raise NotImplementedError(f"unsupported fused expert layout: gate_up {tuple(gu.shape)}, down {tuple(down.shape)}")
+        for e in range(n_exp):
+            self.add_module(str(e), _Expert(gu[e, :inner], gu[e, inner:], down[e]))
+        self.n_experts = n_exp
+        self.act_fn = fused.act_fn
+
+    def __len__(self) -> int:
+        return self.n_experts
+
+    def __getitem__(self, e: int) -> nn.Module:
+        return self.get_submodule(str(e))
+
+    def forward(self, hidden_states, top_k_index, top_k_weights):
+        x = hidden_states.reshape(-1, hidden_states.shape[-1])
+        slots = top_k_index.shape[-1]
+        chosen = top_k_index.reshape(-1)
+        order = torch.argsort(chosen, stable=True)
+        counts = (chosen[None, :] == torch.arange(self.n_experts, device=chosen.device)[:, None]).sum(1).tolist()
+        share = top_k_weights.reshape(-1)
+        out = torch.zeros_like(x)
+        start = 0
+        for e, n in enumerate(counts):
+            pairs = order[start : start + n]
+            start += n
+            if n == 0:
+                continue
+            tokens = pairs // slots
+            mine = x.index_select(0, tokens)
+            ex = self[e]
+            y = ex.down_proj(self.act_fn(ex.gate_proj(mine)) * ex.up_proj(mine))
+            out.index_add_(0, tokens, (y * share[pairs, None]).to(out.dtype))
+        return out.reshape(hidden_states.shape)
+
+
+def unfuse_experts(model: nn.Module) -> int:
+    """Replace every fused-experts module of ``model`` by :class:`ExpertViews` in place (the weights
+    stay where they are); returns how many were replaced."""
+    names = [n for n, m in model.named_modules() if is_fused_experts(m)]
+    for n in names:
+        model.set_submodule(n, ExpertViews(model.get_submodule(n)))
+    return len(names)
+
+
 def expert_weights(tables: dict, share_floor: float = 0.05) -> dict:
     """Allocation multiplier of every expert tensor (hi2/moe.py:188-207): an expert's share of its
     group's calibration tokens relative to an even split, floored at ``share_floor``, divided by
@@ -129,4 +210,4 @@ def expert_weights(tables: dict, share_floor: float = 0.05) -> dict:
 
 
 __all__ = ["expert_parts", "group_key", "sibling_leader", "blend", "accumulate_routed", "top_up",
-           "expert_weights", "HessianStats", "ColumnStats"]
+           "expert_weights", "is_fused_experts", "ExpertViews", "unfuse_experts", "HessianStats", "ColumnStats"]

@@ -151,3 +151,17 @@ def toy_llama(layers=2, hidden=64, ffn=128, heads=2, vocab=256, sequences=6, tok
     model = LlamaForCausalLM(cfg).eval()
     ids = torch.randint(0, vocab, (sequences, tokens), generator=gen(seed + 1))
     return model, ids
+
+
+def toy_olmoe(layers=2, hidden=64, ffn=32, heads=2, vocab=128, experts=4, top_k=2, sequences=6, tokens=48, seed=0):
+    """An OLMoE-shaped fp32 toy model (fused 3-D expert parameters, as ``transformers`` stores them)
+    with seeded weights and seeded calibration ids."""
+    from transformers import OlmoeConfig, OlmoeForCausalLM
+
+    cfg = OlmoeConfig(hidden_size=hidden, intermediate_size=ffn, num_hidden_layers=layers, num_attention_heads=heads,
+                      num_key_value_heads=heads, vocab_size=vocab, num_experts=experts, num_experts_per_tok=top_k,
+                      max_position_embeddings=4 * tokens)
+    torch.manual_seed(seed)
+    model = OlmoeForCausalLM(cfg).eval()
+    ids = torch.randint(0, vocab, (sequences, tokens), generator=gen(seed + 1))
+    return model, ids

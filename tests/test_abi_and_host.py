@@ -356,3 +356,38 @@ def test_stacked_expert_layout_against_the_reference_fixture():
     # an incomplete group (expert 1 lacks up_proj) is not offered for stacking
     some = [n for n in single if not n.endswith("experts.1.up_proj")]
     assert "model.layers.0.mlp.experts.gate_up" not in stack.stack_groups(some)
+
+
+def test_expert_views_run_the_fused_experts_forward():
+    """``moe.unfuse_experts`` on an OLMoE-shaped toy model (fused 3-D expert parameters): the model's
+    output is unchanged (and equals what the fixture's generator saw before it unfused), every expert
+    projection becomes a Linear over a slice of the fused parameter (no copy), and gate and up of an
+    expert are handed one and the same tensor."""
+    from hi2_b200 import moe
+    from tests.helpers import toy_olmoe
+
+    gold = torch.load(ROOT / "tests" / "golden" / "layerwise_moe_golden.pt", weights_only=False)
+    model, ids = toy_olmoe()
+    model.load_state_dict(gold["state"])
+    assert torch.equal(ids, gold["ids"])
+    fused = model.model.layers[0].mlp.experts
+    assert moe.is_fused_experts(fused) and not moe.is_fused_experts(model.model.layers[0].mlp)
+    with torch.no_grad():
+        before = model(ids[:2], use_cache=False).logits
+    assert torch.equal(before, gold["logits"])
+    assert moe.unfuse_experts(model) == 2 and moe.unfuse_experts(model) == 0
+    views = model.model.layers[0].mlp.experts
+    assert len(views) == 4 and views[3].down_proj.weight.data_ptr() == fused.down_proj[3].data_ptr()
+    assert views[1].up_proj.weight.data_ptr() == fused.gate_up_proj[1, 32:].data_ptr()
+    seen = {}
+    hooks = [views[e].get_submodule(p).register_forward_pre_hook(
+        lambda _m, args, key=(e, p): seen.setdefault(key, []).append((args[0].data_ptr(), tuple(args[0].shape))))
+        for e in range(4) for p in ("gate_proj", "up_proj")]
+    with torch.no_grad():
+        after = model(ids[:2], use_cache=False).logits
+    for h in hooks:
+        h.remove()
+    assert torch.equal(after, before)
+    assert all(seen[(e, "gate_proj")] == seen[(e, "up_proj")] for e in range(4) if (e, "gate_proj") in seen)
+    names = [n for n, _ in model.named_parameters() if ".experts." in n]
+    assert "model.layers.1.mlp.experts.2.up_proj.weight" in names and moe.expert_parts(names[0]) is not None
