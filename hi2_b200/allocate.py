@@ -37,6 +37,30 @@ def _overhead(tables) -> int:
     )
 
 
+def restrict(t, keep):
+    """``t`` with only the candidates ``(nbits, block)`` that ``keep`` accepts (hi2/allocate.py:49-59):
+    picks made over the result index its shorter candidate list, which is also what the encoder
+    reads.  ``t`` itself when nothing or everything would go."""
+    import dataclasses
+
+    kept = [i for i, cand in enumerate(t.candidates) if keep(cand)]
+    if not kept or len(kept) == len(t.candidates):
+        return t
+    rows = torch.tensor(kept, device=t.sse.device)
+    return dataclasses.replace(t, sse=t.sse.index_select(0, rows), candidates=[t.candidates[i] for i in kept])
+
+
+def force_int8(tables: dict, sens: dict | None, top: int):
+    """The whole-tensor INT8 rule of hi2/allocate.py:62-76: among the tensors that have INT8
+    candidates, the ``top`` most sensitive ones keep ONLY those, every other tensor loses them.
+    Returns ``(tables, names of the chosen tensors)``."""
+    sens = sens or {}
+    eligible = [n for n, t in tables.items() if any(nb == 8 for nb, _ in t.candidates)]
+    chosen = sorted(eligible, key=lambda n: -sens.get(n, 1.0))[:top]
+    out = {n: restrict(t, (lambda c: c[0] == 8) if n in chosen else (lambda c: c[0] != 8)) for n, t in tables.items()}
+    return out, chosen
+
+
 @dataclass
 class Allocation:
     picks: dict  # name -> candidate index per row (int64, on the device of the tables)

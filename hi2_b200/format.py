@@ -249,3 +249,45 @@ def dequantize(t: HI2Tensor, device=None, dtype: torch.dtype = torch.float64) ->
     """Reconstruction in the original basis: the rotation is its own inverse and the smoothing
     vector is divided back out (hi2/format.py:231-239)."""
     return _dequantize(t, device, True, dtype)
+
+
+# ---- the product a decode kernel computes, and the bit accounting of the format ---------------------
+def reference_linear(x: torch.Tensor, t: HI2Tensor, device=None) -> torch.Tensor:
+    """``x [M, K] @ W^T`` the way an inference kernel forms it (hi2/format.py:242-249): the
+    activation is divided by the smoothing vector and rotated with the tensor's flags, then
+    contracted with the stored-basis reconstruction.  fp64, on the device."""
+    dev = torch.device(device) if device is not None else (x.device if x.is_cuda else torch.device("cuda", torch.cuda.current_device()))
+    xd = x.to(dev, torch.float64)
+    if t.col_scale is not None:
+        xd = xd / t.col_scale.to(dev, torch.float64)
+    return fwht_groups(xd.contiguous(), t.had) @ dequantize_stored(t, dev).T
+
+
+def block_bits_per_weight(nbits: int, block: int) -> float:
+    """Code bits plus the two parameter bytes of a block, per weight (row constants not counted)."""
+    return nbits + 16 / block
+
+
+def metadata_bits(row_nbits: torch.Tensor, row_block: torch.Tensor, had: torch.Tensor) -> int:
+    """Bits a loader needs besides the buffers (hi2/format.py:253-265): the rotation flags (one bit when
+    all groups agree, else one per group), per row ``ceil(log2(#code widths))`` bits when the rows
+    use more than one width, and two more per row when they use more than one block size."""
+    flags = had.reshape(-1)
+    bits = 1 if flags.numel() == 0 or bool((flags == flags[0]).all()) else flags.numel()
+    rows = row_nbits.numel()
+    widths = int(torch.unique(row_nbits).numel())
+    if widths > 1:
+        bits += rows * math.ceil(math.log2(widths))
+    if int(torch.unique(row_block).numel()) > 1:
+        bits += 2 * rows
+    return bits
+
+
+def tensor_bpw(t: HI2Tensor) -> float:
+    """Exact bits per weight of a packed tensor: codes and parameter bytes of every row, 48 bits of
+    row constants per row, the metadata above, and 16 bits per column for a smoothing vector."""
+    r, k = t.shape
+    width, block = t.row_nbits.to(torch.float64), t.row_block.to(torch.float64)
+    payload = float((width * k + 16 * k / block).sum())
+    vector = 16 * k if t.col_scale is not None else 0
+    return (payload + 48 * r + metadata_bits(t.row_nbits, t.row_block, t.had) + vector) / (r * k)

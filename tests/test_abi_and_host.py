@@ -391,3 +391,46 @@ def test_expert_views_run_the_fused_experts_forward():
     assert all(seen[(e, "gate_proj")] == seen[(e, "up_proj")] for e in range(4) if (e, "gate_proj") in seen)
     names = [n for n, _ in model.named_parameters() if ".experts." in n]
     assert "model.layers.1.mlp.experts.2.up_proj.weight" in names and moe.expert_parts(names[0]) is not None
+
+
+def test_bit_accounting_and_table_restriction():
+    """``format.block_bits_per_weight / metadata_bits / tensor_bpw`` on hand-made tensors (and against
+    hi2's own functions when a checkout is beside the repository), ``allocate.restrict / force_int8``
+    on tables."""
+    from hi2_b200 import allocate, format as fmt
+    from hi2_b200.calibrate import TensorTable
+
+    assert fmt.block_bits_per_weight(2, 64) == 2.25 and fmt.block_bits_per_weight(4, 16) == 5.0
+    nb = torch.tensor([2, 2, 4, 8], dtype=torch.uint8)
+    bl = torch.tensor([16, 64, 32, 32], dtype=torch.uint8)
+    same = torch.ones(8, dtype=torch.uint8)
+    mixed = torch.tensor([1, 0, 1, 1, 0, 0, 1, 1], dtype=torch.uint8)
+    assert fmt.metadata_bits(nb[:2], bl[:1].repeat(2), same) == 1  # one width, one block size, uniform flags
+    assert fmt.metadata_bits(nb, bl, same) == 1 + 4 * 2 + 4 * 2  # three widths: 2 bits a row; blocks differ: 2 more
+    assert fmt.metadata_bits(nb[1:3], bl[:1].repeat(2), mixed) == 8 + 2 * 1
+    k = 128
+    t = fmt.HI2Tensor(codes=torch.zeros(0, dtype=torch.int32), code_off=torch.zeros(5, dtype=torch.int32),
+                      blk_params=torch.zeros(0, dtype=torch.uint8), param_off=torch.zeros(5, dtype=torch.int32),
+                      row_consts=torch.zeros(4, 3, dtype=torch.float16), row_nbits=nb, row_block=bl, had=mixed,
+                      shape=(4, k), col_scale=torch.ones(k, dtype=torch.float16))
+    payload = sum(int(n) * k + 16 * k // int(b) for n, b in zip(nb, bl))
+    want = (payload + 48 * 4 + (8 + 8 + 8) + 16 * k) / (4 * k)
+    assert abs(fmt.tensor_bpw(t) - want) < 1e-12
+    ref = ROOT.parent / "reference"
+    if (ref / "hi2" / "format.py").exists():
+        code = (f"import sys; sys.path.insert(0, {str(ref)!r}); import torch; from hi2 import format as f; "
+                "nb=torch.tensor([2,2,4,8],dtype=torch.uint8); bl=torch.tensor([16,64,32,32],dtype=torch.uint8); "
+                "h=torch.tensor([1,0,1,1,0,0,1,1],dtype=torch.uint8); print(f.metadata_bits(nb,bl,h), f.metadata_bits(nb,bl,torch.ones(8,dtype=torch.uint8)))")
+        import subprocess
+        import sys
+
+        out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, check=True).stdout.split()
+        assert [int(v) for v in out] == [fmt.metadata_bits(nb, bl, mixed), fmt.metadata_bits(nb, bl, same)]
+    cands = [(2, 32), (4, 32), (8, 32), (8, 64)]
+    tables = {n: TensorTable(n, (3, 64), same[:4], torch.arange(12.0).reshape(4, 3) + i, list(cands), 1.0, 10)
+              for i, n in enumerate(("a", "b", "c"))}
+    tables["d"] = TensorTable("d", (3, 64), same[:4], torch.zeros(2, 3), cands[:2], 1.0, 10)  # no INT8 candidates
+    out, chosen = allocate.force_int8(tables, {"a": 0.5, "b": 3.0, "c": 2.0, "d": 9.0}, 1)
+    assert chosen == ["b"] and out["b"].candidates == cands[2:] and torch.equal(out["b"].sse, tables["b"].sse[2:])
+    assert out["a"].candidates == cands[:2] and out["c"].candidates == cands[:2] and out["d"] is tables["d"]
+    assert allocate.restrict(tables["a"], lambda c: False) is tables["a"]  # nothing left: unchanged

@@ -34,6 +34,26 @@ def test_dequantize_equals_reference():
         dequantize(bad)
 
 
+def test_reference_linear_and_bit_count():
+    """``format.reference_linear`` (activation divided by the smoothing vector and rotated, contracted
+    with the stored basis) equals the product with the original-basis reconstruction; ``tensor_bpw``
+    counts what the buffers hold."""
+    from hi2_b200.format import HI2Tensor, dequantize, metadata_bits, reference_linear, tensor_bpw
+
+    cases = torch.load(GOLDEN / "dequant_golden.pt", weights_only=False)
+    g = torch.Generator().manual_seed(3)
+    for case in cases.values():
+        t = HI2Tensor(**case["fields"], shape=case["shape"], col_scale=case["col_scale"])
+        x = torch.randn(7, t.shape[1], generator=g, dtype=torch.float64)
+        got = reference_linear(x, t, DEV)
+        want = x.to(DEV) @ dequantize(t, DEV).T
+        assert got.shape == (7, t.shape[0])
+        assert ((got - want).abs().max() / want.abs().max()).item() < 1e-12
+        bits = t.codes.numel() * 32 + t.blk_params.numel() * 8 + 48 * t.shape[0] + metadata_bits(t.row_nbits, t.row_block, t.had)
+        bits += 16 * t.shape[1] if t.col_scale is not None else 0
+        assert abs(tensor_bpw(t) - bits / (t.shape[0] * t.shape[1])) < 1e-12
+
+
 def test_encode_then_dequantize_round_trip():
     """What the encoder packs is what the decoder reads: GPTQ-encode rows on the device, assemble,
     dequantise in the stored basis, and compare with the codes' own reconstruction."""
