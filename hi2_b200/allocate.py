@@ -230,3 +230,39 @@ def allocate_global(tables, target_bpw: float, sensitivity: dict | None = None,
     if best_lam != lam_hi:
         picks, bits_total = flat.solve(best_lam)
     return done(picks, bits_total, best_lam, True)
+
+
+def allocate_by_quality(tables, max_error_ratio: float, sensitivity: dict | None = None,
+                        iters: int = 80) -> Allocation:
+    """The fewest bits whose weighted error stays within ``max_error_ratio`` times the best the allowed
+    candidates can reach (1.0 = every row at its most accurate candidate); the model-wide bits per
+    weight is the result, not an input (hi2/allocate.py:156-209).  Same geometric bisection on the
+    multiplier as the reference, one solve and two small read-backs per step; ``feasible`` is False
+    when even the most accurate assignment is over the error budget (then that assignment is
+    returned)."""
+    sens = sensitivity or {}
+    dev = _lib.need_cuda(*[t.sse for t in tables])
+    total_w = sum(t.shape[0] * t.shape[1] for t in tables)
+    overhead = _overhead(tables)
+    flat = _Flat(tables, sens, dev)
+    best_cost = torch.where(flat.valid, flat.cost, torch.full_like(flat.cost, float("inf"))).min(0).values.sum()
+    budget = max_error_ratio * float(best_cost.item())
+
+    def solve(lam):
+        picks, bits = flat.solve(lam)
+        return picks, bits, float(flat.cost.gather(0, picks[None])[0].sum().item())
+
+    lam_hi = flat.upper_multiplier()
+    lo, hi = lam_hi * 1e-12, lam_hi  # a larger multiplier buys fewer bits with more error
+    picks, bits_total, err = solve(lo)
+    best_lam, feasible = lo, err <= budget
+    if feasible:
+        for _ in range(iters):
+            mid = (lo * hi) ** 0.5
+            p, b, e = solve(mid)
+            if e <= budget:
+                lo, picks, bits_total, best_lam = mid, p, b, mid
+            else:
+                hi = mid
+    ratio, frac = _summary(flat, picks)
+    return Allocation(flat.split(picks), (bits_total + overhead) / total_w, best_lam, feasible, ratio, frac)

@@ -129,3 +129,24 @@ def test_encode_many_nearest_and_refine_paths():
         assert t.code_off[-1] == t.codes.numel() and t.param_off[-1] * 2 == t.blk_params.numel()
     assert comp["comp"].shape == (r, k)
     assert torch.equal(a.row_nbits, b.row_nbits)
+
+
+def test_quality_driven_allocation_equals_reference():
+    """``allocate_by_quality`` against hi2's own function on seeded tables (tests/golden/quality_golden.pt):
+    the picks, the resulting bits per weight and the multiplier, also for a ratio nobody can meet."""
+    import pathlib
+
+    from hi2_b200.allocate import allocate_by_quality
+    from hi2_b200.calibrate import TensorTable
+
+    gold = torch.load(pathlib.Path(__file__).parent / "golden" / "quality_golden.pt", weights_only=False)
+    tables = [TensorTable(t["name"], tuple(t["shape"]), t["had"], t["sse"].to(DEV), list(t["candidates"]), t["energy"],
+                          t["n_tokens"]) for t in gold["tables"]]
+    for ratio, want in gold["cases"].items():
+        got = allocate_by_quality(tables, ratio, gold["sens"])
+        assert got.feasible == want["feasible"], ratio
+        for name, p in want["picks"].items():
+            assert torch.equal(got.picks[name].cpu(), p), (ratio, name)
+        assert got.bpw == want["bpw"] and got.lam == want["lam"]
+        assert abs(got.error_ratio - want["error_ratio"]) <= 1e-12 * want["error_ratio"]
+        assert got.frac_by_bits == pytest.approx(want["frac"])
