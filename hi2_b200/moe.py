@@ -112,6 +112,29 @@ def top_up(stats: dict, hess: dict | None, k_of: dict, min_tokens: float, all_re
     return borrowed
 
 
+def coverage(counts: dict, fallback) -> dict:
+    """Report per layer and projection group (hi2/moe.py:159-182): how many experts, the least, median
+    and most tokens an expert received, and the indices of the experts among ``fallback`` (the names
+    that borrowed statistics).  Groups in natural order (``layers.2`` before ``layers.10``)."""
+    import statistics
+
+    groups: dict[str, list] = {}
+    for name, tokens in counts.items():
+        parts = expert_parts(name)
+        if parts is not None:
+            groups.setdefault(group_key(name), []).append((parts[1], tokens, name in fallback))
+
+    def natural(key):
+        return [int(piece) if piece.isdigit() else piece for piece in re.split(r"(\d+)", key)]
+
+    report = {}
+    for key in sorted(groups, key=natural):
+        tokens = [n for _, n, _ in groups[key]]
+        report[key] = {"experts": len(tokens), "min": min(tokens), "median": statistics.median(tokens), "max": max(tokens),
+                       "fallback": sorted(e for e, _, borrowed in groups[key] if borrowed)}
+    return report
+
+
 # ---- per-expert views of fused experts -------------------------------------------------------------
 def _linear_over(weight: torch.Tensor) -> nn.Linear:
     """An ``nn.Linear`` whose weight IS ``weight`` (a slice of the fused parameter; nothing is copied)."""
@@ -210,4 +233,4 @@ def expert_weights(tables: dict, share_floor: float = 0.05) -> dict:
 
 
 __all__ = ["expert_parts", "group_key", "sibling_leader", "blend", "accumulate_routed", "top_up",
-           "expert_weights", "is_fused_experts", "ExpertViews", "unfuse_experts", "HessianStats", "ColumnStats"]
+           "expert_weights", "coverage", "is_fused_experts", "ExpertViews", "unfuse_experts", "HessianStats", "ColumnStats"]

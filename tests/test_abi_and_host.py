@@ -434,3 +434,14 @@ def test_bit_accounting_and_table_restriction():
     assert chosen == ["b"] and out["b"].candidates == cands[2:] and torch.equal(out["b"].sse, tables["b"].sse[2:])
     assert out["a"].candidates == cands[:2] and out["c"].candidates == cands[:2] and out["d"] is tables["d"]
     assert allocate.restrict(tables["a"], lambda c: False) is tables["a"]  # nothing left: unchanged
+
+
+def test_expert_coverage_report():
+    from hi2_b200.moe import coverage
+
+    counts = {f"m.layers.{l}.mlp.experts.{e}.gate_proj.weight": 10 * l + e for l in (2, 10) for e in range(4)}
+    counts["m.layers.2.self_attn.q_proj.weight"] = 99  # not an expert tensor
+    rep = coverage(counts, {"m.layers.10.mlp.experts.0.gate_proj.weight", "m.layers.10.mlp.experts.3.gate_proj.weight"})
+    assert list(rep) == ["m.layers.2.mlp.experts.*.gate_proj", "m.layers.10.mlp.experts.*.gate_proj"]
+    assert rep["m.layers.2.mlp.experts.*.gate_proj"] == {"experts": 4, "min": 20, "median": 21.5, "max": 23, "fallback": []}
+    assert rep["m.layers.10.mlp.experts.*.gate_proj"]["fallback"] == [0, 3]
