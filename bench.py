@@ -631,7 +631,7 @@ class MoeJob:
 
                 s_in.transform = (smoothing_scale(s_in.moments, self.qcfg.smooth), flags)
             L.start_factors(shared, self.qcfg, self.device, into=factors, release_scratch=True)
-            L.tabulate(weights, self.plan, shared, self.qcfg, into=tables)
+            L.tabulate(weights, self.plan, shared, self.qcfg, into=tables, grouped=True)
             for name, t in tables.items():
                 t.name = f"L{l}.{name}"
                 t.n_tokens = own_tokens[self.plan.reads[name]]  # an expert reports its own tokens (hi2/layerwise.py:230)

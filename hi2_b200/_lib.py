@@ -38,6 +38,11 @@ SIGNATURES = {
         _I,
         [_P, _P, _P, _L, _P, _I, _L, _L, _I, _P, _P, _P, _P, _L, _P, _P, _P, _P],
     ),
+    "hi2_fit_ladder_grouped": (_I, [_P, _L, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P, _P, _P]),
+    "hi2_quantize_rows_grouped": (
+        _I,
+        [_P, _P, _P, _L, _P, _P, _I, _L, _L, _I, _P, _P, _P, _P, _L, _P, _P, _P, _P],
+    ),
     "hi2_gptq_block": (_I, [_P, _L, _L, _L, _I, _P, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P]),
     "hi2_gptq_lazy_update": (_I, [_P, _L, _L, _L, _L, _P, _P, _P]),
     "hi2_gptq_round": (

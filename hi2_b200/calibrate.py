@@ -225,6 +225,45 @@ def build_table(name: str, w: torch.Tensor, stats: ColumnStats | None, cfg: Conf
     )
 
 
+def build_tables_grouped(items: list, cfg: Config) -> list:
+    """:func:`build_table` for several tensors of ONE shape that read different inputs (the experts of
+    a layer): ``items`` holds ``(name, w [R, K], stats, (smoothing vector, flags), n_tokens)`` per
+    tensor.  The stored rows of all of them lie one after the other in one buffer, their column
+    weights form a ``[G, K]`` matrix, and every candidate costs two launches for the whole group
+    instead of two per tensor; per row the arithmetic is that of :func:`build_table`.  Tables come
+    back in the order of ``items`` (their ``sse`` are views of the group's table)."""
+    if cfg.smooth_search or len(items) < 2 or any(it[3] is None for it in items):
+        return [build_table(name, w, st, cfg, transform=tr, n_tokens=n) for name, w, st, tr, n in items]
+    dev = _lib.need_cuda(*[it[1] for it in items])
+    r, k = items[0][1].shape
+    if any(tuple(it[1].shape) != (r, k) for it in items):
+        raise ValueError("build_tables_grouped: the tensors of a group must have one shape")
+    wt = torch.empty(len(items) * r, k, dtype=torch.float32, device=dev)
+    d = torch.empty(len(items), k, dtype=torch.float32, device=dev)
+    kept = []
+    for e, (_, w, st, (s16, had), _) in enumerate(items):
+        if w.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            w = w.float()
+        scale = None if s16 is None else s16.to(dev, torch.float32)
+        fwht_groups(w, had, col_scale=scale, out_dtype=torch.float32, out=wt[e * r : (e + 1) * r])
+        d[e] = _weights(st, k, had, dev, None if scale is None else 1.0 / scale)
+        kept.append((None if s16 is None else s16.clone(), had.clone()))
+    row_group = torch.arange(len(items), device=dev, dtype=torch.int32).repeat_interleave(r)
+    sse, energy = [], None
+    for i, (nb, b) in enumerate(cfg.candidates):
+        enc = encode_rows(wt, d, nb, b, cfg.effort, want_codes=False, want_energy=(i == 0), row_group=row_group)
+        sse.append(enc.sse)
+        if i == 0:
+            energy = enc.energy
+    sse = torch.stack(sse)
+    out = []
+    for e, (name, _, st, tr, n) in enumerate(items):
+        rows = slice(e * r, (e + 1) * r)
+        out.append(TensorTable(name, (r, k), kept[e][1].cpu(), sse[:, rows], list(cfg.candidates), energy[rows].sum(),
+                               n if n is not None else (st.n if st else 0), kept[e][0], transform_ref=tuple(tr)))
+    return out
+
+
 @dataclass
 class EncodeRequest:
     """One tensor for :func:`encode_many`; requests with the same ``sigma_id``, smoothing vector

@@ -134,16 +134,19 @@ __device__ __forceinline__ void block_error2(const BlockRegs<B, WIDE>& r, const 
 
 template <int B, bool WIDE>
 __global__ void __launch_bounds__(256, (B == 16 ? 3 : 2))
-fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, int64_t n_rows,
-           int64_t nb, GridSpec grid, int refits, float nmax, float* __restrict__ lo_out,
+fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d,
+           const int32_t* __restrict__ row_d, int64_t n_rows, int64_t nb, GridSpec grid, int refits, float nmax, float* __restrict__ lo_out,
            float* __restrict__ st_out, float* __restrict__ err_out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t blk = (int64_t)blockIdx.y * 8 + warp;
   if (blk >= nb) return;  // uniform over the warp
   const int64_t row = (int64_t)blockIdx.x * 32 + lane;
   const bool live = row < n_rows;
-  const float* src = w + (live ? row : n_rows - 1) * ldw + blk * B;
-  const float* dd = d + blk * B;
+  const int64_t row_c = live ? row : n_rows - 1;
+  const float* src = w + row_c * ldw + blk * B;
+  // row_d given: d is [groups, k] and row r is weighted by d[row_d[r]] (tensors that read different
+  // inputs, e.g. the experts of a layer, searched in one launch)
+  const float* dd = d + (row_d != nullptr ? (int64_t)row_d[row_c] * (nb * B) : 0) + blk * B;
 
   BlockRegs<B, WIDE> r;
 #pragma unroll
@@ -232,7 +235,7 @@ fit_kernel(const float* __restrict__ w, int64_t ldw, const float* __restrict__ d
   }
 }
 
-int launch_fit(const float* w, int64_t ldw, const float* d, const float* grid_host, int g,
+int launch_fit(const float* w, int64_t ldw, const float* d, const int32_t* row_d, const float* grid_host, int g,
                int refits, int n, int64_t n_rows, int64_t nb, int block, float* lo, float* st,
                float* err, cudaStream_t stream) {
   GridSpec spec;
@@ -241,7 +244,7 @@ int launch_fit(const float* w, int64_t ldw, const float* d, const float* grid_ho
   dim3 grid((unsigned)ceil_div(n_rows, 32), (unsigned)ceil_div(nb, 8));
   const float nmax = (float)(n - 1);
 #define HI2_FIT(BB)                                                                              \
-  fit_kernel<BB, (BB <= 32)><<<grid, 256, 0, stream>>>(w, ldw, d, n_rows, nb, spec, refits, nmax, lo, st, err)
+  fit_kernel<BB, (BB <= 32)><<<grid, 256, 0, stream>>>(w, ldw, d, row_d, n_rows, nb, spec, refits, nmax, lo, st, err)
   if (block == 16) HI2_FIT(16);
   if (block == 32) HI2_FIT(32);
   if (block == 64) HI2_FIT(64);
@@ -278,8 +281,8 @@ constexpr int ROW_UN = 4;  // quads a lane loads before it computes
 template <int B, bool CODES, bool ENERGY>
 __global__ void __launch_bounds__(ROW_THREADS, 4)
 row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
-           const float* __restrict__ w, int64_t ldw, const float* __restrict__ d, float nmax,
-           int64_t n_rows, int64_t k, uint8_t* __restrict__ params, uint16_t* __restrict__ consts,
+           const float* __restrict__ w, int64_t ldw, const float* __restrict__ d_all,
+           const int32_t* __restrict__ row_d, float nmax, int64_t n_rows, int64_t k, uint8_t* __restrict__ params, uint16_t* __restrict__ consts,
            float* __restrict__ lo_d, float* __restrict__ st_d, int64_t ldp,
            uint8_t* __restrict__ codes, float* __restrict__ sse, float* __restrict__ energy) {
   extern __shared__ float dyn[];
@@ -343,6 +346,7 @@ row_kernel(const float* __restrict__ lo_in, const float* __restrict__ st_in,
     // block's correctly rounded reciprocal and Markstein's fused correction, which gives the same
     // correctly rounded number.
     const float* wr = w + row * ldw;
+    const float* d = d_all + (row_d != nullptr ? (int64_t)row_d[row] * k : 0);  // the row's own column weights
     float acc = 0.0f, en = 0.0f;
     for (int64_t j0 = (int64_t)lane * 4; j0 < k; j0 += 128 * ROW_UN) {
       float4 wq[ROW_UN], dq[ROW_UN];
@@ -444,13 +448,13 @@ extern "C" int hi2_ladder_grid(const float* wb, const float* db, const float* gr
   if (n_rows == 0 || nb == 0) return HI2_OK;
   HI2_REQUIRE(wb && db && lo && step, "ladder_grid: null pointer");
   HI2_REQUIRE(aligned16(wb), "ladder_grid: wb must be 16-byte aligned");
-  return launch_fit(wb, nb * block, db, grid_host, g, 0, n, n_rows, nb, block, lo, step, err,
+  return launch_fit(wb, nb * block, db, nullptr, grid_host, g, 0, n, n_rows, nb, block, lo, step, err,
                     static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int hi2_fit_ladder(const float* w, int64_t ldw, const float* d, const float* grid_host,
-                              int g, int refits, int n, int64_t n_rows, int64_t k, int block,
-                              float* lo, float* step, void* stream) {
+extern "C" int hi2_fit_ladder_grouped(const float* w, int64_t ldw, const float* d, const int32_t* row_d,
+                                      const float* grid_host, int g, int refits, int n, int64_t n_rows,
+                                      int64_t k, int block, float* lo, float* step, void* stream) {
   using namespace hi2;
   HI2_REQUIRE(block_ok(block), "fit_ladder: block must be 16, 32 or 64");
   HI2_REQUIRE(k > 0 && k % block == 0, "fit_ladder: k must be a multiple of the block");
@@ -458,16 +462,22 @@ extern "C" int hi2_fit_ladder(const float* w, int64_t ldw, const float* d, const
   HI2_REQUIRE(n >= 2 && refits >= 0, "fit_ladder: bad n or refits");
   if (n_rows == 0) return HI2_OK;
   HI2_REQUIRE(w && d && lo && step, "fit_ladder: null pointer");
-  HI2_REQUIRE(aligned16(w) && ldw % 4 == 0 && ldw >= k, "fit_ladder: w alignment or ldw");
-  return launch_fit(w, ldw, d, grid_host, g, refits, n, n_rows, k / block, block, lo, step,
+  HI2_REQUIRE(aligned16(w) && aligned16(d) && ldw % 4 == 0 && ldw >= k, "fit_ladder: w, d alignment or ldw");
+  return launch_fit(w, ldw, d, row_d, grid_host, g, refits, n, n_rows, k / block, block, lo, step,
                     nullptr, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int hi2_quantize_rows(const float* lo, const float* step, const float* w, int64_t ldw,
-                                 const float* d, int nbits, int64_t n_rows, int64_t k, int block,
-                                 uint8_t* params, uint16_t* consts, float* lo_d, float* step_d,
-                                 int64_t ldp, uint8_t* codes, float* sse, float* energy,
-                                 void* stream) {
+extern "C" int hi2_fit_ladder(const float* w, int64_t ldw, const float* d, const float* grid_host,
+                              int g, int refits, int n, int64_t n_rows, int64_t k, int block,
+                              float* lo, float* step, void* stream) {
+  return hi2_fit_ladder_grouped(w, ldw, d, nullptr, grid_host, g, refits, n, n_rows, k, block, lo, step, stream);
+}
+
+extern "C" int hi2_quantize_rows_grouped(const float* lo, const float* step, const float* w, int64_t ldw,
+                                         const float* d, const int32_t* row_d, int nbits, int64_t n_rows,
+                                         int64_t k, int block, uint8_t* params, uint16_t* consts, float* lo_d,
+                                         float* step_d, int64_t ldp, uint8_t* codes, float* sse,
+                                         float* energy, void* stream) {
   using namespace hi2;
   HI2_REQUIRE(block_ok(block), "quantize_rows: block must be 16, 32 or 64");
   HI2_REQUIRE(k > 0 && k % block == 0, "quantize_rows: k must be a multiple of the block");
@@ -496,8 +506,9 @@ extern "C" int hi2_quantize_rows(const float* lo, const float* step, const float
         cudaFuncSetAttribute(row_kernel<BB, CC, EE>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                              (int)smem) != cudaSuccess)                                                    \
       return fail(HI2_ERR_LAUNCH, "quantize_rows: cannot reserve shared memory");                          \
-    row_kernel<BB, CC, EE><<<grid, ROW_THREADS, smem, s>>>(lo, step, w, ldw, d, nmax, n_rows, k, params,   \
-                                                           consts, lo_d, step_d, ldp, codes, sse, energy); \
+    row_kernel<BB, CC, EE><<<grid, ROW_THREADS, smem, s>>>(lo, step, w, ldw, d, row_d, nmax, n_rows, k,      \
+                                                           params, consts, lo_d, step_d, ldp, codes, sse,    \
+                                                           energy);                                          \
   } while (0)
 #define HI2_ROW(BB)                                     \
   do {                                                  \
@@ -512,6 +523,15 @@ extern "C" int hi2_quantize_rows(const float* lo, const float* step, const float
 #undef HI2_ROW
 #undef HI2_ROW_V
   return check_launch("quantize_rows");
+}
+
+extern "C" int hi2_quantize_rows(const float* lo, const float* step, const float* w, int64_t ldw,
+                                 const float* d, int nbits, int64_t n_rows, int64_t k, int block,
+                                 uint8_t* params, uint16_t* consts, float* lo_d, float* step_d,
+                                 int64_t ldp, uint8_t* codes, float* sse, float* energy,
+                                 void* stream) {
+  return hi2_quantize_rows_grouped(lo, step, w, ldw, d, nullptr, nbits, n_rows, k, block, params, consts, lo_d, step_d,
+                                   ldp, codes, sse, energy, stream);
 }
 
 extern "C" int hi2_ladder_sse(const uint8_t* codes, const float* w, int64_t ldw, const float* d,

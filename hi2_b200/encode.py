@@ -76,8 +76,10 @@ class Encoded:
 
 
 def encode_rows(w: torch.Tensor, d: torch.Tensor, nbits: int, block: int, effort: str = "normal",
-                *, want_codes: bool = True, want_energy: bool = False) -> Encoded:
-    """Quantise ``w [N, K]`` (stored basis) at ``(nbits, block)`` under column weights ``d [K]``.
+                *, want_codes: bool = True, want_energy: bool = False, row_group=None) -> Encoded:
+    """Quantise ``w [N, K]`` (stored basis) at ``(nbits, block)`` under column weights ``d [K]``, or
+    ``d [G, K]`` with ``row_group [N]`` naming every row's vector (default: ``G`` equal groups of
+    consecutive rows).
 
     ``want_codes=False`` skips the code bytes (the tables only read ``sse``); ``want_energy``
     attaches ``energy [N] = sum d * w^2`` as attribute ``energy`` of the result."""
@@ -87,9 +89,11 @@ def encode_rows(w: torch.Tensor, d: torch.Tensor, nbits: int, block: int, effort
     if w.dtype != torch.float32 or w.stride(1) != 1:
         w = w.float().contiguous()
     d = d.to(dev, torch.float32).contiguous()
-    lo, st = _ladder.fit(w, d, cfg["grid"], cfg["ls"], 2**nbits, block)
+    if d.dim() == 2 and d.shape[0] > 1 and row_group is None:  # the index is made once for both launches
+        row_group = _ladder._row_d(d, n_rows, k, None, "encode_rows")
+    lo, st = _ladder.fit(w, d, cfg["grid"], cfg["ls"], 2**nbits, block, row_group)
     out = _ladder.quantize_rows(lo, st, nbits, block, k, w, d, want_codes=want_codes, want_sse=True,
-                                want_energy=want_energy)
+                                want_energy=want_energy, row_group=row_group)
     enc = Encoded(out.get("codes"), out["params"], out["consts"], out["sse"])
     if want_energy:
         enc.energy = out["energy"]

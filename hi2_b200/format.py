@@ -28,12 +28,14 @@ def hadamard16(dtype: torch.dtype = torch.float64, device="cpu") -> torch.Tensor
 
 
 def fwht_groups(x: torch.Tensor, flags: torch.Tensor, col_scale: torch.Tensor | None = None,
-                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+                out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Transform the flagged 16-column groups of ``x[..., K]`` (an involution).
 
-    Extensions over the reference signature, both optional: ``col_scale`` (``[K]``, multiplied
-    in fp32 before the rotation, as ``W * s`` in hi2/calibrate.py:247-250) and ``out_dtype``
-    (``torch.float32`` lets a bf16/fp16 tensor be cast, scaled and rotated in one pass)."""
+    Extensions over the reference signature, all optional: ``col_scale`` (``[K]``, multiplied
+    in fp32 before the rotation, as ``W * s`` in hi2/calibrate.py:247-250), ``out_dtype``
+    (``torch.float32`` lets a bf16/fp16 tensor be cast, scaled and rotated in one pass) and ``out``
+    (a contiguous tensor of the result's shape and dtype to write into, e.g. a slice of a buffer
+    that holds several tensors one after the other)."""
     k = x.shape[-1]
     if k % GROUP:
         raise ValueError(f"K={k} must be a multiple of {GROUP}")
@@ -44,7 +46,12 @@ def fwht_groups(x: torch.Tensor, flags: torch.Tensor, col_scale: torch.Tensor | 
         raise ValueError(f"unsupported dtype {x.dtype}")
     out_dtype = out_dtype or x.dtype
     xc = x.contiguous()
-    y = torch.empty(xc.shape, dtype=out_dtype, device=dev)
+    if out is None:
+        y = torch.empty(xc.shape, dtype=out_dtype, device=dev)
+    else:
+        if out.shape != xc.shape or out.dtype != out_dtype or out.device != dev or not out.is_contiguous():
+            raise ValueError("fwht_groups: out must be a contiguous tensor of the result's shape, dtype and device")
+        y = out
     fl = _lib.upload(flags, dev, torch.uint8)
     cs = None
     if col_scale is not None:

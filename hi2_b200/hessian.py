@@ -302,6 +302,42 @@ def _prepare(ji: int, job: GptqJob, s: int, step_rows: int, effort: str) -> _Uni
                  (cols // job.block).to(torch.int32))
 
 
+# Row units of several jobs are prepared together when there are many small ones (a layer of experts
+# has a thousand): jobs of one width that share (nbits, block) and keep their column order.
+PREPARE_TOGETHER_MIN = 4
+PREPARE_TOGETHER_MAX_ELEMS = 1 << 22  # mean size of a unit up to which gathering them into one buffer pays
+
+
+def _prepare_together(pieces: list, jobs: list, step_rows: int, effort: str) -> list:
+    """``_prepare`` for the units ``pieces = [(job index, first row)]`` of jobs with one width,
+    ``(nbits, block)`` and no column permutation: their rows are gathered into one buffer, the ladder
+    search runs once over all of them with the column weights of each unit's job
+    (``d [units, K]`` and a row index), the parameter bytes and decoded ladders are made in one
+    launch, and every unit gets views.  Per row the arithmetic is that of :func:`_prepare`."""
+    first = jobs[pieces[0][0]]
+    dev, k = first.w.device, first.w.shape[1]
+    cfg = EFFORT[effort]
+    srcs = []
+    for ji, s0 in pieces:
+        src = jobs[ji].w[s0 : s0 + step_rows]
+        srcs.append(src if src.dtype == torch.float32 else src.float())
+    sizes = [x.shape[0] for x in srcs]
+    rows = torch.cat(srcs)
+    d = torch.stack([jobs[ji].d.to(dev, torch.float32) for ji, _ in pieces])
+    row_group = _lib.upload(torch.repeat_interleave(torch.arange(len(pieces), dtype=torch.int32), torch.tensor(sizes)), dev)
+    lo, st = _ladder.fit(rows, d, cfg["grid"], cfg["ls"], 2**first.nbits, first.block, row_group)
+    q = _ladder.quantize_rows(lo, st, first.nbits, first.block, k, want_decoded=True, ldp=k // GROUP)
+    work = rows.clone()
+    blk_of = (torch.arange(k, device=dev) // first.block).to(torch.int32)
+    units, off = [], 0
+    for (ji, s0), n in zip(pieces, sizes):
+        cut = slice(off, off + n)
+        units.append(_Unit(ji, s0, n, work[cut], rows[cut], q["params"][cut], q["consts"][cut], q["lo_d"][cut],
+                           q["step_d"][cut], blk_of))
+        off += n
+    return units
+
+
 # factors at least this wide take the tensor-core trailing update (below it the FMA product wins)
 TC_MIN_K = 512
 
@@ -411,11 +447,20 @@ def encode_jobs_gptq(jobs: list[GptqJob], effort: str = "normal", backend: str |
     checks: list = []
     joins = []
     for gi, ((dev, k), jis) in enumerate(sorted(by_width.items(), key=lambda kv: -kv[0][1])):
-        mine: list[_Unit] = []
         step_rows = max(1, ROW_ELEMS // k)
-        for ji in jis:
-            for s in range(0, jobs[ji].w.shape[0], step_rows):
-                mine.append(_prepare(ji, jobs[ji], s, step_rows, effort))
+        pieces = [(ji, s) for ji in jis for s in range(0, jobs[ji].w.shape[0], step_rows)]
+        alike: dict[tuple, list[int]] = {}
+        for at, (ji, _) in enumerate(pieces):
+            if jobs[ji].perm is None:
+                alike.setdefault((jobs[ji].nbits, jobs[ji].block), []).append(at)
+        ready: dict[int, _Unit] = {}
+        for members in alike.values():
+            elems = sum(min(step_rows, jobs[pieces[at][0]].w.shape[0] - pieces[at][1]) for at in members) * k
+            if len(members) >= PREPARE_TOGETHER_MIN and elems <= PREPARE_TOGETHER_MAX_ELEMS * len(members):
+                for at, unit in zip(members, _prepare_together([pieces[at] for at in members], jobs, step_rows, effort)):
+                    ready[at] = unit
+        mine: list[_Unit] = [ready[at] if at in ready else _prepare(ji, jobs[ji], s, step_rows, effort)
+                             for at, (ji, s) in enumerate(pieces)]
         units.extend(mine)
         bl: list[list[_Unit]] = [[]]
         for x in mine:

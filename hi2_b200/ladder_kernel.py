@@ -41,17 +41,37 @@ def ladder_grid(wb: torch.Tensor, db: torch.Tensor, grid: tuple, n: int):
     return lo, st, err
 
 
-def fit(w: torch.Tensor, d: torch.Tensor, grid: tuple, refits: int, n: int, block: int):
+def _row_d(d: torch.Tensor, rows: int, k: int, row_group, what: str):
+    """None for one weight vector ``d [K]``.  For ``d [G, K]`` the int32 index ``[N]`` of every row's
+    vector: ``row_group`` as given, or, without one, ``G`` equal groups of consecutive rows."""
+    if d.dim() == 1 or d.numel() == k:
+        return None
+    if d.dim() != 2 or d.shape[1] != k:
+        raise ValueError(f"{what}: d must be [K] or [G, K]")
+    if row_group is not None:
+        if row_group.numel() != rows:
+            raise ValueError(f"{what}: row_group must name a vector for every row")
+        return row_group.to(d.device, torch.int32).contiguous()
+    if rows % d.shape[0]:
+        raise ValueError(f"{what}: without row_group the rows must be a multiple of the number of vectors")
+    return torch.arange(d.shape[0], device=d.device, dtype=torch.int32).repeat_interleave(rows // d.shape[0])
+
+
+def fit(w: torch.Tensor, d: torch.Tensor, grid: tuple, refits: int, n: int, block: int, row_group=None):
     """Grid search plus ``refits`` least-squares refits (hi2/encode.py:53-92) on rows
-    ``w [N, K]`` (fp32, unit column stride); returns ``lo, step [N, K / block]``."""
+    ``w [N, K]`` (fp32, unit column stride); returns ``lo, step [N, K / block]``.  ``d`` is ``[K]``,
+    or ``[G, K]`` with ``row_group [N]`` naming every row's vector (default: ``G`` equal groups of
+    consecutive rows)."""
     dev = _lib.need_cuda(w, d)
     rows, k = w.shape
     if w.dtype != torch.float32 or w.stride(1) != 1:
         raise ValueError("fit: w must be fp32 with unit column stride")
+    group = _row_d(d, rows, k, row_group, "fit")
+    d = d.contiguous()
     lo = torch.empty(rows, k // block, dtype=torch.float32, device=dev)
     st = torch.empty(rows, k // block, dtype=torch.float32, device=dev)
     _lib.call(
-        "hi2_fit_ladder", _lib.ptr(w), w.stride(0), _lib.ptr(d), _lib.host_floats(grid), len(grid),
+        "hi2_fit_ladder_grouped", _lib.ptr(w), w.stride(0), _lib.ptr(d), _lib.ptr(group), _lib.host_floats(grid), len(grid),
         int(refits), int(n), rows, k, int(block), _lib.ptr(lo), _lib.ptr(st), _lib.stream(dev),
     )
     return lo, st
@@ -59,7 +79,7 @@ def fit(w: torch.Tensor, d: torch.Tensor, grid: tuple, refits: int, n: int, bloc
 
 def quantize_rows(lo, step, nbits: int, block: int, k: int, w=None, d=None, *, want_params=True,
                   want_decoded=False, ldp: int | None = None, want_codes=False, want_sse=False,
-                  want_energy=False):
+                  want_energy=False, row_group=None):
     """Row-wide quantisation of ladders ``lo, step [N, K/block]`` (hi2/encode.py:95-119), decode
     (hi2/format.py:45-60) and, on request, nearest codes / weighted error / energy of ``w``
     (hi2/encode.py:146-157).  Returns a dict of the requested tensors."""
@@ -82,14 +102,15 @@ def quantize_rows(lo, step, nbits: int, block: int, k: int, w=None, d=None, *, w
         out["sse"] = torch.empty(rows, dtype=torch.float32, device=dev)
     if want_energy:
         out["energy"] = torch.empty(rows, dtype=torch.float32, device=dev)
-    ldw = 0
+    ldw, group = 0, None
     if w is not None:
         if w.dtype != torch.float32 or w.stride(1) != 1:
             raise ValueError("quantize_rows: w must be fp32 with unit column stride")
         ldw = w.stride(0)
+        group = _row_d(d, rows, k, row_group, "quantize_rows")
         d = d.contiguous().float()
     _lib.call(
-        "hi2_quantize_rows", _lib.ptr(lo), _lib.ptr(step), _lib.ptr(w), ldw, _lib.ptr(d), int(nbits),
+        "hi2_quantize_rows_grouped", _lib.ptr(lo), _lib.ptr(step), _lib.ptr(w), ldw, _lib.ptr(d), _lib.ptr(group), int(nbits),
         rows, k, int(block), _lib.ptr(out.get("params")), _lib.ptr(out.get("consts")),
         _lib.ptr(out.get("lo_d")), _lib.ptr(out.get("step_d")), ldp or nb, _lib.ptr(out.get("codes")),
         _lib.ptr(out.get("sse")), _lib.ptr(out.get("energy")), _lib.stream(dev),

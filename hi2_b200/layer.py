@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from .calibrate import Config, EncodeRequest, TensorTable, build_table, encode_many, smoothing_scale
+from .calibrate import Config, EncodeRequest, TensorTable, build_table, build_tables_grouped, encode_many, smoothing_scale
 from .format import GROUP, HI2Tensor
 from .hessian import HessianStats
 from .stats import ColumnStats
@@ -109,15 +109,26 @@ def start_factors(shared: dict, cfg: Config, device, only: str | None = None, in
 
 
 def tabulate(weights: dict, plan: LayerPlan, shared: dict, cfg: Config, only: str | None = None,
-             into: dict | None = None) -> dict:
-    """Error tables of every weight ``{name: [R, K] tensor}`` (or of those reading input ``only``)."""
+             into: dict | None = None, grouped: bool = False) -> dict:
+    """Error tables of every weight ``{name: [R, K] tensor}`` (or of those reading input ``only``).
+    ``grouped`` tabulates the weights of one shape together, a candidate at a time for all of them
+    (:func:`hi2_b200.calibrate.build_tables_grouped`): what a layer of experts wants, whose hundreds
+    of small tables are otherwise bound by the host's launch rate."""
     tables = into if into is not None else {}
-    for name, w in weights.items():
-        if only is not None and plan.reads[name] != only:
-            continue
-        s = shared[plan.reads[name]]
-        tables[name] = build_table(name, w, s.moments, cfg, transform=s.transform)
-    return tables
+    names = [n for n in weights if only is None or plan.reads[n] == only]
+    if not grouped:
+        for name in names:
+            s = shared[plan.reads[name]]
+            tables[name] = build_table(name, weights[name], s.moments, cfg, transform=s.transform)
+        return tables
+    by_shape: dict = {}
+    for name in names:
+        by_shape.setdefault((tuple(weights[name].shape), weights[name].dtype), []).append(name)
+    for group in by_shape.values():
+        items = [(n, weights[n], shared[plan.reads[n]].moments, shared[plan.reads[n]].transform, None) for n in group]
+        for n, t in zip(group, build_tables_grouped(items, cfg)):
+            tables[n] = t
+    return {n: tables[n] for n in names} if into is None else tables
 
 
 def encode(weights: dict, plan: LayerPlan, shared: dict, tables: dict, picks: dict, cfg: Config,

@@ -104,6 +104,19 @@ int hi2_quantize_rows(const float* lo, const float* step, const float* w, int64_
                       const float* d, int nbits, int64_t n_rows, int64_t k, int block,
                       uint8_t* params, uint16_t* consts, float* lo_d, float* step_d, int64_t ldp,
                       uint8_t* codes, float* sse, float* energy, void* stream);
+/* The same two with column weights per row: d is [groups, k] and row r is weighted by d[row_d[r]]
+ * (row_d int32 [n_rows] on the device; null: one d for all rows, as above).  Rows of tensors that
+ * read different inputs (the experts of a layer, hi2/layerwise.py:636-672) are searched and
+ * quantised in one launch this way; per row the arithmetic is the one above.  No counterpart in the
+ * reference. */
+int hi2_fit_ladder_grouped(const float* w, int64_t ldw, const float* d, const int32_t* row_d,
+                           const float* grid_host, int g, int refits, int n, int64_t n_rows,
+                           int64_t k, int block, float* lo, float* step, void* stream);
+int hi2_quantize_rows_grouped(const float* lo, const float* step, const float* w, int64_t ldw,
+                              const float* d, const int32_t* row_d, int nbits, int64_t n_rows,
+                              int64_t k, int block, uint8_t* params, uint16_t* consts, float* lo_d,
+                              float* step_d, int64_t ldp, uint8_t* codes, float* sse, float* energy,
+                              void* stream);
 
 /* ---- GPTQ ----------------------------------------------------------------------------------
  * hi2/gptq_kernel.py:59-127 gptq_block: one lazy block [i1, i1+len) for every row.

@@ -192,6 +192,30 @@ def test_batched_jobs_equal_single_calls(monkeypatch):
             assert torch.equal(getattr(got, f), getattr(ref, f)), f
 
 
+def test_many_small_jobs_prepared_together_equal_single_calls(monkeypatch):
+    """A layer of experts: many small jobs of one width, several (nbits, block) among them, each with
+    column weights and a factor of its own.  Their ladders are searched in one launch per
+    (nbits, block) over a gathered buffer; results must equal one call per job, bit for bit.  Jobs
+    with a column permutation, and kinds with fewer than four jobs, still go one by one."""
+    import hi2_b200.hessian as hm
+
+    k = 256
+    jobs = []
+    for i in range(14):
+        nb, b = ((2, 32), (4, 64), (2, 16))[i % 3] if i < 12 else (4, 16)
+        w, d, u, perm, _ = correlated_layer(9 + 3 * i, k, 100 + i, act_order=(i == 5))
+        jobs.append(hm.GptqJob(w.to(DEV), d.to(DEV), u.to(DEV), nb, b, None if perm is None else perm.to(DEV)))
+    refs = [hm.encode_rows_gptq(j.w, j.d, j.u, j.nbits, j.block, "fast", j.perm) for j in jobs]
+    calls = []
+    together = hm._prepare_together
+    monkeypatch.setattr(hm, "_prepare_together", lambda pieces, *a: calls.append(len(pieces)) or together(pieces, *a))
+    got = hm.encode_jobs_gptq(jobs, "fast", comp=True)
+    assert sorted(calls) == [4, 4]  # (2, 32) lost job 5 to its permutation and (4, 16) has two jobs only
+    for g_, ref in zip(got, refs):
+        for f in ("codes", "params", "consts", "sse", "comp"):
+            assert torch.equal(getattr(g_, f), getattr(ref, f)), f
+
+
 def test_gptq_block_entry_point_matches_driver():
     """The reference-shaped per-block entry point (hi2/hessian.py:304-312 drives it) gives the
     same codes as the fused driver."""

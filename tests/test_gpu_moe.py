@@ -109,3 +109,41 @@ def test_moe_job_routes_tops_up_and_encodes_per_expert():
         assert abs(share[f"L0.experts.{ex}.down_proj"] - max(layer0[ex] / mean, 0.05) / 8) < 1e-12
     t = packed[(1, "experts.3.down_proj")]
     assert t.shape == (cfg["hidden"], cfg["expert_ffn"]) and int(t.code_off[-1]) == t.codes.numel()
+
+
+def test_tables_of_a_group_of_experts_equal_tables_one_by_one():
+    """``calibrate.build_tables_grouped`` (the stored rows of all experts in one buffer, column weights
+    per group of rows, two launches per candidate for the whole group) against ``build_table`` per
+    expert: ``sse``, energy, flags, smoothing vector bit for bit; and through ``layer.tabulate`` with
+    mixed shapes, where only equal shapes are grouped."""
+    import torch
+
+    from hi2_b200 import layer as L
+    from hi2_b200.calibrate import Config, build_table, build_tables_grouped
+    from tests.helpers import DEV, activations, gen
+
+    g = gen(5)
+    cfg = Config(effort="fast")
+    n_exp, r, k = 5, 72, 256  # 72 rows: a warp of the search kernel straddles two experts
+    acts = {f"e{e}": activations(700 + 50 * e, k, 70 + e, spread=1.0, dtype=torch.bfloat16).to(DEV) for e in range(n_exp)}
+    shared = L.accumulate(acts, DEV)
+    L.finish_statistics(shared, cfg)
+    ws = {f"e{e}": (torch.randn(r, k, generator=g) * 0.03).bfloat16().to(DEV) for e in range(n_exp)}
+    items = [(n, ws[n], shared[n].moments, shared[n].transform, 123 + i) for i, n in enumerate(ws)]
+    many = build_tables_grouped(items, cfg)
+    for (name, w, st, tr, n), got in zip(items, many):
+        want = build_table(name, w, st, cfg, transform=tr, n_tokens=n)
+        assert got.name == name and got.n_tokens == n and got.shape == want.shape and got.candidates == want.candidates
+        assert torch.equal(got.sse, want.sse) and torch.equal(got.energy, want.energy)
+        assert torch.equal(got.had, want.had) and torch.equal(got.col_scale, want.col_scale)
+        assert got.transform_ref[0] is tr[0] and got.transform_ref[1] is tr[1]
+    # through the layer: three shapes, one of them alone in its group
+    plan = L.LayerPlan({**{f"a{e}": f"e{e}" for e in range(n_exp)}, **{f"b{e}": f"e{e}" for e in range(2)}, "c": "e0"})
+    weights = {**{f"a{e}": ws[f"e{e}"] for e in range(n_exp)},
+               **{f"b{e}": (torch.randn(40, k, generator=g) * 0.03).bfloat16().to(DEV) for e in range(2)},
+               "c": (torch.randn(24, k, generator=g) * 0.03).float().to(DEV)}
+    one = L.tabulate(weights, plan, shared, cfg)
+    grouped = L.tabulate(weights, plan, shared, cfg, grouped=True)
+    assert list(grouped) == list(one)
+    for name in one:
+        assert torch.equal(grouped[name].sse, one[name].sse) and torch.equal(grouped[name].energy, one[name].energy), name
